@@ -1,0 +1,97 @@
+// Shared host/device helpers of the eddl_b200 CUDA library (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+#include "eddl_b200.h"
+
+#define EDDLB200_MAX_DEVICES 64
+#define EDDLB200_NUM_SMS 148          // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+
+struct ncclComm;
+
+namespace eb {
+
+struct DevCtx;
+
+// Returns the initialised context of `dev` (creating it on first use) or nullptr
+// with last_error set.  Makes `dev` the current device of the calling thread.
+DevCtx *ctx(int dev);
+cudaStream_t stream_of(DevCtx *c);
+// Stream-ordered scratch of at least `bytes` bytes, reused by every kernel that
+// runs on the device's compute stream (valid until the next scratch() call).
+void *scratch(DevCtx *c, size_t bytes);
+// Pinned host words + device words used to return scalars (loss, accuracy).
+float *host_scalars(DevCtx *c);    // 64 floats
+float *dev_scalars(DevCtx *c);     // 64 floats
+ncclComm *comm_of(DevCtx *c);
+int comm_nranks(DevCtx *c);
+void count_launch(DevCtx *c, unsigned n = 1);
+int set_error(int code, const char *fmt, ...);
+int cuda_status(cudaError_t e, const char *what);
+
+}  // namespace eb
+
+#define EB_CTX(dev)                                   \
+    eb::DevCtx *cx = eb::ctx(dev);                    \
+    if (!cx) return EDDLB200_ENOINIT;                 \
+    cudaStream_t st = eb::stream_of(cx);              \
+    (void)st
+
+#define EB_LAUNCH_CHECK(what)                                         \
+    do {                                                              \
+        eb::count_launch(cx);                                         \
+        cudaError_t e__ = cudaGetLastError();                         \
+        if (e__ != cudaSuccess) return eb::cuda_status(e__, what);    \
+    } while (0)
+
+#define EB_REQUIRE(cond, what)                                                   \
+    do {                                                                         \
+        if (!(cond)) return eb::set_error(EDDLB200_EINVAL, "%s: %s", what, #cond); \
+    } while (0)
+
+namespace eb {
+
+__host__ __device__ inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Grid for a grid-stride elementwise kernel over `work` thread-items:
+// a multiple of the SM count, at most `waves` resident waves of blocks.
+inline int grid_for(size_t work_items, int block, int max_blocks_per_sm = 8) {
+    size_t blocks = ceil_div(work_items, (size_t)block);
+    size_t cap = (size_t)EDDLB200_NUM_SMS * max_blocks_per_sm;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+inline bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Block-wide sum; every thread gets the result.  `sm` holds >= 32 floats.
+__device__ __forceinline__ float block_sum(float v, float *sm) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sm[w] = v;
+    __syncthreads();
+    float r = (lane < nw) ? sm[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+// Streaming (evict-first) loads/stores for data touched once per pass.
+__device__ __forceinline__ float4 ld_stream4(const float *p) { return __ldcs(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ void st_stream4(float *p, float4 v) { __stcs(reinterpret_cast<float4 *>(p), v); }
+#endif
+
+}  // namespace eb

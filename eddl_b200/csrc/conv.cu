@@ -1,0 +1,115 @@
+// Conv2D C-ABI entry points: argument checks, kernel selection, bias gradient,
+// split-K combine.  See conv_tc.cu (tcgen05 tensor-core path) and conv_simt.cu
+// (exact-fp32 FMA path).
+#include <cstdlib>
+#include "common.cuh"
+#include "conv_common.cuh"
+
+namespace {
+
+using namespace eb;
+
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ part, float *__restrict__ out, size_t count, int splits) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float s = 0.f;
+        for (int z = 0; z < splits; z++) s += part[(size_t)z * count + i];
+        out[i] = __fadd_rn(out[i], s);
+    }
+}
+
+// gbias[k] += sum_{n,p,q} dy[n,k,p,q]   (cpu_conv2D_grad, src/hardware/cpu/nn/cpu_conv.cpp:466-478)
+__global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict__ dy, float *__restrict__ gbias, int n, int k, int pq) {
+    __shared__ float sm[32];
+    const int kk = blockIdx.x;
+    float s = 0.f;
+    const long long total = (long long)n * pq;
+    for (long long t = threadIdx.x; t < total; t += blockDim.x) {
+        const int img = (int)(t / pq), r = (int)(t - (long long)img * pq);
+        s += dy[((size_t)img * k + kk) * pq + r];
+    }
+    s = block_sum(s, sm);
+    if (threadIdx.x == 0) gbias[kk] = __fadd_rn(gbias[kk], s);
+}
+
+int check(const char *what, const ConvGeom &g) {
+    if (g.n < 0 || g.c <= 0 || g.ih <= 0 || g.iw <= 0 || g.k <= 0 || g.kr <= 0 || g.kc <= 0 || g.oh <= 0 || g.ow <= 0 ||
+        g.sr <= 0 || g.sc <= 0 || g.pt < 0 || g.pl < 0)
+        return set_error(EDDLB200_EINVAL, "%s: bad geometry", what);
+    if ((long long)g.n * g.c * g.ih * g.iw >= 0x7fffffffLL || (long long)g.n * g.k * g.oh * g.ow >= 0x7fffffffLL ||
+        (long long)g.k * g.c * g.kr * g.kc >= 0x7fffffffLL)
+        return set_error(EDDLB200_ELIMIT, "%s: tensor larger than 2^31 elements", what);
+    return 0;
+}
+
+// EDDL_B200_CONV=simt forces the FMA path (used by tests to compare the two paths).
+bool tc_enabled() {
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("EDDL_B200_CONV"); v = (e && e[0] == 's') ? 0 : 1; }
+    return v == 1;
+}
+
+}  // namespace
+
+namespace eb {
+int splitk_reduce_accumulate(DevCtx *cx, cudaStream_t st, const float *part, float *out, size_t count, int splits) {
+    splitk_reduce_kernel<<<grid_for(count, 256), 256, 0, st>>>(part, out, count, splits);
+    EB_LAUNCH_CHECK("splitk_reduce");
+    return 0;
+}
+}  // namespace eb
+
+using namespace eb;
+
+extern "C" {
+
+int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias, float *y,
+                        int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
+                        int sr, int sc, int pad_top, int pad_left, int precision) {
+    EB_CTX(dev);
+    ConvGeom g{n, c, ih, iw, k, kr, kc, oh, ow, sr, sc, pad_top, pad_left};
+    if (int r = check("gpu_conv2D", g)) return r;
+    EB_REQUIRE(x && w && y, "gpu_conv2D");
+    if (n == 0) return 0;
+    if (tc_enabled()) {
+        int r = conv_tc_fwd(cx, st, g, x, w, bias, y, precision);
+        if (r != 1) return r;
+    }
+    return conv_simt_fwd(cx, st, g, x, w, bias, y);
+}
+
+int eddlb200_conv2d_bwd_data(int dev, const float *dy, const float *w, float *dx,
+                             int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
+                             int sr, int sc, int pad_top, int pad_left, int precision) {
+    EB_CTX(dev);
+    ConvGeom g{n, c, ih, iw, k, kr, kc, oh, ow, sr, sc, pad_top, pad_left};
+    if (int r = check("gpu_conv2D_back", g)) return r;
+    EB_REQUIRE(dy && w && dx, "gpu_conv2D_back");
+    if (n == 0) return 0;
+    if (tc_enabled()) {
+        int r = conv_tc_bwd_data(cx, st, g, dy, w, dx, precision);
+        if (r != 1) return r;
+    }
+    return conv_simt_bwd_data(cx, st, g, dy, w, dx);
+}
+
+int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *gw, float *gbias,
+                               int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
+                               int sr, int sc, int pad_top, int pad_left, int precision) {
+    EB_CTX(dev);
+    ConvGeom g{n, c, ih, iw, k, kr, kc, oh, ow, sr, sc, pad_top, pad_left};
+    if (int r = check("gpu_conv2D_grad", g)) return r;
+    EB_REQUIRE(x && dy && gw, "gpu_conv2D_grad");
+    if (n == 0) return 0;
+    if (gbias) {
+        bias_grad_kernel<<<k, 256, 0, st>>>(dy, gbias, n, k, oh * ow);
+        EB_LAUNCH_CHECK("gpu_conv2D_grad(bias)");
+    }
+    if (tc_enabled()) {
+        int r = conv_tc_bwd_weight(cx, st, g, x, dy, gw, precision);
+        if (r != 1) return r;
+    }
+    return conv_simt_bwd_weight(cx, st, g, x, dy, gw);
+}
+
+}  // extern "C"

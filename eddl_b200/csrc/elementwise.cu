@@ -1,0 +1,200 @@
+// Bandwidth-bound elementwise kernels: fill, axpby, scale, sqr, sqrt, clamp, el_div,
+// el_mult, ReLU forward/backward, CCE delta, padding.
+// Replaces the one-thread-per-element kernels of EDDL's src/hardware/gpu/gpu_math_kernels.cu,
+// gpu_core_kernels.cu and nn/gpu_activations_kernels.cu:21-41.  Each kernel is a
+// grid-stride loop over float4 (16-byte, fully coalesced) with a scalar tail; the
+// grid is a multiple of the 148 SMs.  Arithmetic is written with explicit
+// round-to-nearest intrinsics where the reference evaluates a*b+c in two roundings,
+// so that results are bit-identical to its CPU code (no FMA contraction).
+#include "common.cuh"
+
+namespace {
+
+using namespace eb;
+
+constexpr int kBlock = 256;
+
+template <typename F>
+__global__ void __launch_bounds__(kBlock) map1_kernel(const float *a, float *b, size_t n4, size_t n, F f) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t j = i; j < n4; j += stride) {
+        float4 v = *reinterpret_cast<const float4 *>(a + 4 * j);
+        v.x = f(v.x); v.y = f(v.y); v.z = f(v.z); v.w = f(v.w);
+        *reinterpret_cast<float4 *>(b + 4 * j) = v;
+    }
+    for (size_t j = 4 * n4 + i; j < n; j += stride) b[j] = f(a[j]);
+}
+
+template <typename F>
+__global__ void __launch_bounds__(kBlock) map1_scalar_kernel(const float *a, float *b, size_t n, F f) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride) b[j] = f(a[j]);
+}
+
+// c = f(a, b, c)
+template <typename F>
+__global__ void __launch_bounds__(kBlock) map3_kernel(const float *a, const float *b, float *c, size_t n4, size_t n, F f) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t j = i; j < n4; j += stride) {
+        float4 x = *reinterpret_cast<const float4 *>(a + 4 * j);
+        float4 y = *reinterpret_cast<const float4 *>(b + 4 * j);
+        float4 z = F::reads_c ? *reinterpret_cast<const float4 *>(c + 4 * j) : make_float4(0, 0, 0, 0);
+        z.x = f(x.x, y.x, z.x); z.y = f(x.y, y.y, z.y); z.z = f(x.z, y.z, z.z); z.w = f(x.w, y.w, z.w);
+        *reinterpret_cast<float4 *>(c + 4 * j) = z;
+    }
+    for (size_t j = 4 * n4 + i; j < n; j += stride) c[j] = f(a[j], b[j], F::reads_c ? c[j] : 0.f);
+}
+
+template <typename F>
+__global__ void __launch_bounds__(kBlock) map3_scalar_kernel(const float *a, const float *b, float *c, size_t n, F f) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride) c[j] = f(a[j], b[j], F::reads_c ? c[j] : 0.f);
+}
+
+template <typename F>
+int launch1(DevCtx *cx, cudaStream_t st, const float *a, float *b, size_t n, F f, const char *what) {
+    if (n == 0) return 0;
+    if (!a || !b) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
+    if (aligned16(a) && aligned16(b)) {
+        size_t n4 = n / 4;
+        map1_kernel<<<grid_for(n4 ? n4 : 1, kBlock), kBlock, 0, st>>>(a, b, n4, n, f);
+    } else {
+        map1_scalar_kernel<<<grid_for(n, kBlock), kBlock, 0, st>>>(a, b, n, f);
+    }
+    EB_LAUNCH_CHECK(what);
+    return 0;
+}
+
+template <typename F>
+int launch3(DevCtx *cx, cudaStream_t st, const float *a, const float *b, float *c, size_t n, F f, const char *what) {
+    if (n == 0) return 0;
+    if (!a || !b || !c) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
+    if (aligned16(a) && aligned16(b) && aligned16(c)) {
+        size_t n4 = n / 4;
+        map3_kernel<<<grid_for(n4 ? n4 : 1, kBlock), kBlock, 0, st>>>(a, b, c, n4, n, f);
+    } else {
+        map3_scalar_kernel<<<grid_for(n, kBlock), kBlock, 0, st>>>(a, b, c, n, f);
+    }
+    EB_LAUNCH_CHECK(what);
+    return 0;
+}
+
+struct FillF { float v; __device__ float operator()(float) const { return v; } };
+struct ScaleF { float v; __device__ float operator()(float x) const { return __fmul_rn(x, v); } };
+struct AddcF { float v; __device__ float operator()(float x) const { return __fadd_rn(x, v); } };
+struct SqrF { __device__ float operator()(float x) const { return __fmul_rn(x, x); } };
+struct SqrtF { __device__ float operator()(float x) const { return __fsqrt_rn(x); } };
+struct ClampF { float lo, hi; __device__ float operator()(float x) const { return x < lo ? lo : (x > hi ? hi : x); } };
+struct ReluF { __device__ float operator()(float x) const { return x > 0.f ? x : 0.f; } };
+
+// gpu_add: C = scA*A + scB*B (+ C).  Reference (cpu_math.cpp cpu_add): two products, one sum,
+// then "+=" when incC -- four roundings, reproduced here.
+template <bool INC> struct AxpbyF {
+    static constexpr bool reads_c = INC;
+    float sa, sb;
+    __device__ float operator()(float a, float b, float c) const {
+        float r = __fadd_rn(__fmul_rn(sa, a), __fmul_rn(sb, b));
+        return INC ? __fadd_rn(c, r) : r;
+    }
+};
+template <bool INC> struct DivF {
+    static constexpr bool reads_c = INC;
+    __device__ float operator()(float a, float b, float c) const { float r = __fdiv_rn(a, b); return INC ? __fadd_rn(c, r) : r; }
+};
+template <bool INC> struct MulF {
+    static constexpr bool reads_c = INC;
+    __device__ float operator()(float a, float b, float c) const { float r = __fmul_rn(a, b); return INC ? __fadd_rn(c, r) : r; }
+};
+// pd += (i > 0) ? d : 0      a = d, b = i, c = pd
+struct ReluBwdF {
+    static constexpr bool reads_c = true;
+    __device__ float operator()(float d, float i, float pd) const { return i > 0.f ? __fadd_rn(pd, d) : pd; }
+};
+// delta = -y * (1.0f / (p + 1e-7))   a = y_true, b = y_pred  (cpu_losses.cpp:50-57)
+struct CceDeltaF {
+    static constexpr bool reads_c = false;
+    __device__ float operator()(float y, float p, float) const { return __fmul_rn(-y, __fdiv_rn(1.0f, __fadd_rn(p, 10e-8f))); }
+};
+
+// Copy the interior: one thread per element of the SMALL tensor a[n*c,h,w].
+template <bool BACK>
+__global__ void __launch_bounds__(kBlock) pad_kernel(float *a, float *b, size_t total, int h, int w, int top, int left, int bh, int bw) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int x = (int)(i % w);
+        size_t t = i / w;
+        int y = (int)(t % h);
+        size_t plane = t / h;
+        size_t j = (plane * bh + (y + top)) * bw + (x + left);
+        if (BACK) a[i] = __fadd_rn(a[i], b[j]); else b[j] = a[i];
+    }
+}
+
+}  // namespace
+
+using namespace eb;
+
+extern "C" {
+
+int eddlb200_fill(int dev, float *a, size_t n, float v) {
+    EB_CTX(dev);
+    return launch1(cx, st, a, a, n, FillF{v}, "gpu_fill_");
+}
+int eddlb200_scale(int dev, const float *a, float *b, float v, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, ScaleF{v}, "gpu_mult"); }
+int eddlb200_addc(int dev, const float *a, float *b, float v, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, AddcF{v}, "gpu_add"); }
+int eddlb200_sqr(int dev, const float *a, float *b, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, SqrF{}, "gpu_sqr"); }
+int eddlb200_sqrt(int dev, const float *a, float *b, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, SqrtF{}, "gpu_sqrt"); }
+int eddlb200_clamp(int dev, const float *a, float *b, float lo, float hi, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, ClampF{lo, hi}, "gpu_clamp"); }
+int eddlb200_relu_fwd(int dev, const float *a, float *b, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, ReluF{}, "gpu_relu"); }
+
+int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b, float *c, int inc_c, size_t n) {
+    EB_CTX(dev);
+    if (inc_c) return launch3(cx, st, a, b, c, n, AxpbyF<true>{sca, scb}, "gpu_add");
+    return launch3(cx, st, a, b, c, n, AxpbyF<false>{sca, scb}, "gpu_add");
+}
+int eddlb200_inc(int dev, const float *a, float *b, size_t n) {
+    // gpu_inc: B += A  ==  gpu_add(1, A, 1, B, B, 0) in the reference (tensor_math.cpp Tensor::inc)
+    EB_CTX(dev);
+    return launch3(cx, st, a, b, b, n, AxpbyF<false>{1.f, 1.f}, "gpu_inc");
+}
+int eddlb200_el_div(int dev, const float *a, const float *b, float *c, int inc_c, size_t n) {
+    EB_CTX(dev);
+    if (inc_c) return launch3(cx, st, a, b, c, n, DivF<true>{}, "gpu_el_div");
+    return launch3(cx, st, a, b, c, n, DivF<false>{}, "gpu_el_div");
+}
+int eddlb200_el_mult(int dev, const float *a, const float *b, float *c, int inc_c, size_t n) {
+    EB_CTX(dev);
+    if (inc_c) return launch3(cx, st, a, b, c, n, MulF<true>{}, "gpu_el_mult");
+    return launch3(cx, st, a, b, c, n, MulF<false>{}, "gpu_el_mult");
+}
+int eddlb200_relu_bwd(int dev, const float *d, const float *i, float *pd, size_t n) {
+    EB_CTX(dev);
+    return launch3(cx, st, d, i, pd, n, ReluBwdF{}, "gpu_d_relu");
+}
+int eddlb200_cce_delta(int dev, const float *y_true, const float *y_pred, float *delta, size_t n) {
+    EB_CTX(dev);
+    return launch3(cx, st, y_true, y_pred, delta, n, CceDeltaF{}, "gpu_d_categorical_cross_entropy");
+}
+
+int eddlb200_pad(int dev, const float *a, float *b, int n, int c, int h, int w, int top, int bottom, int left, int right) {
+    EB_CTX(dev);
+    EB_REQUIRE(a && b && n >= 0 && c >= 0 && h >= 0 && w >= 0 && top >= 0 && bottom >= 0 && left >= 0 && right >= 0, "gpu_pad");
+    size_t total = (size_t)n * c * h * w;
+    if (!total) return 0;
+    pad_kernel<false><<<grid_for(total, kBlock), kBlock, 0, st>>>(const_cast<float *>(a), b, total, h, w, top, left, h + top + bottom, w + left + right);
+    EB_LAUNCH_CHECK("gpu_pad");
+    return 0;
+}
+int eddlb200_pad_bwd(int dev, float *a_delta, const float *b_delta, int n, int c, int h, int w, int top, int bottom, int left, int right) {
+    EB_CTX(dev);
+    EB_REQUIRE(a_delta && b_delta && n >= 0 && c >= 0 && h >= 0 && w >= 0 && top >= 0 && bottom >= 0 && left >= 0 && right >= 0, "gpu_pad_back");
+    size_t total = (size_t)n * c * h * w;
+    if (!total) return 0;
+    pad_kernel<true><<<grid_for(total, kBlock), kBlock, 0, st>>>(a_delta, const_cast<float *>(b_delta), total, h, w, top, left, h + top + bottom, w + left + right);
+    EB_LAUNCH_CHECK("gpu_pad_back");
+    return 0;
+}
+
+}  // extern "C"

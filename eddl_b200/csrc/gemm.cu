@@ -1,0 +1,136 @@
+// Dense-layer algebra: C = op(A)*op(B) (+C), row bias add, column/row sums.
+// Replaces gpu_mult2D (cublasSgemm, EDDL src/hardware/gpu/gpu_math.cu:457-490),
+// gpu_sum2D_rowwise (gpu_math.cu:517-528) and gpu_reduce_sum2D (gpu_reduction.cu:232-244,
+// one atomicAdd per element); arithmetic as cpu_mult2D / cpu_sum2D_rowwise /
+// cpu_reduce_sum2D (src/hardware/cpu/cpu_math.cpp:302-325,369-380; cpu_reduction.cpp:91-112).
+// The dense layers of the convnets are small (<= 64x2048x1000), so this is an fp32
+// FMA kernel: 64x64 block tile, 16-deep k slices staged in shared memory, 4x4
+// accumulators per thread, exact fp32 accumulation.
+#include "common.cuh"
+
+namespace {
+
+using namespace eb;
+
+constexpr int BM = 64, BN = 64, BK = 16, TB = 256;
+
+// Row-major storage.  A: ta ? [k,m] : [m,k]; B: tb ? [n,k] : [k,n]; C: [m,n].
+__global__ void __launch_bounds__(TB) sgemm_kernel(const float *__restrict__ A, int ta, const float *__restrict__ B, int tb,
+                                                   float *__restrict__ C, int inc_c, int m, int n, int k) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Bs[BK][BN + 4];
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < k; k0 += BK) {
+        for (int e = threadIdx.x; e < BM * BK; e += TB) {
+            // choose the traversal that is contiguous in memory
+            int mi, ki;
+            if (ta) { mi = e % BM; ki = e / BM; } else { ki = e % BK; mi = e / BK; }
+            const int gm = m0 + mi, gk = k0 + ki;
+            float v = 0.f;
+            if (gm < m && gk < k) v = ta ? A[(size_t)gk * m + gm] : A[(size_t)gm * k + gk];
+            As[ki][mi] = v;
+        }
+        for (int e = threadIdx.x; e < BN * BK; e += TB) {
+            int ni, ki;
+            if (tb) { ki = e % BK; ni = e / BK; } else { ni = e % BN; ki = e / BN; }
+            const int gn = n0 + ni, gk = k0 + ki;
+            float v = 0.f;
+            if (gn < n && gk < k) v = tb ? B[(size_t)gn * k + gk] : B[(size_t)gk * n + gn];
+            Bs[ki][ni] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int gm = m0 + ty * 4 + i;
+        if (gm >= m) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= n) continue;
+            float *c = C + (size_t)gm * n + gn;
+            *c = inc_c ? __fadd_rn(*c, acc[i][j]) : acc[i][j];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) rowbias_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ c, size_t total, int cols) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += stride) c[p] = __fadd_rn(a[p], __ldg(b + (p % cols)));
+}
+
+// axis 0: one thread per column walks the rows in order (the reference's order), coalesced
+// across columns.  axis 1: one warp per row.
+__global__ void __launch_bounds__(256) colsum_kernel(const float *__restrict__ a, float *__restrict__ b, int rows, int cols, int inc_b) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= cols) return;
+    float s = inc_b ? b[j] : 0.f;
+    for (int i = 0; i < rows; i++) s = __fadd_rn(s, a[(size_t)i * cols + j]);
+    b[j] = s;
+}
+__global__ void __launch_bounds__(256) rowsum_kernel(const float *__restrict__ a, float *__restrict__ b, int rows, int cols, int inc_b) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    float s = 0.f;
+    for (int j = lane; j < cols; j += 32) s += a[(size_t)r * cols + j];
+    s = warp_sum(s);
+    if (lane == 0) b[r] = inc_b ? __fadd_rn(b[r], s) : s;
+}
+
+}  // namespace
+
+using namespace eb;
+
+extern "C" {
+
+int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, float *c, int inc_c, int m, int n, int k) {
+    EB_CTX(dev);
+    EB_REQUIRE(a && b && c && m >= 0 && n >= 0 && k >= 0, "gpu_mult2D");
+    if (m == 0 || n == 0) return 0;
+    dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+    sgemm_kernel<<<grid, TB, 0, st>>>(a, ta, b, tb, c, inc_c, m, n, k);
+    EB_LAUNCH_CHECK("gpu_mult2D");
+    return 0;
+}
+
+int eddlb200_sum2d_rowwise(int dev, const float *a, const float *b, float *c, int rows, int cols) {
+    EB_CTX(dev);
+    EB_REQUIRE(a && b && c && rows >= 0 && cols >= 0, "gpu_sum2D_rowwise");
+    const size_t total = (size_t)rows * cols;
+    if (!total) return 0;
+    rowbias_kernel<<<grid_for(total, 256), 256, 0, st>>>(a, b, c, total, cols);
+    EB_LAUNCH_CHECK("gpu_sum2D_rowwise");
+    return 0;
+}
+
+int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols, int axis, int inc_b) {
+    EB_CTX(dev);
+    EB_REQUIRE(a && b && rows >= 0 && cols >= 0 && (axis == 0 || axis == 1), "gpu_reduce_sum2D");
+    if (axis == 0) {
+        if (!cols) return 0;
+        colsum_kernel<<<(cols + 255) / 256, 256, 0, st>>>(a, b, rows, cols, inc_b);
+    } else {
+        if (!rows) return 0;
+        rowsum_kernel<<<(rows + 7) / 8, 256, 0, st>>>(a, b, rows, cols, inc_b);
+    }
+    EB_LAUNCH_CHECK("gpu_reduce_sum2D");
+    return 0;
+}
+
+}  // extern "C"

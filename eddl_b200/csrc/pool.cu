@@ -1,0 +1,180 @@
+// MaxPool2D / AvgPool2D forward and backward, NCHW fp32.
+// Replaces maxpool2d / maxpool2d_back / avgpool2d / avgpool2d_back
+// (EDDL src/hardware/gpu/nn/gpu_pool_kernels.cu:43-169,353-482); semantics follow
+// cpu_mpool2D / cpu_mpool2D_back / cpu_avgpool2D / cpu_avgpool2D_back
+// (src/hardware/cpu/nn/cpu_pool.cpp:74-145,226-304):
+//   * window scan is rows-outer / cols-inner with a strict '>' from -3.40282e38, out of
+//     bounds positions count as that lowest value, so ties keep the first position;
+//   * ind_x / ind_y hold the absolute input column / row of the maximum AS FLOATS;
+//   * average divides by the full window kr*kc, padded positions included.
+// Forward: one thread per output element, consecutive threads on consecutive output
+// columns (coalesced stores of y and both index planes).  Backward is written in
+// gather form -- one thread per INPUT element that visits the (at most
+// ceil(kr/sr)*ceil(kc/sc)) windows covering it in increasing output order -- so there
+// are no float atomics and the sum order equals the reference's sequential order.
+#include "common.cuh"
+
+namespace {
+
+using namespace eb;
+constexpr int kBlock = 256;
+
+struct PoolGeom { int ih, iw, oh, ow, kr, kc, sr, sc, pt, pl; };
+
+__global__ void __launch_bounds__(kBlock) maxpool_fwd_kernel(const float *__restrict__ in, float *__restrict__ out,
+                                                             float *__restrict__ ind_x, float *__restrict__ ind_y,
+                                                             size_t total, PoolGeom g) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += stride) {
+        const int oj = (int)(p % g.ow);
+        const size_t t = p / g.ow;
+        const int oi = (int)(t % g.oh);
+        const size_t plane = t / g.oh;
+        const float *src = in + plane * (size_t)g.ih * g.iw;
+        const int i0 = oi * g.sr - g.pt, j0 = oj * g.sc - g.pl;
+        float m = -3.40282e+38f;
+        // A window in which nothing exceeds the lowest value (all NaN / -inf) reports
+        // position (0, 0); the reference leaves the previous content there.
+        float bx = 0.f, by = 0.f;
+        for (int ki = 0; ki < g.kr; ki++) {
+            const int y = i0 + ki;
+            for (int kj = 0; kj < g.kc; kj++) {
+                const int x = j0 + kj;
+                float v = -3.40282e+38f;
+                if (y >= 0 && y < g.ih && x >= 0 && x < g.iw) v = __ldg(src + (size_t)y * g.iw + x);
+                if (v > m) { m = v; bx = (float)x; by = (float)y; }
+            }
+        }
+        out[p] = m; ind_x[p] = bx; ind_y[p] = by;
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) avgpool_fwd_kernel(const float *__restrict__ in, float *__restrict__ out, size_t total, PoolGeom g) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const float ksize = (float)(g.kr * g.kc);
+    for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += stride) {
+        const int oj = (int)(p % g.ow);
+        const size_t t = p / g.ow;
+        const int oi = (int)(t % g.oh);
+        const size_t plane = t / g.oh;
+        const float *src = in + plane * (size_t)g.ih * g.iw;
+        const int i0 = oi * g.sr - g.pt, j0 = oj * g.sc - g.pl;
+        float s = 0.f;
+        for (int ki = 0; ki < g.kr; ki++) {
+            const int y = i0 + ki;
+            if (y < 0 || y >= g.ih) continue;
+            for (int kj = 0; kj < g.kc; kj++) {
+                const int x = j0 + kj;
+                if (x >= 0 && x < g.iw) s = __fadd_rn(s, __ldg(src + (size_t)y * g.iw + x));
+            }
+        }
+        out[p] = __fdiv_rn(s, ksize);
+    }
+}
+
+// First / last output index whose window [o*s - pad, o*s - pad + k) contains position v.
+__device__ __forceinline__ void covering(int v, int k, int s, int pad, int on, int &lo, int &hi) {
+    const int a = v + pad;                 // o*s <= a  and  o*s > a - k
+    hi = a / s;
+    if (hi > on - 1) hi = on - 1;
+    int num = a - k + 1;                   // o*s >= num
+    lo = num <= 0 ? 0 : (num + s - 1) / s;
+}
+
+template <bool MAX>
+__global__ void __launch_bounds__(kBlock) pool_bwd_kernel(const float *__restrict__ d, const float *__restrict__ ind_x,
+                                                          const float *__restrict__ ind_y, float *__restrict__ id,
+                                                          size_t total_in, PoolGeom g) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const float ksize = (float)(g.kr * g.kc);
+    for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < total_in; q += stride) {
+        const int x = (int)(q % g.iw);
+        const size_t t = q / g.iw;
+        const int y = (int)(t % g.ih);
+        const size_t plane = t / g.ih;
+        int oi0, oi1, oj0, oj1;
+        covering(y, g.kr, g.sr, g.pt, g.oh, oi0, oi1);
+        covering(x, g.kc, g.sc, g.pl, g.ow, oj0, oj1);
+        float acc = id[q];
+        bool touched = false;
+        const size_t obase = plane * (size_t)g.oh * g.ow;
+        for (int oi = oi0; oi <= oi1; oi++)
+            for (int oj = oj0; oj <= oj1; oj++) {
+                const size_t p = obase + (size_t)oi * g.ow + oj;
+                if (MAX) {
+                    // int x = D->indX->ptr[p]  (float -> int conversion in the reference)
+                    if ((int)__ldg(ind_x + p) == x && (int)__ldg(ind_y + p) == y) { acc = __fadd_rn(acc, __ldg(d + p)); touched = true; }
+                } else {
+                    acc = __fadd_rn(acc, __fdiv_rn(__ldg(d + p), ksize));
+                    touched = true;
+                }
+            }
+        if (touched) id[q] = acc;
+    }
+}
+
+int check_geom(const char *what, int n, int c, int ih, int iw, int oh, int ow, int kr, int kc, int sr, int sc, int pt, int pl) {
+    if (n < 0 || c < 0 || ih <= 0 || iw <= 0 || oh <= 0 || ow <= 0 || kr <= 0 || kc <= 0 || sr <= 0 || sc <= 0 || pt < 0 || pl < 0)
+        return set_error(EDDLB200_EINVAL, "%s: bad geometry", what);
+    return 0;
+}
+
+}  // namespace
+
+using namespace eb;
+
+extern "C" {
+
+int eddlb200_maxpool2d_fwd(int dev, const float *in, float *out, float *ind_x, float *ind_y, int n, int c, int ih, int iw, int oh, int ow,
+                           int kr, int kc, int sr, int sc, int pad_top, int pad_left) {
+    EB_CTX(dev);
+    if (int r = check_geom("gpu_mpool2D", n, c, ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left)) return r;
+    EB_REQUIRE(in && out && ind_x && ind_y, "gpu_mpool2D");
+    const size_t total = (size_t)n * c * oh * ow;
+    if (!total) return 0;
+    PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    maxpool_fwd_kernel<<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, ind_x, ind_y, total, g);
+    EB_LAUNCH_CHECK("gpu_mpool2D");
+    return 0;
+}
+
+int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const float *ind_y, float *id, int n, int c, int ih, int iw, int oh, int ow,
+                           int kr, int kc, int sr, int sc, int pad_top, int pad_left) {
+    EB_CTX(dev);
+    if (int r = check_geom("gpu_mpool2D_back", n, c, ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left)) return r;
+    EB_REQUIRE(d && ind_x && ind_y && id, "gpu_mpool2D_back");
+    const size_t total = (size_t)n * c * ih * iw;
+    if (!total) return 0;
+    PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    pool_bwd_kernel<true><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g);
+    EB_LAUNCH_CHECK("gpu_mpool2D_back");
+    return 0;
+}
+
+int eddlb200_avgpool2d_fwd(int dev, const float *in, float *out, int n, int c, int ih, int iw, int oh, int ow,
+                           int kr, int kc, int sr, int sc, int pad_top, int pad_left) {
+    EB_CTX(dev);
+    if (int r = check_geom("gpu_avgpool2D", n, c, ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left)) return r;
+    EB_REQUIRE(in && out, "gpu_avgpool2D");
+    const size_t total = (size_t)n * c * oh * ow;
+    if (!total) return 0;
+    PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    avgpool_fwd_kernel<<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, total, g);
+    EB_LAUNCH_CHECK("gpu_avgpool2D");
+    return 0;
+}
+
+int eddlb200_avgpool2d_bwd(int dev, const float *d, float *id, int n, int c, int ih, int iw, int oh, int ow,
+                           int kr, int kc, int sr, int sc, int pad_top, int pad_left) {
+    EB_CTX(dev);
+    if (int r = check_geom("gpu_avgpool2D_back", n, c, ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left)) return r;
+    EB_REQUIRE(d && id, "gpu_avgpool2D_back");
+    const size_t total = (size_t)n * c * ih * iw;
+    if (!total) return 0;
+    PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    pool_bwd_kernel<false><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g);
+    EB_LAUNCH_CHECK("gpu_avgpool2D_back");
+    return 0;
+}
+
+}  // extern "C"

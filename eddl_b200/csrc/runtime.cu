@@ -1,0 +1,248 @@
+// Device contexts, caching allocator, copies, timers.
+// Replaces gpu_init / gpu_create_tensor / gpu_delete_tensor / gpu_copy_*
+// (EDDL src/hardware/gpu/gpu_tensor.cu:133-233, gpu_core.cu:49-78): one context per
+// device holding one compute stream, a size-bucketed free-list allocator (the
+// reference does a cudaMalloc/cudaFree per tensor and its Net frees and re-creates
+// every tensor on a batch-size change), a growable scratch arena and pinned words
+// for scalar read-back.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+#include "common.cuh"
+
+namespace eb {
+
+struct DevCtx {
+    int dev = -1;
+    bool ready = false;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;
+    std::multimap<size_t, void *> free_blocks;          // rounded size -> block
+    std::unordered_map<void *, size_t> live;            // block -> rounded size
+    size_t bytes_in_use = 0, bytes_cached = 0;
+    void *scratch_ptr = nullptr; size_t scratch_bytes = 0;
+    float *h_scalars = nullptr, *d_scalars = nullptr;
+    cudaEvent_t ev_start[16] = {}, ev_stop[16] = {};
+    unsigned long long launches = 0;
+    ncclComm *comm = nullptr; int nranks = 1, rank = 0;
+};
+
+static DevCtx g_ctx[EDDLB200_MAX_DEVICES];
+static std::mutex g_init_mu;
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char *fmt, ...) {
+    va_list ap; va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_status(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return 0;
+    set_error((int)e, "[CUDA ERROR]: %s (%d) raised in %s", cudaGetErrorString(e), (int)e, what);
+    return (int)e;
+}
+
+static int init_locked(int dev) {
+    DevCtx &c = g_ctx[dev];
+    if (c.ready) return 0;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) return cuda_status(e, "cudaGetDeviceCount");
+    if (dev >= n) return set_error(EDDLB200_ENOINIT, "device %d requested but only %d visible", dev, n);
+    if ((e = cudaSetDevice(dev)) != cudaSuccess) return cuda_status(e, "cudaSetDevice");
+    if ((e = cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking)) != cudaSuccess) return cuda_status(e, "cudaStreamCreate");
+    if ((e = cudaMallocHost((void **)&c.h_scalars, 64 * sizeof(float))) != cudaSuccess) return cuda_status(e, "cudaMallocHost");
+    if ((e = cudaMalloc((void **)&c.d_scalars, 64 * sizeof(float))) != cudaSuccess) return cuda_status(e, "cudaMalloc");
+    for (int i = 0; i < 16; i++) { cudaEventCreate(&c.ev_start[i]); cudaEventCreate(&c.ev_stop[i]); }
+    c.dev = dev;
+    c.ready = true;
+    return 0;
+}
+
+DevCtx *ctx(int dev) {
+    if (dev < 0 || dev >= EDDLB200_MAX_DEVICES) { set_error(EDDLB200_ENOINIT, "device ordinal %d out of range", dev); return nullptr; }
+    DevCtx &c = g_ctx[dev];
+    if (!c.ready) {
+        std::lock_guard<std::mutex> lk(g_init_mu);
+        if (init_locked(dev) != 0) return nullptr;
+    }
+    if (cudaSetDevice(dev) != cudaSuccess) { set_error(EDDLB200_ENOINIT, "cudaSetDevice(%d) failed", dev); return nullptr; }
+    return &c;
+}
+
+cudaStream_t stream_of(DevCtx *c) { return c->stream; }
+float *host_scalars(DevCtx *c) { return c->h_scalars; }
+float *dev_scalars(DevCtx *c) { return c->d_scalars; }
+ncclComm *comm_of(DevCtx *c) { return c->comm; }
+int comm_nranks(DevCtx *c) { return c->nranks; }
+void count_launch(DevCtx *c, unsigned n) { c->launches += n; }
+
+void set_comm(DevCtx *c, ncclComm *comm, int nranks, int rank) { c->comm = comm; c->nranks = nranks; c->rank = rank; }
+int comm_rank(DevCtx *c) { return c->rank; }
+
+void *scratch(DevCtx *c, size_t bytes) {
+    if (bytes <= c->scratch_bytes) return c->scratch_ptr;
+    // Work already enqueued may still read the old arena: drain before replacing it.
+    cudaStreamSynchronize(c->stream);
+    if (c->scratch_ptr) cudaFree(c->scratch_ptr);
+    size_t want = bytes < (size_t(8) << 20) ? (size_t(8) << 20) : bytes + bytes / 2;
+    c->scratch_ptr = nullptr; c->scratch_bytes = 0;
+    if (cudaMalloc(&c->scratch_ptr, want) != cudaSuccess) { set_error(cudaErrorMemoryAllocation, "scratch arena of %zu bytes", want); return nullptr; }
+    c->scratch_bytes = want;
+    return c->scratch_ptr;
+}
+
+static size_t round_size(size_t b) {
+    if (b < 512) return 512;
+    if (b < (size_t(1) << 20)) return (b + 511) & ~size_t(511);
+    return (b + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+}
+
+}  // namespace eb
+
+using namespace eb;
+
+extern "C" {
+
+const char *eddlb200_last_error(void) { return g_err; }
+int eddlb200_version(void) { return 100; }
+
+int eddlb200_device_count(int *n) {
+    if (!n) return set_error(EDDLB200_EINVAL, "device_count: null");
+    cudaError_t e = cudaGetDeviceCount(n);
+    if (e != cudaSuccess) { *n = 0; return cuda_status(e, "cudaGetDeviceCount"); }
+    return 0;
+}
+
+int eddlb200_init(int dev) { return ctx(dev) ? 0 : EDDLB200_ENOINIT; }
+
+int eddlb200_alloc(int dev, size_t bytes, void **out) {
+    EB_CTX(dev);
+    if (!out) return set_error(EDDLB200_EINVAL, "alloc: null out");
+    size_t r = round_size(bytes);
+    std::lock_guard<std::mutex> lk(cx->mu);
+    auto it = cx->free_blocks.lower_bound(r);
+    // Reuse a cached block when it wastes at most 25% (exact match for small ones).
+    if (it != cx->free_blocks.end() && it->first <= r + r / 4) {
+        *out = it->second; size_t sz = it->first;
+        cx->free_blocks.erase(it);
+        cx->live[*out] = sz; cx->bytes_cached -= sz; cx->bytes_in_use += sz;
+        return 0;
+    }
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, r);
+    if (e != cudaSuccess) {
+        // Give cached blocks back to the driver and retry once.
+        cudaGetLastError();
+        cudaStreamSynchronize(cx->stream);
+        for (auto &kv : cx->free_blocks) cudaFree(kv.second);
+        cx->free_blocks.clear(); cx->bytes_cached = 0;
+        e = cudaMalloc(&p, r);
+        if (e != cudaSuccess) return cuda_status(e, "gpu_create_tensor");
+    }
+    cx->live[p] = r; cx->bytes_in_use += r;
+    *out = p;
+    return 0;
+}
+
+int eddlb200_free(int dev, void *p) {
+    EB_CTX(dev);
+    if (!p) return 0;
+    std::lock_guard<std::mutex> lk(cx->mu);
+    auto it = cx->live.find(p);
+    if (it == cx->live.end()) return set_error(EDDLB200_EINVAL, "free: pointer %p was not allocated by this library on device %d", p, dev);
+    size_t sz = it->second;
+    cx->live.erase(it);
+    cx->bytes_in_use -= sz;
+    // All work of this library runs on one stream per device, so a block handed out
+    // again is only touched by work ordered after everything that used it before.
+    cx->free_blocks.emplace(sz, p); cx->bytes_cached += sz;
+    return 0;
+}
+
+int eddlb200_mem_info(int dev, size_t *in_use, size_t *cached) {
+    EB_CTX(dev);
+    std::lock_guard<std::mutex> lk(cx->mu);
+    if (in_use) *in_use = cx->bytes_in_use;
+    if (cached) *cached = cx->bytes_cached;
+    return 0;
+}
+
+int eddlb200_memcpy_h2d(int dev, void *dst, const void *src, size_t bytes) {
+    EB_CTX(dev);
+    if (bytes == 0) return 0;
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    return cuda_status(e, "gpu_copy_to_gpu");
+}
+
+int eddlb200_memcpy_h2d_async(int dev, void *dst, const void *src, size_t bytes) {
+    EB_CTX(dev);
+    if (bytes == 0) return 0;
+    return cuda_status(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st), "memcpy_h2d_async");
+}
+
+int eddlb200_memcpy_d2h(int dev, void *dst, const void *src, size_t bytes) {
+    EB_CTX(dev);
+    if (bytes == 0) return 0;
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    return cuda_status(e, "gpu_copy_from_gpu");
+}
+
+int eddlb200_memcpy_d2d(int dev, void *dst, const void *src, size_t bytes) {
+    EB_CTX(dev);
+    if (bytes == 0) return 0;
+    return cuda_status(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st), "gpu_copy_gpu");
+}
+
+int eddlb200_host_alloc(size_t bytes, void **out) {
+    if (!out) return set_error(EDDLB200_EINVAL, "host_alloc: null out");
+    return cuda_status(cudaMallocHost(out, bytes ? bytes : 1), "cudaMallocHost");
+}
+int eddlb200_host_free(void *p) { return p ? cuda_status(cudaFreeHost(p), "cudaFreeHost") : 0; }
+
+int eddlb200_stream(int dev, void **s) {
+    EB_CTX(dev);
+    if (!s) return set_error(EDDLB200_EINVAL, "stream: null out");
+    *s = (void *)st;
+    return 0;
+}
+
+int eddlb200_sync(int dev) {
+    EB_CTX(dev);
+    return cuda_status(cudaStreamSynchronize(st), "eddlb200_sync");
+}
+
+int eddlb200_timer_start(int dev, int slot) {
+    EB_CTX(dev);
+    if (slot < 0 || slot >= 16) return set_error(EDDLB200_EINVAL, "timer slot %d", slot);
+    return cuda_status(cudaEventRecord(cx->ev_start[slot], st), "timer_start");
+}
+int eddlb200_timer_stop(int dev, int slot) {
+    EB_CTX(dev);
+    if (slot < 0 || slot >= 16) return set_error(EDDLB200_EINVAL, "timer slot %d", slot);
+    return cuda_status(cudaEventRecord(cx->ev_stop[slot], st), "timer_stop");
+}
+int eddlb200_timer_elapsed_ms(int dev, int slot, float *ms) {
+    EB_CTX(dev);
+    if (slot < 0 || slot >= 16 || !ms) return set_error(EDDLB200_EINVAL, "timer slot %d", slot);
+    cudaError_t e = cudaEventSynchronize(cx->ev_stop[slot]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(ms, cx->ev_start[slot], cx->ev_stop[slot]);
+    return cuda_status(e, "timer_elapsed");
+}
+
+int eddlb200_launch_count(int dev, unsigned long long *n) {
+    EB_CTX(dev);
+    if (!n) return set_error(EDDLB200_EINVAL, "launch_count: null");
+    *n = cx->launches;
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,195 @@
+/*
+ * eddl_b200 -- C ABI of the B200 (sm_100a) backend for EDDL's convnet training step.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, and returns an
+ * int status: 0 = ok, >0 = a cudaError_t, <0 = one of the EDDLB200_E* codes below
+ * (eddlb200_last_error() gives the text).  `dev` is a CUDA device ordinal; every call
+ * makes that device current and enqueues its work on that device's single compute
+ * stream (eddlb200_stream).  Calls are stream-ordered and asynchronous unless the
+ * comment says "blocking".  Device pointers are float* (fp32) in NCHW / row-major
+ * layout, exactly what EDDL's Tensor::ptr holds.  There is no CPU fallback: a call
+ * made without a usable GPU fails with a CUDA error.
+ *
+ * Each declaration cites the EDDL v1.1 function it replaces (path inside the EDDL
+ * source tree : line) -- the `gpu_*` function the reference's Tensor / tensorNN
+ * dispatch calls, and the `cpu_*` twin that defines the arithmetic.
+ */
+#ifndef EDDL_B200_H
+#define EDDL_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EDDLB200_EINVAL   (-1)  /* bad argument (null pointer, negative size, unsupported shape) */
+#define EDDLB200_ENOINIT  (-2)  /* device context not initialised / device ordinal out of range */
+#define EDDLB200_ENCCL    (-3)  /* NCCL reported an error */
+#define EDDLB200_ETIMEOUT (-4)  /* a bounded device-side wait gave up */
+#define EDDLB200_ELIMIT   (-5)  /* size beyond a documented maximum */
+
+const char *eddlb200_last_error(void);
+int eddlb200_version(void);
+
+/* ---- lifecycle, memory, copies ------------------------------------------------
+ * gpu_devices / gpu_init / gpu_create_tensor / gpu_delete_tensor
+ *   (src/hardware/gpu/gpu_tensor.cu:133-233);  gpu_copy_to_gpu / gpu_copy_from_gpu /
+ *   gpu_copy_gpu (src/hardware/gpu/gpu_core.cu:49-78). */
+int eddlb200_device_count(int *n);
+int eddlb200_init(int dev);                                  /* idempotent, thread-safe */
+int eddlb200_alloc(int dev, size_t bytes, void **out);       /* caching allocator, 256-byte aligned */
+int eddlb200_free(int dev, void *p);
+int eddlb200_memcpy_h2d(int dev, void *dst, const void *src, size_t bytes);  /* blocking */
+int eddlb200_memcpy_d2h(int dev, void *dst, const void *src, size_t bytes);  /* blocking */
+int eddlb200_memcpy_d2d(int dev, void *dst, const void *src, size_t bytes);
+/* Pinned-host staged copies for a caller that overlaps transfers itself
+ * (Net::train_batch does blocking copies: src/net/net_api.cpp:1269-1285). */
+int eddlb200_host_alloc(size_t bytes, void **out);
+int eddlb200_host_free(void *p);
+int eddlb200_memcpy_h2d_async(int dev, void *dst, const void *src, size_t bytes);
+int eddlb200_stream(int dev, void **cuda_stream);
+int eddlb200_sync(int dev);                                  /* blocking */
+int eddlb200_mem_info(int dev, size_t *in_use, size_t *cached);
+/* Device timers on the compute stream (CUDA events); slot in [0,16). */
+int eddlb200_timer_start(int dev, int slot);
+int eddlb200_timer_stop(int dev, int slot);
+int eddlb200_timer_elapsed_ms(int dev, int slot, float *ms);  /* blocking */
+/* Number of kernels this library has launched on `dev` since init. */
+int eddlb200_launch_count(int dev, unsigned long long *n);
+
+/* ---- elementwise (src/hardware/gpu/gpu_math.cu:108-116,148-156,275-284,390-410,
+ *      446-455,493-503; gpu_core.cu:139-147; cpu twins in src/hardware/cpu/cpu_math.cpp) */
+int eddlb200_fill(int dev, float *a, size_t n, float v);                      /* gpu_fill_ */
+/* gpu_add(scA,A,scB,B,C,incC): C = (incC ? C : 0) + scA*A + scB*B */
+int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b, float *c, int inc_c, size_t n);
+int eddlb200_inc(int dev, const float *a, float *b, size_t n);                /* gpu_inc: B += A */
+int eddlb200_scale(int dev, const float *a, float *b, float v, size_t n);     /* gpu_mult: B = A*v */
+int eddlb200_addc(int dev, const float *a, float *b, float v, size_t n);      /* gpu_add(A,B,v): B = A+v */
+int eddlb200_sqr(int dev, const float *a, float *b, size_t n);                /* gpu_sqr */
+int eddlb200_sqrt(int dev, const float *a, float *b, size_t n);               /* gpu_sqrt */
+int eddlb200_clamp(int dev, const float *a, float *b, float lo, float hi, size_t n);   /* gpu_clamp */
+int eddlb200_el_div(int dev, const float *a, const float *b, float *c, int inc_c, size_t n);  /* gpu_el_div */
+int eddlb200_el_mult(int dev, const float *a, const float *b, float *c, int inc_c, size_t n); /* gpu_el_mult */
+
+/* ---- activations (src/hardware/gpu/nn/gpu_activations.cu:25-45,294-385;
+ *      src/hardware/cpu/nn/cpu_activations.cpp:20-45,329-436) */
+int eddlb200_relu_fwd(int dev, const float *a, float *b, size_t n);
+/* pd += (i > 0) ? d : 0   (tests the layer INPUT i, accumulates) */
+int eddlb200_relu_bwd(int dev, const float *d, const float *i, float *pd, size_t n);
+/* Row softmax over the last axis of a [rows, cols] view; the denominator starts at
+ * 1.19209e-07 like the reference. */
+int eddlb200_softmax_fwd(int dev, const float *a, float *b, int rows, int cols);
+/* pd[r,i] += sum_j d[r,j] * (s[r,i]*[i==j] - s[r,j]*s[r,i]) ; s = softmax OUTPUT */
+int eddlb200_softmax_bwd(int dev, const float *d, const float *s, float *pd, int rows, int cols);
+/* Same over the middle axis of an [outer, cols, inner] view (gpu_full_softmax's `axis`). */
+int eddlb200_softmax_fwd_nd(int dev, const float *a, float *b, int outer, int cols, int inner);
+int eddlb200_softmax_bwd_nd(int dev, const float *d, const float *s, float *pd, int outer, int cols, int inner);
+
+/* ---- losses / metrics (src/hardware/gpu/nn/gpu_losses.cu:49-92, gpu_metrics.cu:26-49;
+ *      src/hardware/cpu/nn/cpu_losses.cpp:29-57, cpu_metrics.cpp:17-29) */
+/* value = -sum_rows sum_cols y*logf(p + 1e-7)   (a SUM over the batch). Blocking. */
+int eddlb200_cce_value(int dev, const float *y_true, const float *y_pred, int rows, int cols, float *host_out);
+int eddlb200_cce_delta(int dev, const float *y_true, const float *y_pred, float *delta, size_t n);
+/* rows whose argmax(y_true) == argmax(y_pred), first maximum wins. Blocking. */
+int eddlb200_accuracy(int dev, const float *y_true, const float *y_pred, int rows, int cols, int *host_out);
+
+/* ---- batch normalisation (src/hardware/gpu/nn/gpu_bn.cu:65-117;
+ *      src/hardware/cpu/nn/cpu_bn.cpp:118-249).  x is [b, z, rc].  Argument order and
+ *      meaning are those of gpu_batchnorm_forward / gpu_batchnorm_backward:
+ *      train: mean = sum/N, var = sumsq/N - mean^2, running stats updated when
+ *      momentum != 0, then `variance` receives sqrt(var + eps); opa = (x-mean)/variance;
+ *      y = opa*g + b.  `relu_out`, when not null, additionally receives max(y, 0)
+ *      (what a following ReLU layer would compute), so a BN+ReLU pair costs one pass. */
+int eddlb200_bn_fwd(int dev, int b, int z, int rc,
+                    const float *input, float *output, float *opa,
+                    float *global_mean, float *global_variance,
+                    const float *affine_g, const float *affine_b,
+                    float *mean, float *variance,
+                    int trmode, float epsilon, float momentum, float *relu_out);
+/* gbn_g += mean(delta*opa); gbn_b += mean(delta)  (means, not sums);
+ * delta *= bn_g in place; pdelta += (delta - (opa*m1 + m2)) / variance. */
+int eddlb200_bn_bwd(int dev, int b, int z, int rc,
+                    float *delta, const float *opa, float *pdelta,
+                    float *gbn_g, float *gbn_b, const float *bn_g,
+                    const float *variance, float *mean1, float *mean2);
+
+/* ---- pooling (src/hardware/gpu/nn/gpu_pool.cu:26-60,101-135;
+ *      src/hardware/cpu/nn/cpu_pool.cpp:74-145,226-304).  Input [n,c,ih,iw], output
+ *      [n,c,oh,ow]; ind_x/ind_y are float tensors shaped like the output that hold the
+ *      absolute input column/row of the maximum (first in row-major window order). */
+int eddlb200_maxpool2d_fwd(int dev, const float *in, float *out, float *ind_x, float *ind_y,
+                           int n, int c, int ih, int iw, int oh, int ow,
+                           int kr, int kc, int sr, int sc, int pad_top, int pad_left);
+int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const float *ind_y, float *id,
+                           int n, int c, int ih, int iw, int oh, int ow,
+                           int kr, int kc, int sr, int sc, int pad_top, int pad_left);
+int eddlb200_avgpool2d_fwd(int dev, const float *in, float *out,
+                           int n, int c, int ih, int iw, int oh, int ow,
+                           int kr, int kc, int sr, int sc, int pad_top, int pad_left);
+int eddlb200_avgpool2d_bwd(int dev, const float *d, float *id,
+                           int n, int c, int ih, int iw, int oh, int ow,
+                           int kr, int kc, int sr, int sc, int pad_top, int pad_left);
+
+/* ---- padding (src/hardware/gpu/gpu_da.cu:144-168; spec src/hardware/cpu/cpu_da.cpp:502-534)
+ *      a [n,c,h,w] -> b [n,c,h+top+bottom,w+left+right]; only the interior of b is written. */
+int eddlb200_pad(int dev, const float *a, float *b, int n, int c, int h, int w,
+                 int top, int bottom, int left, int right);
+int eddlb200_pad_bwd(int dev, float *a_delta, const float *b_delta, int n, int c, int h, int w,
+                     int top, int bottom, int left, int right);   /* a_delta += crop(b_delta) */
+
+/* ---- dense algebra (src/hardware/gpu/gpu_math.cu:457-528; gpu_reduction.cu:232-244;
+ *      src/hardware/cpu/cpu_math.cpp:302-325,369-401) */
+/* gpu_mult2D: C[m,n] = (inc_c ? C : 0) + op(A) * op(B), row-major; A is [m,k] (or [k,m]
+ * when ta), B is [k,n] (or [n,k] when tb). */
+int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, float *c, int inc_c,
+                    int m, int n, int k);
+int eddlb200_sum2d_rowwise(int dev, const float *a, const float *b, float *c, int rows, int cols); /* C = A + b[col] */
+/* gpu_reduce_sum2D: axis 0 -> B[cols] (+)= sum over rows; axis 1 -> B[rows] (+)= sum over cols */
+int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols, int axis, int inc_b);
+
+/* ---- Conv2D (src/hardware/gpu/nn/gpu_conv.cu:159-372;
+ *      src/hardware/cpu/nn/cpu_conv.cpp:114-280,316-527).  Cross-correlation, zero padding,
+ *      x [n,c,ih,iw], w [k,c,kr,kc], y [n,k,oh,ow].  precision: 0 = fp32-equivalent
+ *      (3xTF32 split on the tensor cores or fp32 FMA), 1 = plain TF32. */
+int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias /* may be null */, float *y,
+                        int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
+                        int sr, int sc, int pad_top, int pad_left, int precision);
+/* gw += sum_{n,p,q} dy * x ; gbias += sum dy when gbias != null  (accumulates) */
+int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *gw, float *gbias,
+                               int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
+                               int sr, int sc, int pad_top, int pad_left, int precision);
+/* dx += sum_{k,r,s} dy * w  (accumulates into the parent delta) */
+int eddlb200_conv2d_bwd_data(int dev, const float *dy, const float *w, float *dx,
+                             int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
+                             int sr, int sc, int pad_top, int pad_left, int precision);
+
+/* ---- optimizers (src/optimizers/optim_sgd.cpp:68-89; optim_adam.cpp:85-120) */
+/* m = lr*g + mu*m ; p = p - m   (no weight decay, no nesterov: the reference ignores both) */
+int eddlb200_sgd_momentum(int dev, float *p, const float *g, float *m, float lr, float mu, size_t n);
+/* Multi-tensor form: ntensors triples (p[i], g[i], m[i]) of sizes[i] floats, one launch. */
+int eddlb200_sgd_momentum_multi(int dev, float *const *p, const float *const *g, float *const *m,
+                                const size_t *sizes, int ntensors, float lr, float mu);
+/* m = b1*m + (1-b1)*g ; g = g*g (in place, like the reference) ; v = b2*v + (1-b2)*g ;
+ * p -= lr * (m/(1-b1^t)) / sqrt(v/(1-b2^t) + eps)      (eps inside the sqrt) */
+int eddlb200_adam(int dev, float *p, float *g, float *m, float *v,
+                  float lr, float beta1, float beta2, float eps, int t, size_t n);
+
+/* ---- cross-replica averaging (replaces Net::sync_weights, src/net/net_func.cpp:111-127:
+ *      acc = sum over replicas in fp32, acc *= 1.0f/N, every replica receives acc).
+ *      One process per GPU; the 128-byte id is made on rank 0 and given to every rank. */
+int eddlb200_comm_unique_id(void *id128);
+int eddlb200_comm_init_rank(int dev, int nranks, int rank, const void *id128);
+int eddlb200_comm_destroy(int dev);
+int eddlb200_comm_info(int dev, int *nranks, int *rank);
+int eddlb200_allreduce_avg(int dev, float *buf, size_t n);            /* in place */
+int eddlb200_allreduce_avg_multi(int dev, float *const *bufs, const size_t *sizes, int ntensors);
+int eddlb200_broadcast(int dev, float *buf, size_t n, int root);
+/* Gradient averaging fused with the SGD-momentum step of an equal-size parameter
+ * buffer: g <- allreduce(g)/N ; m = lr*g + mu*m ; p -= m. */
+int eddlb200_avg_grad_sgd(int dev, float *p, float *g, float *m, float lr, float mu, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

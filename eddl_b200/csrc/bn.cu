@@ -235,6 +235,7 @@ int eddlb200_bn_fwd(int dev, int b, int z, int rc, const float *input, float *ou
     EB_REQUIRE((size_t)b * rc < 0xfffffff0u, "gpu_batchnorm_forward");
     EB_REQUIRE(!affine_g || (affine_b && opa), "gpu_batchnorm_forward");
     EB_REQUIRE(!trmode || mean, "gpu_batchnorm_forward");
+    ProfScope prof(cx, PROF_BN_FWD, 16.0 * b * (double)z * rc);
     const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
     const bool vec = (rc % 4 == 0) && aligned16(input) && aligned16(output) && (!opa || aligned16(opa)) && (!relu_out || aligned16(relu_out));
     dim3 grid(z, S);
@@ -261,6 +262,7 @@ int eddlb200_bn_bwd(int dev, int b, int z, int rc, float *delta, const float *op
     EB_REQUIRE(b > 0 && z > 0 && rc > 0 && delta && opa && pdelta && variance && mean1 && mean2, "gpu_batchnorm_backward");
     EB_REQUIRE((size_t)b * rc < 0xfffffff0u, "gpu_batchnorm_backward");
     EB_REQUIRE(!bn_g || (gbn_g && gbn_b), "gpu_batchnorm_backward");
+    ProfScope prof(cx, PROF_BN_BWD, 24.0 * b * (double)z * rc);
     const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
     const bool vec = (rc % 4 == 0) && aligned16(delta) && aligned16(opa) && aligned16(pdelta);
     dim3 grid(z, S);

@@ -28,6 +28,19 @@ ncclComm *comm_of(DevCtx *c);
 int comm_nranks(DevCtx *c);
 void count_launch(DevCtx *c, unsigned n = 1);
 int set_error(int code, const char *fmt, ...);
+
+// Optional per-kernel-family device timing (CUDA events on the compute stream), off by
+// default.  `work` is the family's algorithmic work of this call (FLOPs or bytes).
+enum ProfKind { PROF_CONV_FWD = 0, PROF_CONV_BWD_DATA, PROF_CONV_BWD_WEIGHT, PROF_BN_FWD, PROF_BN_BWD,
+                PROF_ELEMENTWISE, PROF_POOL, PROF_GEMM, PROF_OPTIM, PROF_COMM, PROF_NKINDS };
+bool prof_enabled(DevCtx *c);
+void prof_begin(DevCtx *c, int kind, double work);
+void prof_end(DevCtx *c);
+struct ProfScope {
+    DevCtx *c; bool on;
+    ProfScope(DevCtx *cx, int kind, double work) : c(cx), on(prof_enabled(cx)) { if (on) prof_begin(c, kind, work); }
+    ~ProfScope() { if (on) prof_end(c); }
+};
 int cuda_status(cudaError_t e, const char *what);
 
 }  // namespace eb

@@ -71,6 +71,7 @@ int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bi
     if (int r = check("gpu_conv2D", g)) return r;
     EB_REQUIRE(x && w && y, "gpu_conv2D");
     if (n == 0) return 0;
+    ProfScope prof(cx, PROF_CONV_FWD, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
         int r = conv_tc_fwd(cx, st, g, x, w, bias, y, precision);
         if (r != 1) return r;
@@ -86,6 +87,7 @@ int eddlb200_conv2d_bwd_data(int dev, const float *dy, const float *w, float *dx
     if (int r = check("gpu_conv2D_back", g)) return r;
     EB_REQUIRE(dy && w && dx, "gpu_conv2D_back");
     if (n == 0) return 0;
+    ProfScope prof(cx, PROF_CONV_BWD_DATA, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
         int r = conv_tc_bwd_data(cx, st, g, dy, w, dx, precision);
         if (r != 1) return r;
@@ -101,6 +103,7 @@ int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *
     if (int r = check("gpu_conv2D_grad", g)) return r;
     EB_REQUIRE(x && dy && gw, "gpu_conv2D_grad");
     if (n == 0) return 0;
+    ProfScope prof(cx, PROF_CONV_BWD_WEIGHT, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (gbias) {
         bias_grad_kernel<<<k, 256, 0, st>>>(dy, gbias, n, k, oh * ow);
         EB_LAUNCH_CHECK("gpu_conv2D_grad(bias)");

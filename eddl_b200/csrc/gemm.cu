@@ -103,6 +103,7 @@ int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, flo
     EB_CTX(dev);
     EB_REQUIRE(a && b && c && m >= 0 && n >= 0 && k >= 0, "gpu_mult2D");
     if (m == 0 || n == 0) return 0;
+    ProfScope prof(cx, PROF_GEMM, 2.0 * m * (double)n * k);
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
     sgemm_kernel<<<grid, TB, 0, st>>>(a, ta, b, tb, c, inc_c, m, n, k);
     EB_LAUNCH_CHECK("gpu_mult2D");

@@ -121,6 +121,8 @@ int eddlb200_sgd_momentum_multi(int dev, float *const *p, const float *const *g,
         for (size_t c = 0; c < nch; c++) chunks.push_back(Chunk{(unsigned)(refs.size() - 1), (unsigned)c});
     }
     if (chunks.empty()) return 0;
+    double total = 0; for (auto &r : refs) total += (double)r.n;
+    ProfScope prof(cx, PROF_OPTIM, 20.0 * total);
     const size_t bytes_t = refs.size() * sizeof(TensorRef), bytes_c = chunks.size() * sizeof(Chunk);
     const size_t off_c = (bytes_t + 255) & ~size_t(255);
     // The table lives in the stream-ordered scratch arena; the copy below is ordered

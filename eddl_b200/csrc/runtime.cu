@@ -29,6 +29,11 @@ struct DevCtx {
     cudaEvent_t ev_start[16] = {}, ev_stop[16] = {};
     unsigned long long launches = 0;
     ncclComm *comm = nullptr; int nranks = 1, rank = 0;
+    // profiling: one (start, stop) event pair per profiled call, summed at read time
+    bool prof_on = false;
+    struct ProfRec { int kind; double work; cudaEvent_t a, b; };
+    std::vector<ProfRec> prof_recs;
+    std::vector<cudaEvent_t> prof_pool;
 };
 
 static DevCtx g_ctx[EDDLB200_MAX_DEVICES];
@@ -82,6 +87,18 @@ float *dev_scalars(DevCtx *c) { return c->d_scalars; }
 ncclComm *comm_of(DevCtx *c) { return c->comm; }
 int comm_nranks(DevCtx *c) { return c->nranks; }
 void count_launch(DevCtx *c, unsigned n) { c->launches += n; }
+
+bool prof_enabled(DevCtx *c) { return c->prof_on; }
+static cudaEvent_t prof_event(DevCtx *c) {
+    if (!c->prof_pool.empty()) { cudaEvent_t e = c->prof_pool.back(); c->prof_pool.pop_back(); return e; }
+    cudaEvent_t e; cudaEventCreate(&e); return e;
+}
+void prof_begin(DevCtx *c, int kind, double work) {
+    DevCtx::ProfRec r{kind, work, prof_event(c), prof_event(c)};
+    cudaEventRecord(r.a, c->stream);
+    c->prof_recs.push_back(r);
+}
+void prof_end(DevCtx *c) { if (!c->prof_recs.empty()) cudaEventRecord(c->prof_recs.back().b, c->stream); }
 
 void set_comm(DevCtx *c, ncclComm *comm, int nranks, int rank) { c->comm = comm; c->nranks = nranks; c->rank = rank; }
 int comm_rank(DevCtx *c) { return c->rank; }
@@ -236,6 +253,35 @@ int eddlb200_timer_elapsed_ms(int dev, int slot, float *ms) {
     cudaError_t e = cudaEventSynchronize(cx->ev_stop[slot]);
     if (e == cudaSuccess) e = cudaEventElapsedTime(ms, cx->ev_start[slot], cx->ev_stop[slot]);
     return cuda_status(e, "timer_elapsed");
+}
+
+int eddlb200_profile_enable(int dev, int on) {
+    EB_CTX(dev);
+    cx->prof_on = on != 0;
+    return 0;
+}
+
+int eddlb200_profile_read(int dev, int kind, unsigned long long *calls, double *total_ms, double *total_work) {
+    EB_CTX(dev);
+    if (kind < 0 || kind >= PROF_NKINDS) return set_error(EDDLB200_EINVAL, "profile_read: kind %d", kind);
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_status(e, "profile_read");
+    unsigned long long n = 0; double ms = 0, work = 0;
+    for (auto &r : cx->prof_recs) {
+        if (r.kind != kind) continue;
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, r.a, r.b) == cudaSuccess) { ms += t; work += r.work; n++; }
+    }
+    if (calls) *calls = n; if (total_ms) *total_ms = ms; if (total_work) *total_work = work;
+    return 0;
+}
+
+int eddlb200_profile_reset(int dev) {
+    EB_CTX(dev);
+    cudaStreamSynchronize(st);
+    for (auto &r : cx->prof_recs) { cx->prof_pool.push_back(r.a); cx->prof_pool.push_back(r.b); }
+    cx->prof_recs.clear();
+    return 0;
 }
 
 int eddlb200_launch_count(int dev, unsigned long long *n) {

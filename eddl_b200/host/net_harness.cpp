@@ -249,6 +249,9 @@ int ebh_train_resident(int id, int steps, float *loss_sum) {
         for (int s = 0; s < steps; s++) {
             rep->do_reset(); rep->do_reset_grads(); rep->do_forward(); rep->do_compute_loss();
             rep->do_delta(); rep->do_backward(); rep->do_applygrads();
+#ifdef cGPU
+            if (eddl_b200::get_world_size_distributed() > 1) eddl_b200::avg_weights_distributed(h->net, 1, 1);
+#endif
         }
         if (loss_sum) *loss_sum = rep->fiterr[0];
     });

@@ -55,6 +55,13 @@ int eddlb200_mem_info(int dev, size_t *in_use, size_t *cached);
 int eddlb200_timer_start(int dev, int slot);
 int eddlb200_timer_stop(int dev, int slot);
 int eddlb200_timer_elapsed_ms(int dev, int slot, float *ms);  /* blocking */
+/* Per-family device timing, off by default: when enabled every call of a family is bracketed by
+ * CUDA events on the compute stream.  kind: 0 conv fwd, 1 conv bwd-data, 2 conv bwd-weight, 3 BN fwd,
+ * 4 BN bwd, 5 elementwise, 6 pooling, 7 dense, 8 optimizer, 9 collectives.  total_work is the sum of
+ * the calls' algorithmic work (FLOPs for 0-2 and 7, bytes otherwise).  read is blocking. */
+int eddlb200_profile_enable(int dev, int on);
+int eddlb200_profile_read(int dev, int kind, unsigned long long *calls, double *total_ms, double *total_work);
+int eddlb200_profile_reset(int dev);
 /* Number of kernels this library has launched on `dev` since init. */
 int eddlb200_launch_count(int dev, unsigned long long *n);
 

@@ -1,0 +1,112 @@
+"""GPU parity tests of Conv2D forward / backward-data / backward-weight through the C ABI.
+Tolerance: max |got - want| <= 1e-5 * max |want| for the fp32-equivalent mode (precision 0; the requirement is rel 1e-5 of
+the reference's fp32 path) and 1e-3 for plain TF32 (precision 1).  `want` is the float64-accumulated restatement, the
+committed outputs of the reference's CPU code, its golden vectors, and that code run live where oracle/_ref is present."""
+import numpy as np
+import pytest
+
+from oracle import eddl_oracle as orc
+
+pytestmark = pytest.mark.gpu
+F = np.float32
+
+
+def relerr(got, want):
+    return float(np.max(np.abs(got.astype(np.float64) - want.astype(np.float64))) / max(float(np.max(np.abs(want))), 1e-30))
+
+
+def run_conv(lib, x, w, b, dy, gw0, gb0, dx0, stride, pads, precision=0):
+    n, c, ih, iw = x.shape; k, _, kr, kc = w.shape
+    oh, ow, pads = orc.resolve(pads, ih, iw, kr, kc, *stride)
+    geo = (n, c, ih, iw, k, kr, kc, oh, ow, stride[0], stride[1], pads[0], pads[2], precision)
+    dx_, dw_ = lib.to_device(x), lib.to_device(w)
+    y = lib.empty((n, k, oh, ow))
+    lib.call("conv2d_fwd", 0, dx_, dw_, None if b is None else lib.to_device(b), y, *geo)
+    out = dict(y=y.numpy())
+    if dy is not None:
+        ddy = lib.to_device(dy)
+        gw = lib.to_device(gw0 if gw0 is not None else np.zeros_like(w))
+        gb = None if b is None else lib.to_device(gb0 if gb0 is not None else np.zeros(k, F))
+        lib.call("conv2d_bwd_weight", 0, dx_, ddy, gw, gb, *geo)
+        dxx = lib.to_device(dx0 if dx0 is not None else np.zeros_like(x))
+        lib.call("conv2d_bwd_data", 0, ddy, dw_, dxx, *geo)
+        out.update(gw=gw.numpy(), gb=None if gb is None else gb.numpy(), dx=dxx.numpy())
+    return out
+
+
+SHAPES = [  # n, c, h, w, k, kr, kc, stride, pads(t,b,l,r), bias
+    (2, 3, 9, 8, 5, 3, 3, 1, (1, 1, 1, 1), True),
+    (3, 4, 11, 11, 6, 3, 3, 2, (1, 1, 1, 1), False),
+    (2, 8, 6, 6, 7, 1, 1, 1, (0, 0, 0, 0), False),
+    (2, 3, 14, 14, 4, 7, 7, 2, (3, 3, 3, 3), False),
+    (4, 1, 28, 28, 16, 3, 3, 1, (1, 1, 1, 1), True),       # small-CNN first layer
+    (2, 64, 8, 8, 64, 3, 3, 1, (1, 1, 1, 1), False),
+    (2, 128, 7, 7, 256, 1, 1, 1, (0, 0, 0, 0), False),
+    (2, 64, 16, 16, 128, 1, 1, 2, (0, 0, 0, 0), False),    # 1x1 stride-2 downsample
+    (1, 32, 10, 10, 32, 3, 3, 2, (0, 0, 0, 0), False),     # "valid" stride 2 after an explicit Pad layer
+    (2, 5, 7, 9, 3, 2, 3, 1, (0, 1, 1, 1), True),          # ragged: rectangular kernel, asymmetric pads
+    (1, 256, 14, 14, 256, 3, 3, 1, (1, 1, 1, 1), False),
+    (2, 512, 7, 7, 512, 3, 3, 1, (1, 1, 1, 1), False),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_conv_all_three_passes(lib, ref, shape):
+    n, c, h, w, k, kr, kc, st, pads, use_bias = shape
+    rng = np.random.default_rng(abs(hash(shape)) % (1 << 31))
+    x = rng.standard_normal((n, c, h, w)).astype(F); wt = rng.standard_normal((k, c, kr, kc)).astype(F)
+    b = rng.standard_normal(k).astype(F) if use_bias else None
+    y0 = orc.conv2d_fwd(x, wt, b, (st, st), pads)
+    dy = rng.standard_normal(y0.shape).astype(F)
+    gw0 = rng.standard_normal(wt.shape).astype(F); dx0 = rng.standard_normal(x.shape).astype(F)
+    gb0 = rng.standard_normal(k).astype(F) if use_bias else None
+    got = run_conv(lib, x, wt, b, dy, gw0, gb0, dx0, (st, st), pads)
+    assert relerr(got["y"], y0) <= 1e-5
+    gw, gb = orc.conv2d_bwd_weight(x, dy, gw0, gb0, (st, st), pads, (kr, kc))
+    assert relerr(got["gw"], gw) <= 1e-5                    # accumulates into the incoming gradient
+    if use_bias:
+        assert relerr(got["gb"], gb) <= 1e-5
+    assert relerr(got["dx"], orc.conv2d_bwd_data(dy, wt, x.shape, dx0, (st, st), pads)) <= 1e-5
+    if ref is not None and x.size * k * kr * kc < 5e8:
+        ry, rgw, rgb, rdx = ref.conv2d(x, wt, b, dy, gw0, gb0, dx0, stride=(st, st), pads=pads)
+        assert relerr(got["y"], ry) <= 1e-5 and relerr(got["gw"], rgw) <= 1e-5 and relerr(got["dx"], rdx) <= 1e-5
+
+
+def test_conv_golden_vectors(lib, kats):
+    for c in kats["conv2d"]:
+        x = np.array(c["x"], F).reshape(c["x_shape"]); k = c["filters"]; kr, kc = c["kernel"]
+        w = np.ones((k, x.shape[1], kr, kc), F) if c["w"] is None else np.array(c["w"], F).reshape(k, x.shape[1], kr, kc)
+        b = np.zeros(k, F) if c["bias"] is None else np.array(c["bias"], F)
+        oh, ow, _ = orc.resolve(c["padding"], x.shape[2], x.shape[3], kr, kc, *c["stride"])
+        got = run_conv(lib, x, w, b, np.ones((1, k, oh, ow), F), None, None, None, tuple(c["stride"]), c["padding"])
+        np.testing.assert_allclose(got["y"].ravel(), c["fwd"], atol=1e-3, rtol=0, err_msg=c["name"])
+        np.testing.assert_allclose(got["dx"].ravel(), c["bwd"], atol=1e-3, rtol=0, err_msg=c["name"])
+
+
+@pytest.mark.parametrize("tag", ["conv_a", "conv_b", "conv_c", "conv_d"])
+def test_conv_against_reference_fixture(lib, refout, tag):
+    r = refout; st, pt, pb, pl, pr, ub = [int(v) for v in r[tag + "_meta"]]
+    got = run_conv(lib, r[tag + "_x"], r[tag + "_w"], r[tag + "_b"] if ub else None, r[tag + "_dy"], r[tag + "_gw0"],
+                   r[tag + "_gb0"] if ub else None, r[tag + "_dx0"], (st, st), (pt, pb, pl, pr))
+    assert relerr(got["y"], r[tag + "_y"]) <= 1e-5
+    assert relerr(got["gw"], r[tag + "_gw"]) <= 1e-5
+    assert relerr(got["dx"], r[tag + "_dx"]) <= 1e-5
+    if ub:
+        assert relerr(got["gb"], r[tag + "_gb"]) <= 1e-5
+
+
+def test_conv_linearity_at_benchmark_size(lib):
+    """Size-independent property at a full microbenchmark shape (N=64, C=1024 -> K=256, 14x14, 1x1): conv(x1 + x2) ==
+    conv(x1) + conv(x2), and <dy, conv(x)> == <conv^T(dy), x> ties the three passes together (adjoint identity)."""
+    rng = np.random.default_rng(11)
+    n, c, h, k = 64, 1024, 14, 256
+    x1 = rng.standard_normal((n, c, h, h)).astype(F); x2 = rng.standard_normal((n, c, h, h)).astype(F)
+    w = (rng.standard_normal((k, c, 1, 1)) / 32).astype(F)
+    dy = rng.standard_normal((n, k, h, h)).astype(F)
+    a = run_conv(lib, x1, w, None, dy, None, None, None, (1, 1), (0, 0, 0, 0))
+    b = run_conv(lib, x2, w, None, None, None, None, None, (1, 1), (0, 0, 0, 0))
+    s = run_conv(lib, (x1 + x2).astype(F), w, None, None, None, None, None, (1, 1), (0, 0, 0, 0))
+    assert relerr(s["y"], a["y"] + b["y"]) <= 2e-5
+    lhs = float(np.sum(dy.astype(np.float64) * a["y"].astype(np.float64)))
+    assert abs(lhs - float(np.sum(a["dx"].astype(np.float64) * x1.astype(np.float64)))) <= 1e-5 * abs(lhs)
+    assert abs(lhs - float(np.sum(a["gw"].astype(np.float64) * w.astype(np.float64)))) <= 1e-5 * abs(lhs)

@@ -133,6 +133,8 @@ def run_reference_arm(args):
 
 
 def run_b200_arm(args):
+    if args.gpus > 1:
+        import torch  # noqa: F401  (first, so that the process-wide libnccl.so.2 is the one torch was built against)
     from eddl_b200 import capi, harness, dist as ebd
     rank, world, local = ebd.rendezvous("gloo")
     if world != args.gpus:

@@ -62,16 +62,20 @@ def share_unique_id(make_id):
 
 
 def max_over_ranks(value):
+    if env_world()[1] == 1:
+        return float(value)
+    import torch
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()):
         return float(value)
-    import torch
     t = torch.tensor([float(value)], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
 
 def barrier():
+    if env_world()[1] == 1:
+        return
     import torch.distributed as dist
     if dist.is_available() and dist.is_initialized():
         dist.barrier()

@@ -176,8 +176,10 @@ def make_ref_outputs():
     net.set_params(w0)
     drng = np.random.default_rng(1234)
     x = drng.random((100, 1, 28, 28), dtype=np.float32); lab = drng.integers(0, 10, 100); y = np.eye(10, dtype=np.float32)[lab]
-    losses = [net.train_batch(x, y)[0] for _ in range(10)]
-    out.update(cnn_losses=np.array(losses, np.float32), cnn_params_after=net.get_params(), cnn_labels=lab.astype(np.int32))
+    losses = [net.train_batch(x, y)[0]]
+    p1 = net.get_params()
+    losses += [net.train_batch(x, y)[0] for _ in range(9)]
+    out.update(cnn_losses=np.array(losses, np.float32), cnn_params_step1=p1, cnn_params_after=net.get_params(), cnn_labels=lab.astype(np.int32))
     net.close()
     np.savez_compressed(os.path.join(HERE, "ref_outputs.npz"), **out)
     print("ref_outputs.npz: %d arrays, cnn losses %s" % (len(out), np.array2string(np.array(losses[:4]), precision=6)))

@@ -338,8 +338,14 @@ def test_single_rank_averaging_is_identity_and_fused_update(lib):
 
 
 def test_allocator_reuse_and_errors(lib):
-    a = lib.empty((1000,)); p = a.ptr.value; del a
-    b = lib.empty((1000,)); assert b.ptr.value == p           # freed block is handed out again
+    import ctypes as ct
+    used0, cached0 = ct.c_size_t(), ct.c_size_t()
+    a = lib.empty((123457,)); del a                          # freed blocks go to the cache ...
+    lib.call("mem_info", 0, ct.byref(used0), ct.byref(cached0))
+    b = lib.empty((123457,))                                 # ... and are handed out again instead of a new cudaMalloc
+    used1, cached1 = ct.c_size_t(), ct.c_size_t()
+    lib.call("mem_info", 0, ct.byref(used1), ct.byref(cached1))
+    assert cached1.value < cached0.value and used1.value > used0.value
     from eddl_b200 import capi
     with pytest.raises(capi.Error):
         lib.call("free", 0, ctypes.c_void_p(12345))

@@ -2,6 +2,7 @@
 // split-K combine.  See conv_tc.cu (tcgen05 tensor-core path) and conv_simt.cu
 // (exact-fp32 FMA path).
 #include <cstdlib>
+#include <cstring>
 #include "common.cuh"
 #include "conv_common.cuh"
 
@@ -42,11 +43,12 @@ int check(const char *what, const ConvGeom &g) {
     return 0;
 }
 
-// EDDL_B200_CONV=simt forces the FMA path (used by tests to compare the two paths).
+// EDDL_B200_CONV=simt (or eddlb200_set_option("conv_path", 1)) forces the FMA path; tests use it to
+// compare the two paths.
+int g_conv_path = -1;
 bool tc_enabled() {
-    static int v = -1;
-    if (v < 0) { const char *e = getenv("EDDL_B200_CONV"); v = (e && e[0] == 's') ? 0 : 1; }
-    return v == 1;
+    if (g_conv_path < 0) { const char *e = getenv("EDDL_B200_CONV"); g_conv_path = (e && e[0] == 's') ? 1 : 0; }
+    return g_conv_path == 0;
 }
 
 }  // namespace
@@ -62,6 +64,11 @@ int splitk_reduce_accumulate(DevCtx *cx, cudaStream_t st, const float *part, flo
 using namespace eb;
 
 extern "C" {
+
+int eddlb200_set_option(const char *name, int value) {
+    if (name && !strcmp(name, "conv_path") && (value == 0 || value == 1)) { g_conv_path = value; return 0; }
+    return set_error(EDDLB200_EINVAL, "set_option: unknown option or value");
+}
 
 int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias, float *y,
                         int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,

@@ -22,6 +22,9 @@ int conv_tc_fwd(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, 
 int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision);
 int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *dy, float *gw, int precision);
 
+// Reads and clears the device's time-out flag of the tensor-core kernels (blocking).
+int conv_tc_status(int dev, cudaStream_t st, int *out);
+
 // out[i] += sum_{s<splits} part[s*count + i], s ascending.
 int splitk_reduce_accumulate(DevCtx *cx, cudaStream_t st, const float *part, float *out, size_t count, int splits);
 

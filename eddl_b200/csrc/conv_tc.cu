@@ -1,7 +1,489 @@
-// placeholder, replaced below
+// Conv2D forward / backward-data / backward-weight as ONE implicit-GEMM kernel on the
+// Blackwell tensor cores: tcgen05.mma (kind::tf32, cta_group::1, M=128) with the fp32
+// accumulator in tensor memory, operands staged in shared memory in the canonical K-major
+// SWIZZLE_128B layout, mbarrier producer/consumer pipeline, tcgen05.ld epilogue.
+// Replaces gpu_im2col_k + cublasSgemm + gpu_traspose_batch_depth of EDDL
+// (src/hardware/gpu/nn/gpu_conv.cu:159-372); the contraction is cpu_conv2D / cpu_conv2D_grad /
+// cpu_conv2D_back (src/hardware/cpu/nn/cpu_conv.cpp:114-280).
+//
+// GEMM view (D[m][n] = sum_k A[m][k] * B[n][k], 128 x BN output tile per CTA):
+//   forward          m = output pixel (n,p,q)   n = filter        k = (c,r,s)   A = x gathered, B = w
+//   backward-data    m = input pixel (n,y,x)    n = in-channel    k = (f,r,s)   A = dy gathered, B = w
+//   backward-weight  m = (c,r,s)                n = filter        k = (n,p,q)   A = x gathered, B = dy
+// In all three the address of an operand element separates into a row part plus a k part
+// (src[rowOff[row] + kOff[k]]) and zero padding is the test 0 <= rowY+kY < limY, 0 <= rowX+kX < limX,
+// so small index tables built by a set-up kernel drive a single gather routine: no im2col
+// buffer, no col2im atomics, no layout transposes.  Pixels sit on the M (TMEM lane) axis, so the
+// epilogue's stores are coalesced along the NCHW pixel dimension.
+//
+// fp32-equivalent mode (precision 0) is the 3xTF32 split: every operand value v is staged as
+// hi = v with the 13 low mantissa bits cleared and lo = v - hi (exact), and each k-step issues
+// hi*hi + lo*hi + hi*lo into the same fp32 accumulator.  precision 1 issues hi*hi only.
+//
+// The producers gather with ordinary coalesced loads rather than TMA tensor copies: the tap
+// offset (s - pad) of an NCHW row is not a multiple of 16 bytes, and the hi/lo split needs a
+// pass through registers anyway.
+// Every wait on an mbarrier is bounded; on time-out the kernel records a status code, leaves
+// its loops, frees its tensor memory and returns.
+#include "common.cuh"
 #include "conv_common.cuh"
-namespace eb {
-int conv_tc_fwd(DevCtx *, cudaStream_t, const ConvGeom &, const float *, const float *, const float *, float *, int) { return 1; }
-int conv_tc_bwd_data(DevCtx *, cudaStream_t, const ConvGeom &, const float *, const float *, float *, int) { return 1; }
-int conv_tc_bwd_weight(DevCtx *, cudaStream_t, const ConvGeom &, const float *, const float *, float *, int) { return 1; }
+
+namespace {
+
+using namespace eb;
+
+constexpr int BM = 128;             // UMMA M (TMEM lanes)
+constexpr int BK = 32;              // fp32 per 128-byte swizzle row
+constexpr int NPROD = 256;          // producer threads (warps 0-7); warp 8 issues the MMAs
+constexpr int NTHREADS = NPROD + 32;
+constexpr int INVALID_Y = -20000;
+
+struct TcParams {
+    const float *srcA, *srcB;
+    float *out;
+    const float *bias;      // per n (forward only), may be null
+    const int2 *rowA;       // [M_total]  .x = offset part, .y = (y << 16) | (x & 0xffff)
+    const int2 *kA;         // [K_pad]
+    const int *rowB;        // [N_total]
+    const int *kB;          // [K_pad]    -1 = beyond K_total
+    const int *outM;        // [M_total]
+    int out_n_stride;
+    int M_total, N_total, K_pad;
+    int limY, limX;
+    int kblocks_per_split;
+    long long split_stride; // elements between the partial outputs of consecutive splits
+    int accumulate;
+    int *status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2 s of SM clock and reports false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++) if (mbar_try(bar, parity)) return true;
+        if (clock64() - t0 > 4000000000LL) return false;
+    }
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major SWIZZLE_128B shared-memory matrix descriptor: rows of 128 bytes, 8-row groups 1024 bytes
+// apart (stride byte offset), descriptor version 1, layout type 2, 1024-byte aligned tile base.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// fp32 accumulate, TF32 x TF32, both operands K-major, M = 128, N = bn
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void split_tf32(float v, float &hi, float &lo) {
+    hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    lo = __fsub_rn(v, hi);
+}
+
+// byte offset of element (row, k) inside a [rows][32 fp32] SWIZZLE_128B tile
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t k) {
+    return row * 128u + ((((k >> 2) ^ row) & 7u) << 4) + ((k & 3u) << 2);
+}
+
+template <int BN_, bool SPLIT3>
+struct Layout {
+    static constexpr int A_BYTES = BM * BK * 4;
+    static constexpr int B_BYTES = BN_ * BK * 4;
+    static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (SPLIT3 ? 2 : 1);
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 4 ? 4 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int TABLE_BYTES = BM * 8 + BN_ * 4;
+    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + TABLE_BYTES + 256;
+};
+
+// A_ROWMAJOR: consecutive rows of A are consecutive in memory (pixels) -> one thread per row, vector stores;
+// otherwise consecutive k are consecutive in memory -> one lane per k.
+template <int BN_, bool SPLIT3, bool A_ROWMAJOR>
+__global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P) {
+    using L = Layout<BN_, SPLIT3>;
+    constexpr int STAGES = L::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *stage_base = smem;
+    int2 *sRowA = (int2 *)(smem + STAGES * L::STAGE_BYTES);
+    int *sRowB = (int *)(sRowA + BM);
+    uint64_t *bars = (uint64_t *)(sRowB + BN_);             // full[STAGES], empty[STAGES], accum
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN_;
+    const int kb_begin = blockIdx.z * P.kblocks_per_split;
+    const int kb_total = P.K_pad / BK;
+    const int kb_end = min(kb_total, kb_begin + P.kblocks_per_split);
+    const int nkb = kb_end - kb_begin;
+
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_accum = smem_u32(bars + 2 * STAGES);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD); mbar_init(bar_empty + 8 * s, 1); }
+        mbar_init(bar_accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < BM; i += NTHREADS) {
+        const int m = m0 + i;
+        sRowA[i] = m < P.M_total ? P.rowA[m] : make_int2(0, (INVALID_Y << 16));
+    }
+    for (int i = tid; i < BN_; i += NTHREADS) {
+        const int n = n0 + i;
+        sRowB[i] = n < P.N_total ? P.rowB[n] : -1;
+    }
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), BN_);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool failed = false;
+
+    if (warp < 8) {
+        // ============================ producers ============================
+        int2 myRow = make_int2(0, 0);
+        if (A_ROWMAJOR) myRow = sRowA[tid & (BM - 1)];
+        for (int it = 0; it < nkb; it++) {
+            const int s = it % STAGES;
+            const uint32_t par = ((it / STAGES) & 1) ^ 1;
+            if (!mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+            uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
+            uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
+            uint8_t *sB_hi = sA_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
+            uint8_t *sB_lo = sB_hi + L::B_BYTES;
+            const int kbase = (kb_begin + it) * BK;
+            // ---- A tile: 128 rows x 32 k ----
+            if (A_ROWMAJOR) {
+                const int row = tid & (BM - 1), half = tid >> 7;
+                const int ry = myRow.y >> 16, rx = (int)(short)(myRow.y & 0xffff);
+                const float *base = P.srcA + myRow.x;
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    float v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int2 ke = __ldg(P.kA + kbase + half * 16 + g * 4 + u);
+                        const int y = ry + (ke.y >> 16), x = rx + (int)(short)(ke.y & 0xffff);
+                        const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
+                        v[u] = ok ? __ldg(base + ke.x) : 0.f;
+                    }
+                    float4 hi, lo;
+                    split_tf32(v[0], hi.x, lo.x); split_tf32(v[1], hi.y, lo.y); split_tf32(v[2], hi.z, lo.z); split_tf32(v[3], hi.w, lo.w);
+                    const uint32_t off = swz(row, half * 16 + g * 4);
+                    if (SPLIT3) { *(float4 *)(sA_hi + off) = hi; *(float4 *)(sA_lo + off) = lo; }
+                    else *(float4 *)(sA_hi + off) = make_float4(v[0], v[1], v[2], v[3]);
+                }
+            } else {
+                const int2 ke = __ldg(P.kA + kbase + lane);
+                const int ky = ke.y >> 16, kx = (int)(short)(ke.y & 0xffff);
+                const float *base = P.srcA + ke.x;
+#pragma unroll 4
+                for (int r = 0; r < BM / 8; r++) {
+                    const int row = warp * (BM / 8) + r;
+                    const int2 re = sRowA[row];
+                    const int y = (re.y >> 16) + ky, x = (int)(short)(re.y & 0xffff) + kx;
+                    const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
+                    const float v = ok ? __ldg(base + re.x) : 0.f;
+                    const uint32_t off = swz(row, lane);
+                    if (SPLIT3) { float hi, lo; split_tf32(v, hi, lo); *(float *)(sA_hi + off) = hi; *(float *)(sA_lo + off) = lo; }
+                    else *(float *)(sA_hi + off) = v;
+                }
+            }
+            // ---- B tile: BN rows x 32 k, one lane per k ----
+            {
+                const int kb = __ldg(P.kB + kbase + lane);
+                const float *base = P.srcB + (kb < 0 ? 0 : kb);
+#pragma unroll 4
+                for (int r = 0; r < BN_ / 8; r++) {
+                    const int row = warp * (BN_ / 8) + r;
+                    const int ro = sRowB[row];
+                    const float v = (kb >= 0 && ro >= 0) ? __ldg(base + ro) : 0.f;
+                    const uint32_t off = swz(row, lane);
+                    if (SPLIT3) { float hi, lo; split_tf32(v, hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
+                    else *(float *)(sB_hi + off) = v;
+                }
+            }
+            fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
+            mbar_arrive(bar_full + 8 * s);
+        }
+    } else if (lane == 0) {
+        // ============================ MMA issuer (one thread) ============================
+        const uint32_t idesc = make_idesc(BN_);
+        for (int it = 0; it < nkb; it++) {
+            const int s = it % STAGES;
+            if (!mbar_wait(bar_full + 8 * s, (it / STAGES) & 1)) { failed = true; break; }
+            tc_fence_after();
+            const uint32_t a_hi = smem_u32(stage_base + s * L::STAGE_BYTES);
+            const uint32_t a_lo = a_hi + L::A_BYTES;
+            const uint32_t b_hi = a_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
+            const uint32_t b_lo = b_hi + L::B_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ks++) {
+                const uint32_t o = ks * 32;      // 8 fp32 = 32 bytes along K inside the swizzle row
+                const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
+                if (SPLIT3) {
+                    // small terms first, the dominant hi*hi term last
+                    umma_tf32(tmem_base, make_desc(a_lo + o), make_desc(b_hi + o), idesc, acc);
+                    umma_tf32(tmem_base, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
+                    umma_tf32(tmem_base, make_desc(a_hi + o), make_desc(b_hi + o), idesc, 1u);
+                } else {
+                    umma_tf32(tmem_base, make_desc(a_hi + o), make_desc(b_hi + o), idesc, acc);
+                }
+            }
+            umma_commit(bar_empty + 8 * s);      // frees the stage when these MMAs have read it
+        }
+        umma_commit(bar_accum);                  // accumulator complete
+    }
+    __syncwarp();
+
+    // ============================ epilogue (warps 0-3: TMEM lanes 32*warp ..) ============================
+    if (warp < 4 && nkb > 0) {
+        if (!failed && !mbar_wait(bar_accum, 0)) failed = true;
+        tc_fence_after();
+        if (!failed) {
+            const int m = m0 + warp * 32 + lane;
+            const bool m_ok = m < P.M_total;
+            float *obase = P.out + (long long)blockIdx.z * P.split_stride + (m_ok ? (long long)P.outM[m] : 0);
+#pragma unroll 1
+            for (int c = 0; c < BN_ / 32; c++) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
+                if (m_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int n = n0 + c * 32 + j;
+                        if (n < P.N_total) {
+                            float v = __uint_as_float(r[j]);
+                            if (P.bias) v = __fadd_rn(v, __ldg(P.bias + n));
+                            float *dst = obase + (long long)n * P.out_n_stride;
+                            if (P.accumulate) v = __fadd_rn(*dst, v);
+                            *dst = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (failed) atomicExch(P.status, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) tmem_dealloc(tmem_base, BN_);
+}
+
+// ---- index tables ----------------------------------------------------------------------------------
+__device__ __forceinline__ int pack_yx(int y, int x) { return (y << 16) | (x & 0xffff); }
+
+struct TableArgs {
+    ConvGeom g; int mode;       // 0 fwd, 1 bwd-data, 2 bwd-weight
+    int2 *rowA, *kA; int *rowB, *kB, *outM;
+    int M_total, N_total, K_total, K_pad;
+};
+
+__global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
+    const ConvGeom g = T.g;
+    const int pq = g.oh * g.ow, hw = g.ih * g.iw, rs = g.kr * g.kc;
+    const long long total = (long long)T.M_total + T.K_pad + T.N_total;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        if (i < T.M_total) {
+            const int m = (int)i;
+            if (T.mode == 0) {              // output pixel
+                const int n = m / pq, t = m - n * pq, p = t / g.ow, q = t - p * g.ow;
+                const int y = p * g.sr - g.pt, x = q * g.sc - g.pl;
+                T.rowA[m] = make_int2(n * g.c * hw + y * g.iw + x, pack_yx(y, x));
+                T.outM[m] = n * g.k * pq + t;
+            } else if (T.mode == 1) {       // input pixel (stride 1)
+                const int n = m / hw, t = m - n * hw, y = t / g.iw, x = t - y * g.iw;
+                T.rowA[m] = make_int2(n * g.k * pq + (y + g.pt) * g.ow + (x + g.pl), pack_yx(y + g.pt, x + g.pl));
+                T.outM[m] = n * g.c * hw + t;
+            } else {                        // (c, r, s)
+                const int c = m / rs, t = m - c * rs, r = t / g.kc, s = t - r * g.kc;
+                T.rowA[m] = make_int2(c * hw + (r - g.pt) * g.iw + (s - g.pl), pack_yx(r - g.pt, s - g.pl));
+                T.outM[m] = m;
+            }
+        } else if (i < (long long)T.M_total + T.K_pad) {
+            const int k = (int)(i - T.M_total);
+            if (k >= T.K_total) { T.kA[k] = make_int2(0, pack_yx(INVALID_Y, 0)); T.kB[k] = -1; continue; }
+            if (T.mode == 0) {              // (c, r, s)
+                const int c = k / rs, t = k - c * rs, r = t / g.kc, s = t - r * g.kc;
+                T.kA[k] = make_int2(c * hw + r * g.iw + s, pack_yx(r, s));
+                T.kB[k] = k;
+            } else if (T.mode == 1) {       // (f, r, s)
+                const int f = k / rs, t = k - f * rs, r = t / g.kc, s = t - r * g.kc;
+                T.kA[k] = make_int2(f * pq - r * g.ow - s, pack_yx(-r, -s));
+                T.kB[k] = f * g.c * rs + t;
+            } else {                        // (n, p, q)
+                const int n = k / pq, t = k - n * pq, p = t / g.ow, q = t - p * g.ow;
+                T.kA[k] = make_int2(n * g.c * hw + p * g.sr * g.iw + q * g.sc, pack_yx(p * g.sr, q * g.sc));
+                T.kB[k] = n * g.k * pq + t;
+            }
+        } else {
+            const int n = (int)(i - T.M_total - T.K_pad);
+            if (T.mode == 0) T.rowB[n] = n * T.K_total;         // filter row of w[f][c*r*s]
+            else if (T.mode == 1) T.rowB[n] = n * rs;           // in-channel c of w[f][c][r][s]
+            else T.rowB[n] = n * pq;                            // filter plane of dy[n][f][p*q]
+        }
+    }
+}
+
+template <int BN_, bool SPLIT3, bool A_ROWMAJOR>
+int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
+    using L = Layout<BN_, SPLIT3>;
+    static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
+    bool &configured = configured_dev[dev];
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, SPLIT3, A_ROWMAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_status(e, "conv_tc(smem attribute)");
+        configured = true;
+    }
+    igemm_tc_kernel<BN_, SPLIT3, A_ROWMAJOR><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
+    EB_LAUNCH_CHECK("conv_tc");
+    return 0;
+}
+
+template <bool SPLIT3, bool A_ROWMAJOR>
+int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn, int dev) {
+    if (bn == 64) return launch_variant<64, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
+    if (bn == 128) return launch_variant<128, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
+    return launch_variant<256, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
+}
+
+int *g_status[EDDLB200_MAX_DEVICES] = {};
+
+int run(DevCtx *cx, cudaStream_t st, int dev, int mode, const ConvGeom &g, const float *srcA, const float *srcB, float *out,
+        const float *bias, int precision) {
+    const int pq = g.oh * g.ow, hw = g.ih * g.iw, rs = g.kr * g.kc;
+    TableArgs T{};
+    T.g = g; T.mode = mode;
+    TcParams P{};
+    if (mode == 0) { T.M_total = g.n * pq; T.N_total = g.k; T.K_total = g.c * rs; P.limY = g.ih; P.limX = g.iw; P.out_n_stride = pq; }
+    else if (mode == 1) { T.M_total = g.n * hw; T.N_total = g.c; T.K_total = g.k * rs; P.limY = g.oh; P.limX = g.ow; P.out_n_stride = hw; }
+    else { T.M_total = g.c * rs; T.N_total = g.k; T.K_total = g.n * pq; P.limY = g.ih; P.limX = g.iw; P.out_n_stride = g.c * rs; }
+    T.K_pad = (T.K_total + BK - 1) / BK * BK;
+    const int bn = T.N_total <= 64 ? 64 : (T.N_total <= 128 ? 128 : 256);
+    const int tiles_m = (T.M_total + BM - 1) / BM, tiles_n = (T.N_total + bn - 1) / bn;
+    const int kblocks = T.K_pad / BK;
+    int splits = 1;
+    if (mode == 2) {
+        const int tiles = tiles_m * tiles_n;
+        splits = (EDDLB200_NUM_SMS * 2 + tiles - 1) / tiles;
+        if (splits > kblocks / 4) splits = kblocks / 4;
+        if (splits > 128) splits = 128;
+        if (splits < 1) splits = 1;
+    }
+    int kbs = (kblocks + splits - 1) / splits;
+    splits = (kblocks + kbs - 1) / kbs;
+    const size_t out_elems = (size_t)T.M_total * T.N_total;
+    // one scratch carve-up: tables, status word, split-K partials
+    size_t off = 0;
+    auto carve = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };
+    const size_t o_rowA = carve((size_t)T.M_total * 8), o_kA = carve((size_t)T.K_pad * 8), o_rowB = carve((size_t)T.N_total * 4),
+                 o_kB = carve((size_t)T.K_pad * 4), o_outM = carve((size_t)T.M_total * 4),
+                 o_part = carve(splits > 1 ? out_elems * splits * sizeof(float) : 0);
+    char *ws = (char *)scratch(cx, off);
+    if (!ws) return cudaErrorMemoryAllocation;
+    if (!g_status[dev]) {
+        if (cudaMalloc((void **)&g_status[dev], sizeof(int)) != cudaSuccess) return cudaErrorMemoryAllocation;
+        cudaMemsetAsync(g_status[dev], 0, sizeof(int), st);
+    }
+    T.rowA = (int2 *)(ws + o_rowA); T.kA = (int2 *)(ws + o_kA); T.rowB = (int *)(ws + o_rowB); T.kB = (int *)(ws + o_kB); T.outM = (int *)(ws + o_outM);
+    const long long entries = (long long)T.M_total + T.K_pad + T.N_total;
+    build_tables_kernel<<<grid_for((size_t)entries, 256), 256, 0, st>>>(T);
+    EB_LAUNCH_CHECK("conv_tc(tables)");
+    P.srcA = srcA; P.srcB = srcB; P.bias = bias;
+    P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM;
+    P.M_total = T.M_total; P.N_total = T.N_total; P.K_pad = T.K_pad;
+    P.kblocks_per_split = kbs;
+    P.status = g_status[dev];
+    if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_elems; P.accumulate = 0; }
+    else { P.out = out; P.split_stride = 0; P.accumulate = (mode != 0); }
+    dim3 grid(tiles_m, tiles_n, splits);
+    int r;
+    const bool split3 = precision == 0;
+    if (mode == 2) r = split3 ? launch_bn<true, false>(cx, st, P, grid, bn, dev) : launch_bn<false, false>(cx, st, P, grid, bn, dev);
+    else r = split3 ? launch_bn<true, true>(cx, st, P, grid, bn, dev) : launch_bn<false, true>(cx, st, P, grid, bn, dev);
+    if (r) return r;
+    if (splits > 1) return splitk_reduce_accumulate(cx, st, (const float *)(ws + o_part), out, out_elems, splits);
+    return 0;
+}
+
+bool fits(const ConvGeom &g) {
+    // index tables hold 16-bit coordinates and 32-bit offsets
+    return g.ih < 16000 && g.iw < 16000 && g.oh < 16000 && g.ow < 16000;
+}
+
+}  // namespace
+
+namespace eb {
+
+int conv_tc_fwd(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *w, const float *bias, float *y, int precision) {
+    if (!fits(g)) return 1;
+    int dev = 0; cudaGetDevice(&dev);
+    return run(cx, st, dev, 0, g, x, w, y, bias, precision);
+}
+
+int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision) {
+    if (!fits(g) || g.sr != 1 || g.sc != 1) return 1;   // strided backward-data keeps the FMA path
+    int dev = 0; cudaGetDevice(&dev);
+    return run(cx, st, dev, 1, g, dy, w, dx, nullptr, precision);
+}
+
+int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *dy, float *gw, int precision) {
+    if (!fits(g)) return 1;
+    int dev = 0; cudaGetDevice(&dev);
+    return run(cx, st, dev, 2, g, x, dy, gw, nullptr, precision);
+}
+
+// 0 = no kernel of this file has timed out on the device since the last call
+int conv_tc_status(int dev, cudaStream_t st, int *out) {
+    *out = 0;
+    if (!g_status[dev]) return 0;
+    cudaError_t e = cudaMemcpyAsync(out, g_status[dev], sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess && *out) e = cudaMemsetAsync(g_status[dev], 0, sizeof(int), st);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+}  // namespace eb

@@ -13,6 +13,7 @@
 #include <unordered_map>
 #include <vector>
 #include "common.cuh"
+#include "conv_common.cuh"
 
 namespace eb {
 
@@ -234,7 +235,11 @@ int eddlb200_stream(int dev, void **s) {
 
 int eddlb200_sync(int dev) {
     EB_CTX(dev);
-    return cuda_status(cudaStreamSynchronize(st), "eddlb200_sync");
+    if (int r = cuda_status(cudaStreamSynchronize(st), "eddlb200_sync")) return r;
+    int flag = 0;
+    if (int r = conv_tc_status(dev, st, &flag)) return cuda_status((cudaError_t)r, "eddlb200_sync");
+    if (flag) return set_error(EDDLB200_ETIMEOUT, "a tensor-core convolution kernel gave up waiting on a pipeline barrier");
+    return 0;
 }
 
 int eddlb200_timer_start(int dev, int slot) {

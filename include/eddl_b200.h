@@ -159,6 +159,8 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *      src/hardware/cpu/nn/cpu_conv.cpp:114-280,316-527).  Cross-correlation, zero padding,
  *      x [n,c,ih,iw], w [k,c,kr,kc], y [n,k,oh,ow].  precision: 0 = fp32-equivalent
  *      (3xTF32 split on the tensor cores or fp32 FMA), 1 = plain TF32. */
+/* Options: "conv_path" 0 = tensor-core kernel where it applies (default), 1 = fp32 FMA kernel only. */
+int eddlb200_set_option(const char *name, int value);
 int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias /* may be null */, float *y,
                         int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
                         int sr, int sc, int pad_top, int pad_left, int precision);

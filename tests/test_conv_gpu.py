@@ -110,3 +110,24 @@ def test_conv_linearity_at_benchmark_size(lib):
     lhs = float(np.sum(dy.astype(np.float64) * a["y"].astype(np.float64)))
     assert abs(lhs - float(np.sum(a["dx"].astype(np.float64) * x1.astype(np.float64)))) <= 1e-5 * abs(lhs)
     assert abs(lhs - float(np.sum(a["gw"].astype(np.float64) * w.astype(np.float64)))) <= 1e-5 * abs(lhs)
+
+
+@pytest.mark.parametrize("shape", [(4, 64, 14, 14, 96, 3, 3, 1, (1, 1, 1, 1)), (2, 48, 9, 9, 40, 1, 1, 1, (0, 0, 0, 0)), (2, 16, 20, 20, 24, 3, 3, 2, (1, 1, 1, 1))])
+def test_tensor_core_path_against_fma_path_and_tf32_mode(lib, shape):
+    """The tcgen05 kernel (3xTF32) and the fp32 FMA kernel agree to 1e-5; plain TF32 (precision 1) stays within 1e-3."""
+    n, c, h, w, k, kr, kc, st, pads = shape
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((n, c, h, w)).astype(F); wt = rng.standard_normal((k, c, kr, kc)).astype(F)
+    oh, ow, _ = orc.resolve(pads, h, w, kr, kc, st, st)
+    dy = rng.standard_normal((n, k, oh, ow)).astype(F)
+    try:
+        lib.call("set_option", b"conv_path", 1)
+        a = run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads)
+    finally:
+        lib.call("set_option", b"conv_path", 0)
+    b = run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads)
+    t = run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads, precision=1)
+    for key in ("y", "gw", "dx"):
+        assert relerr(b[key], a[key]) <= 1e-5, key
+        assert relerr(t[key], a[key]) <= 1e-3, key
+    lib.call("sync", 0)     # also reports a pipeline time-out of the tensor-core kernel, if any

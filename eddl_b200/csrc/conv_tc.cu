@@ -20,6 +20,12 @@
 // hi = v with the 13 low mantissa bits cleared and lo = v - hi (exact), and each k-step issues
 // hi*hi + lo*hi + hi*lo into the same fp32 accumulator.  precision 1 issues hi*hi only.
 //
+// The tensor core adds each MMA into the fp32 accumulator with truncation, so a long chain of
+// accumulations drifts toward zero in proportion to its length (measured: 3e-5 relative at K = 4096
+// with a single accumulator).  The kernel therefore keeps FOUR accumulators of BN columns in tensor
+// memory: the dominant hi*hi products rotate over three of them k-step by k-step (chain length K/24)
+// and the two small cross terms go to the fourth; the epilogue adds the four in fp32 with rounding.
+//
 // The producers gather with ordinary coalesced loads rather than TMA tensor copies: the tap
 // offset (s - pad) of an NCHW row is not a multiple of 16 bytes, and the hi/lo split needs a
 // pass through registers anyway.
@@ -37,6 +43,7 @@ constexpr int BK = 32;              // fp32 per 128-byte swizzle row
 constexpr int NPROD = 256;          // producer threads (warps 0-7); warp 8 issues the MMAs
 constexpr int NTHREADS = NPROD + 32;
 constexpr int INVALID_Y = -20000;
+constexpr int NMAIN = 3;             // rotating hi*hi accumulators; a fourth holds the cross terms
 
 struct TcParams {
     const float *srcA, *srcB;
@@ -175,7 +182,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
         const int n = n0 + i;
         sRowB[i] = n < P.N_total ? P.rowB[n] : -1;
     }
-    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), BN_);
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), 4 * BN_);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -263,15 +270,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
 #pragma unroll
             for (int ks = 0; ks < BK / 8; ks++) {
                 const uint32_t o = ks * 32;      // 8 fp32 = 32 bytes along K inside the swizzle row
-                const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
+                const int step = it * (BK / 8) + ks;
+                const uint32_t d_main = tmem_base + (uint32_t)((step % NMAIN) * BN_);
                 if (SPLIT3) {
-                    // small terms first, the dominant hi*hi term last
-                    umma_tf32(tmem_base, make_desc(a_lo + o), make_desc(b_hi + o), idesc, acc);
-                    umma_tf32(tmem_base, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
-                    umma_tf32(tmem_base, make_desc(a_hi + o), make_desc(b_hi + o), idesc, 1u);
-                } else {
-                    umma_tf32(tmem_base, make_desc(a_hi + o), make_desc(b_hi + o), idesc, acc);
+                    const uint32_t d_small = tmem_base + (uint32_t)(NMAIN * BN_);
+                    umma_tf32(d_small, make_desc(a_lo + o), make_desc(b_hi + o), idesc, step > 0 ? 1u : 0u);
+                    umma_tf32(d_small, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
                 }
+                umma_tf32(d_main, make_desc(a_hi + o), make_desc(b_hi + o), idesc, step >= NMAIN ? 1u : 0u);
             }
             umma_commit(bar_empty + 8 * s);      // frees the stage when these MMAs have read it
         }
@@ -288,9 +294,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             const bool m_ok = m < P.M_total;
             float *obase = P.out + (long long)blockIdx.z * P.split_stride + (m_ok ? (long long)P.outM[m] : 0);
 #pragma unroll 1
-            for (int c = 0; c < BN_ / 32; c++) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
+            for (int c = 0; c < (BN_ + 31) / 32; c++) {
+                uint32_t r[32], t[32];
+                const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32);
+                tmem_ld32(lane_base, r);
+                // nkb >= 1 gives at least four k-steps, so all three rotating accumulators hold data
+#pragma unroll 1
+                for (int a = 1; a < (SPLIT3 ? NMAIN + 1 : NMAIN); a++) {
+                    tmem_ld32(lane_base + (uint32_t)(a * BN_), t);
+#pragma unroll
+                    for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(t[j])));
+                }
                 if (m_ok) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
@@ -310,7 +324,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
     if (failed) atomicExch(P.status, 1);
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) tmem_dealloc(tmem_base, BN_);
+    if (warp == 8) tmem_dealloc(tmem_base, 4 * BN_);
 }
 
 // ---- index tables ----------------------------------------------------------------------------------
@@ -318,6 +332,10 @@ __device__ __forceinline__ int pack_yx(int y, int x) { return (y << 16) | (x & 0
 
 struct TableArgs {
     ConvGeom g; int mode;       // 0 fwd, 1 bwd-data, 2 bwd-weight
+    // backward-data only: residue class (ca, cb) of (y+pt, x+pl) modulo the strides.  Input pixels of one
+    // class receive contributions only from the taps r = ca + r'*sr, s = cb + s'*sc, which turns a strided
+    // backward pass into sr*sc dense stride-1 problems with no wasted taps.
+    int ca, cb, y0, x0, hc, wc, rt, st_;
     int2 *rowA, *kA; int *rowB, *kB, *outM;
     int M_total, N_total, K_total, K_pad;
 };
@@ -334,10 +352,13 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
                 const int y = p * g.sr - g.pt, x = q * g.sc - g.pl;
                 T.rowA[m] = make_int2(n * g.c * hw + y * g.iw + x, pack_yx(y, x));
                 T.outM[m] = n * g.k * pq + t;
-            } else if (T.mode == 1) {       // input pixel (stride 1)
-                const int n = m / hw, t = m - n * hw, y = t / g.iw, x = t - y * g.iw;
-                T.rowA[m] = make_int2(n * g.k * pq + (y + g.pt) * g.ow + (x + g.pl), pack_yx(y + g.pt, x + g.pl));
-                T.outM[m] = n * g.c * hw + t;
+            } else if (T.mode == 1) {       // input pixel of the residue class
+                const int per = T.hc * T.wc;
+                const int n = m / per, t = m - n * per, i = t / T.wc, j = t - i * T.wc;
+                const int y = T.y0 + i * g.sr, x = T.x0 + j * g.sc;
+                const int yc = (y + g.pt - T.ca) / g.sr, xc = (x + g.pl - T.cb) / g.sc;
+                T.rowA[m] = make_int2(n * g.k * pq + yc * g.ow + xc, pack_yx(yc, xc));
+                T.outM[m] = n * g.c * hw + y * g.iw + x;
             } else {                        // (c, r, s)
                 const int c = m / rs, t = m - c * rs, r = t / g.kc, s = t - r * g.kc;
                 T.rowA[m] = make_int2(c * hw + (r - g.pt) * g.iw + (s - g.pl), pack_yx(r - g.pt, s - g.pl));
@@ -350,10 +371,11 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
                 const int c = k / rs, t = k - c * rs, r = t / g.kc, s = t - r * g.kc;
                 T.kA[k] = make_int2(c * hw + r * g.iw + s, pack_yx(r, s));
                 T.kB[k] = k;
-            } else if (T.mode == 1) {       // (f, r, s)
-                const int f = k / rs, t = k - f * rs, r = t / g.kc, s = t - r * g.kc;
-                T.kA[k] = make_int2(f * pq - r * g.ow - s, pack_yx(-r, -s));
-                T.kB[k] = f * g.c * rs + t;
+            } else if (T.mode == 1) {       // (f, r', s') with r = ca + r'*sr, s = cb + s'*sc
+                const int taps = T.rt * T.st_;
+                const int f = k / taps, t = k - f * taps, r2 = t / T.st_, s2 = t - r2 * T.st_;
+                T.kA[k] = make_int2(f * pq - r2 * g.ow - s2, pack_yx(-r2, -s2));
+                T.kB[k] = f * g.c * rs + (T.ca + r2 * g.sr) * g.kc + (T.cb + s2 * g.sc);
             } else {                        // (n, p, q)
                 const int n = k / pq, t = k - n * pq, p = t / g.ow, q = t - p * g.ow;
                 T.kA[k] = make_int2(n * g.c * hw + p * g.sr * g.iw + q * g.sc, pack_yx(p * g.sr, q * g.sc));
@@ -385,43 +407,51 @@ int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, in
 
 template <bool SPLIT3, bool A_ROWMAJOR>
 int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn, int dev) {
+    if (bn == 32) return launch_variant<32, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
     if (bn == 64) return launch_variant<64, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
-    if (bn == 128) return launch_variant<128, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
-    return launch_variant<256, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
+    return launch_variant<128, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
 }
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
 
-int run(DevCtx *cx, cudaStream_t st, int dev, int mode, const ConvGeom &g, const float *srcA, const float *srcB, float *out,
-        const float *bias, int precision) {
-    const int pq = g.oh * g.ow, hw = g.ih * g.iw, rs = g.kr * g.kc;
-    TableArgs T{};
-    T.g = g; T.mode = mode;
-    TcParams P{};
-    if (mode == 0) { T.M_total = g.n * pq; T.N_total = g.k; T.K_total = g.c * rs; P.limY = g.ih; P.limX = g.iw; P.out_n_stride = pq; }
-    else if (mode == 1) { T.M_total = g.n * hw; T.N_total = g.c; T.K_total = g.k * rs; P.limY = g.oh; P.limX = g.ow; P.out_n_stride = hw; }
-    else { T.M_total = g.c * rs; T.N_total = g.k; T.K_total = g.n * pq; P.limY = g.ih; P.limX = g.iw; P.out_n_stride = g.c * rs; }
+// out[i] = sum_s part[s][i] (+ bias[(i / plane) % nbias])      (split-K forward)
+__global__ void __launch_bounds__(256) splitk_store_kernel(const float *__restrict__ part, float *__restrict__ out, size_t count, int splits,
+                                                           const float *__restrict__ bias, int plane, int nbias) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float v = 0.f;
+        for (int z = 0; z < splits; z++) v += part[(size_t)z * count + i];
+        if (bias) v = __fadd_rn(v, __ldg(bias + (i / plane) % nbias));
+        out[i] = v;
+    }
+}
+
+// One GEMM launch (tables + main kernel + optional split-K combine).  T carries mode / class fields and the
+// problem extents; out_total is the element count of the output tensor (the unit of a split-K partial).
+int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const float *srcA, const float *srcB, float *out,
+            const float *bias, int precision, size_t out_total, bool allow_split) {
+    const ConvGeom &g = T.g;
+    const int mode = T.mode;
     T.K_pad = (T.K_total + BK - 1) / BK * BK;
-    const int bn = T.N_total <= 64 ? 64 : (T.N_total <= 128 ? 128 : 256);
+    const int bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);
     const int tiles_m = (T.M_total + BM - 1) / BM, tiles_n = (T.N_total + bn - 1) / bn;
     const int kblocks = T.K_pad / BK;
     int splits = 1;
-    if (mode == 2) {
-        const int tiles = tiles_m * tiles_n;
+    const int tiles = tiles_m * tiles_n;
+    if (allow_split && tiles < EDDLB200_NUM_SMS * 2) {
         splits = (EDDLB200_NUM_SMS * 2 + tiles - 1) / tiles;
         if (splits > kblocks / 4) splits = kblocks / 4;
         if (splits > 128) splits = 128;
         if (splits < 1) splits = 1;
     }
-    int kbs = (kblocks + splits - 1) / splits;
+    const int kbs = (kblocks + splits - 1) / splits;
     splits = (kblocks + kbs - 1) / kbs;
-    const size_t out_elems = (size_t)T.M_total * T.N_total;
-    // one scratch carve-up: tables, status word, split-K partials
+    // one scratch carve-up: tables and split-K partials
     size_t off = 0;
     auto carve = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };
     const size_t o_rowA = carve((size_t)T.M_total * 8), o_kA = carve((size_t)T.K_pad * 8), o_rowB = carve((size_t)T.N_total * 4),
                  o_kB = carve((size_t)T.K_pad * 4), o_outM = carve((size_t)T.M_total * 4),
-                 o_part = carve(splits > 1 ? out_elems * splits * sizeof(float) : 0);
+                 o_part = carve(splits > 1 ? out_total * splits * sizeof(float) : 0);
     char *ws = (char *)scratch(cx, off);
     if (!ws) return cudaErrorMemoryAllocation;
     if (!g_status[dev]) {
@@ -432,20 +462,59 @@ int run(DevCtx *cx, cudaStream_t st, int dev, int mode, const ConvGeom &g, const
     const long long entries = (long long)T.M_total + T.K_pad + T.N_total;
     build_tables_kernel<<<grid_for((size_t)entries, 256), 256, 0, st>>>(T);
     EB_LAUNCH_CHECK("conv_tc(tables)");
-    P.srcA = srcA; P.srcB = srcB; P.bias = bias;
+    P.srcA = srcA; P.srcB = srcB;
     P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM;
     P.M_total = T.M_total; P.N_total = T.N_total; P.K_pad = T.K_pad;
     P.kblocks_per_split = kbs;
     P.status = g_status[dev];
-    if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_elems; P.accumulate = 0; }
-    else { P.out = out; P.split_stride = 0; P.accumulate = (mode != 0); }
+    if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
+    else { P.out = out; P.split_stride = 0; P.accumulate = (mode != 0); P.bias = bias; }
     dim3 grid(tiles_m, tiles_n, splits);
     int r;
     const bool split3 = precision == 0;
     if (mode == 2) r = split3 ? launch_bn<true, false>(cx, st, P, grid, bn, dev) : launch_bn<false, false>(cx, st, P, grid, bn, dev);
     else r = split3 ? launch_bn<true, true>(cx, st, P, grid, bn, dev) : launch_bn<false, true>(cx, st, P, grid, bn, dev);
     if (r) return r;
-    if (splits > 1) return splitk_reduce_accumulate(cx, st, (const float *)(ws + o_part), out, out_elems, splits);
+    if (splits > 1) {
+        if (mode == 0) {
+            splitk_store_kernel<<<grid_for(out_total, 256), 256, 0, st>>>((const float *)(ws + o_part), out, out_total, splits, bias, g.oh * g.ow, g.k);
+            EB_LAUNCH_CHECK("conv_tc(split-K store)");
+            return 0;
+        }
+        return splitk_reduce_accumulate(cx, st, (const float *)(ws + o_part), out, out_total, splits);
+    }
+    return 0;
+}
+
+int run(DevCtx *cx, cudaStream_t st, int dev, int mode, const ConvGeom &g, const float *srcA, const float *srcB, float *out,
+        const float *bias, int precision) {
+    const int pq = g.oh * g.ow, hw = g.ih * g.iw, rs = g.kr * g.kc;
+    TableArgs T{};
+    T.g = g; T.mode = mode;
+    TcParams P{};
+    if (mode == 0) {
+        T.M_total = g.n * pq; T.N_total = g.k; T.K_total = g.c * rs; P.limY = g.ih; P.limX = g.iw; P.out_n_stride = pq;
+        return run_one(cx, st, dev, T, P, srcA, srcB, out, bias, precision, (size_t)g.n * g.k * pq, true);
+    }
+    if (mode == 2) {
+        T.M_total = g.c * rs; T.N_total = g.k; T.K_total = g.n * pq; P.limY = g.ih; P.limX = g.iw; P.out_n_stride = g.c * rs;
+        return run_one(cx, st, dev, T, P, srcA, srcB, out, nullptr, precision, (size_t)g.k * g.c * rs, true);
+    }
+    // backward-data: one dense problem per residue class of the strides
+    P.limY = g.oh; P.limX = g.ow; P.out_n_stride = hw; T.N_total = g.c;
+    for (int ca = 0; ca < g.sr; ca++)
+        for (int cb = 0; cb < g.sc; cb++) {
+            T.ca = ca; T.cb = cb;
+            T.y0 = ((ca - g.pt) % g.sr + g.sr) % g.sr; T.x0 = ((cb - g.pl) % g.sc + g.sc) % g.sc;
+            T.hc = T.y0 < g.ih ? (g.ih - T.y0 + g.sr - 1) / g.sr : 0;
+            T.wc = T.x0 < g.iw ? (g.iw - T.x0 + g.sc - 1) / g.sc : 0;
+            T.rt = ca < g.kr ? (g.kr - ca + g.sr - 1) / g.sr : 0;
+            T.st_ = cb < g.kc ? (g.kc - cb + g.sc - 1) / g.sc : 0;
+            T.M_total = g.n * T.hc * T.wc; T.K_total = g.k * T.rt * T.st_;
+            if (T.M_total == 0 || T.K_total == 0) continue;       // this class receives nothing
+            const bool dense = (g.sr == 1 && g.sc == 1);
+            if (int r = run_one(cx, st, dev, T, P, srcA, srcB, out, nullptr, precision, (size_t)g.n * g.c * hw, dense)) return r;
+        }
     return 0;
 }
 
@@ -465,7 +534,7 @@ int conv_tc_fwd(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, 
 }
 
 int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision) {
-    if (!fits(g) || g.sr != 1 || g.sc != 1) return 1;   // strided backward-data keeps the FMA path
+    if (!fits(g)) return 1;
     int dev = 0; cudaGetDevice(&dev);
     return run(cx, st, dev, 1, g, dy, w, dx, nullptr, precision);
 }

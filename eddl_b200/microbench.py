@@ -1,0 +1,171 @@
+"""Kernel microbenchmarks through the C ABI (CUDA-event timed, L2 flushed between timed launches).
+
+    python -m eddl_b200.microbench conv [--precision 0|1] [--batch-scale 1.0] [--iters 5]
+    python -m eddl_b200.microbench hbm
+    python -m eddl_b200.microbench allreduce          (under torchrun for N > 1)
+
+conv      forward / backward-data / backward-weight at the four Conv2D microbenchmark shapes
+          (N=64 C=K=256 56x56 3x3; N=64 C=1024 K=256 14x14 1x1; N=64 C=3 K=64 224x224 7x7 s2 p3; N=32 C=K=512 7x7 3x3),
+          TFLOP/s = 2*N*K*C*kr*kc*P*Q / time.
+hbm       BatchNorm forward/backward, ReLU forward/backward, max-pool, axpby, fused SGD at ResNet-50 sizes,
+          GB/s = algorithmic bytes / time.
+allreduce parameter averaging over NCCL for 1 KB ... 1 GB buffers: algbw = S/t, busbw = algbw * 2(N-1)/N.
+Each line of output is one JSON object.
+"""
+import argparse
+import ctypes
+import json
+import os
+import sys
+
+import numpy as np
+
+CONV_SHAPES = [  # n, c, h, w, k, kr, kc, stride, pad
+    (64, 256, 56, 56, 256, 3, 3, 1, 1),
+    (64, 1024, 14, 14, 256, 1, 1, 1, 0),
+    (64, 3, 224, 224, 64, 7, 7, 2, 3),
+    (32, 512, 7, 7, 512, 3, 3, 1, 1),
+]
+
+
+def _timed(L, dev, fn, iters, flush):
+    ms_all = []
+    for _ in range(iters):
+        if flush is not None:
+            L.call("fill", dev, flush, flush.size, 0.0)      # 256 MB write: evicts the 126 MB L2
+        L.call("timer_start", dev, 2)
+        fn()
+        L.call("timer_stop", dev, 2)
+        ms = ctypes.c_float()
+        L.call("timer_elapsed_ms", dev, 2, ctypes.byref(ms))
+        ms_all.append(ms.value)
+    return float(np.median(ms_all)), float(min(ms_all))
+
+
+def run_conv(args):
+    from . import capi
+    L = capi.lib(); dev = 0
+    L.call("init", dev)
+    flush = L.empty((64 << 20,), dev)
+    rng = np.random.default_rng(0)
+    for (n, c, h, w, k, kr, kc, st, pad) in CONV_SHAPES:
+        n = max(1, int(round(n * args.batch_scale)))
+        oh = (h + 2 * pad - kr) // st + 1; ow = (w + 2 * pad - kc) // st + 1
+        x = L.to_device(rng.standard_normal((n, c, h, w), dtype=np.float32), dev)
+        wt = L.to_device(rng.standard_normal((k, c, kr, kc), dtype=np.float32), dev)
+        dy = L.to_device(rng.standard_normal((n, k, oh, ow), dtype=np.float32), dev)
+        y, gw, dx = L.empty((n, k, oh, ow), dev), L.zeros((k, c, kr, kc), dev), L.zeros((n, c, h, w), dev)
+        geo = (n, c, h, w, k, kr, kc, oh, ow, st, st, pad, pad, args.precision)
+        flops = 2.0 * n * k * c * kr * kc * oh * ow
+        passes = {"fwd": lambda: L.call("conv2d_fwd", dev, x, wt, None, y, *geo),
+                  "bwd_data": lambda: L.call("conv2d_bwd_data", dev, dy, wt, dx, *geo),
+                  "bwd_weight": lambda: L.call("conv2d_bwd_weight", dev, x, dy, gw, None, *geo)}
+        for name, fn in passes.items():
+            if args.only and name != args.only:
+                continue
+            fn(); fn(); fn(); L.sync(dev)
+            med, best = _timed(L, dev, fn, args.iters, flush)
+            print(json.dumps({"bench": "conv", "pass": name, "shape": {"n": n, "c": c, "h": h, "w": w, "k": k, "kr": kr, "kc": kc, "stride": st, "pad": pad},
+                              "precision": "3xTF32" if args.precision == 0 else "TF32", "gflop": flops / 1e9, "ms": med, "ms_best": best,
+                              "tflops": flops / (med * 1e-3) / 1e12}), flush=True)
+        L.sync(dev)
+
+
+def run_hbm(args):
+    from . import capi
+    L = capi.lib(); dev = 0
+    L.call("init", dev)
+    flush = L.empty((64 << 20,), dev)
+    rng = np.random.default_rng(0)
+    peak = 6541.5
+    p = os.path.join(capi.ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        peak = json.load(open(p))["hbm_gbs"]
+
+    def report(name, shape, nbytes, fn):
+        fn(); fn(); fn(); L.sync(dev)
+        med, best = _timed(L, dev, fn, args.iters, flush)
+        gbs = nbytes / (med * 1e-3) / 1e9
+        print(json.dumps({"bench": "hbm", "kernel": name, "shape": shape, "bytes": nbytes, "ms": med, "GB/s": gbs, "frac_of_measured_hbm": gbs / peak}), flush=True)
+
+    for (b, z, hw) in [(64, 64, 112), (64, 256, 56), (64, 512, 28), (64, 1024, 14), (64, 2048, 7)]:
+        rc = hw * hw; E = b * z * rc
+        x = L.to_device(rng.standard_normal((b, z, hw, hw), dtype=np.float32), dev)
+        y, opa, d, pd, r = L.empty(x.shape, dev), L.empty(x.shape, dev), L.to_device(rng.standard_normal(x.shape, dtype=np.float32), dev), L.zeros(x.shape, dev), L.empty(x.shape, dev)
+        g, bt, gm, gv, mean, var = (L.to_device(np.ones(z, np.float32), dev), L.zeros((z,), dev), L.zeros((z,), dev), L.zeros((z,), dev), L.zeros((z,), dev), L.zeros((z,), dev))
+        gg, gb, m1, m2 = L.zeros((z,), dev), L.zeros((z,), dev), L.zeros((z,), dev), L.zeros((z,), dev)
+        shape = [b, z, hw, hw]
+        report("bn_fwd", shape, 16 * E, lambda: L.call("bn_fwd", dev, b, z, rc, x, y, opa, gm, gv, g, bt, mean, var, 1, 1e-3, 0.99, None))
+        report("bn_relu_fwd_fused", shape, 16 * E, lambda: L.call("bn_fwd", dev, b, z, rc, x, y, opa, gm, gv, g, bt, mean, var, 1, 1e-3, 0.99, r))
+        report("bn_bwd", shape, 24 * E, lambda: L.call("bn_bwd", dev, b, z, rc, d, opa, pd, gg, gb, g, var, m1, m2))
+        report("relu_fwd", shape, 8 * E, lambda: L.call("relu_fwd", dev, x, y, E))
+        report("relu_bwd", shape, 16 * E, lambda: L.call("relu_bwd", dev, d, x, pd, E))
+        report("axpby_inc", shape, 16 * E, lambda: L.call("axpby", dev, 1.0, x, 1.0, d, pd, 1, E))
+        report("fill", shape, 4 * E, lambda: L.call("fill", dev, pd, E, 0.0))
+    # max-pool 3x3 s2 p1 on 64x64x112x112 (ResNet stem) and 2x2 s2 on 128x64x32x32 (VGG)
+    for (n, c, ih, k, s, pad) in [(64, 64, 112, 3, 2, 1), (128, 64, 32, 2, 2, 0)]:
+        oh = (ih + 2 * pad - k) // s + 1
+        x = L.to_device(rng.standard_normal((n, c, ih, ih), dtype=np.float32), dev)
+        y, ix, iy = L.empty((n, c, oh, oh), dev), L.empty((n, c, oh, oh), dev), L.empty((n, c, oh, oh), dev)
+        d, dx = L.to_device(rng.standard_normal((n, c, oh, oh), dtype=np.float32), dev), L.zeros((n, c, ih, ih), dev)
+        geo = (n, c, ih, ih, oh, oh, k, k, s, s, pad, pad)
+        Ein, Eout = n * c * ih * ih, n * c * oh * oh
+        report("maxpool_fwd", [n, c, ih, ih, k, s], 4 * Ein + 12 * Eout, lambda: L.call("maxpool2d_fwd", dev, x, y, ix, iy, *geo))
+        report("maxpool_bwd", [n, c, ih, ih, k, s], 12 * Eout + 8 * Ein, lambda: L.call("maxpool2d_bwd", dev, d, ix, iy, dx, *geo))
+    # fused SGD over a ResNet-50 sized parameter set (25.6 M floats in one tensor)
+    nparam = 25636712
+    p_, g_, m_ = L.zeros((nparam,), dev), L.zeros((nparam,), dev), L.zeros((nparam,), dev)
+    report("sgd_momentum", [nparam], 20 * nparam, lambda: L.call("sgd_momentum", dev, p_, g_, m_, 0.1, 0.9, nparam))
+
+
+def run_allreduce(args):
+    import torch  # noqa: F401  first: the process-wide libnccl.so.2 must be the one torch was built against
+    from . import capi, dist as ebd
+    rank, world, local = ebd.rendezvous("gloo")
+    L = capi.lib()
+    L.call("init", local)
+    if world > 1:
+        def make_id():
+            buf = ctypes.create_string_buffer(128); L.call("comm_unique_id", buf); return buf.raw
+        uid = ebd.share_unique_id(make_id)
+        L.call("comm_init_rank", local, world, rank, uid)
+    size = 256
+    while size <= (1 << 28):
+        rng = np.random.default_rng(1234 + rank)
+        host = rng.standard_normal(size, dtype=np.float32)
+        buf = L.to_device(host, local)
+        p_, m_ = L.zeros((size,), local), L.zeros((size,), local)
+        for mode, fn in (("weight_avg", lambda: L.call("allreduce_avg", local, buf, size)),
+                         ("grad_avg_sgd", lambda: L.call("avg_grad_sgd", local, p_, buf, m_, 0.1, 0.9, size))):
+            for _ in range(3):
+                fn()
+            L.sync(local); ebd.barrier()
+            iters = 20 if size <= (1 << 22) else 5
+            L.call("timer_start", local, 3)
+            for _ in range(iters):
+                fn()
+            L.call("timer_stop", local, 3)
+            ms = ctypes.c_float(); L.call("timer_elapsed_ms", local, 3, ctypes.byref(ms))
+            t = ebd.max_over_ranks(ms.value / iters) * 1e-3
+            if rank == 0:
+                alg = size * 4 / t / 1e9
+                print(json.dumps({"bench": "allreduce", "mode": mode, "ranks": world, "bytes": size * 4, "us": t * 1e6, "algbw_GB/s": alg,
+                                  "busbw_GB/s": alg * 2 * (world - 1) / world if world > 1 else 0.0}), flush=True)
+        size *= 4
+    if world > 1:
+        L.call("comm_destroy", local)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["conv", "hbm", "allreduce"])
+    ap.add_argument("--precision", type=int, default=0)
+    ap.add_argument("--batch-scale", type=float, default=1.0)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--only", default=None)
+    args = ap.parse_args()
+    {"conv": run_conv, "hbm": run_hbm, "allreduce": run_allreduce}[args.what](args)
+
+
+if __name__ == "__main__":
+    main()

@@ -51,13 +51,16 @@ def test_small_cnn_trajectory_matches_reference_fixture(gpu_lib, refout):
 
 
 @pytest.mark.parametrize("opt", ["sgd", "sgd_fused"])
-@pytest.mark.parametrize("cfg,hw,classes,batch,steps,mode", [("vgg16bn", 32, 10, 16, 3, "he"), ("resnet50", 64, 100, 8, 2, "he")])
+@pytest.mark.parametrize("cfg,hw,classes,batch,steps,mode", [("vgg16bn", 32, 10, 16, 3, "he"), ("resnet50", 64, 100, 8, 3, "he"), ("resnet50", 224, 1000, 2, 2, "he")])
 def test_bn_nets_match_live_reference(gpu_lib, ref, cfg, hw, classes, batch, steps, mode, opt):
     if ref is None:
         pytest.skip("oracle/_ref not built")
     os.environ["OMP_NUM_THREADS"] = "1"
-    cpu = harness.NetHarness(ref.lib(), cfg, device=-1, hw=hw, classes=classes, threads=1, optimizer="sgd", lr=0.01, mu=0.9)
-    gpu = harness.NetHarness(gpu_lib, cfg, device=0, hw=hw, classes=classes, optimizer=opt, lr=0.01, mu=0.9)
+    # A small learning rate keeps each update a small perturbation: with lr 0.01 the first update of these randomly
+    # initialised nets changes the loss by 50-90%, and a handful of ReLU / max-pool decisions that flip on 1e-7
+    # differences of the forward pass (different fp32 summation orders) then move the next loss by several 1e-4.
+    cpu = harness.NetHarness(ref.lib(), cfg, device=-1, hw=hw, classes=classes, threads=1, optimizer="sgd", lr=1e-3, mu=0.9)
+    gpu = harness.NetHarness(gpu_lib, cfg, device=0, hw=hw, classes=classes, optimizer=opt, lr=1e-3, mu=0.9)
     # layer names carry process-wide counters; shapes and order must agree
     assert cpu.nfloats == gpu.nfloats and [s for _, s in cpu.param_info()] == [s for _, s in gpu.param_info()]
     w0 = harness.init_weights(cpu.param_info(), seed=99, mode="he_normal")
@@ -69,8 +72,8 @@ def test_bn_nets_match_live_reference(gpu_lib, ref, cfg, hw, classes, batch, ste
         lg, ag = gpu.train_batch(x, y)
         assert abs(lg - lc) <= 1e-4 * abs(lc), (s, lg, lc)
     pc, pg = cpu.get_params(), gpu.get_params()
-    # parameters (BatchNorm running statistics included) after `steps` updates
-    assert np.max(np.abs(pc - pg)) <= 1e-3 * np.max(np.abs(pc))
+    # parameters (BatchNorm running statistics included) after `steps` updates, in the L2 sense
+    assert np.linalg.norm(pc.astype(np.float64) - pg) <= 1e-4 * np.linalg.norm(pc.astype(np.float64))
     cpu.close(); gpu.close()
 
 

@@ -13,6 +13,7 @@
 //           the backward formula.  Block y == 0 also writes the per-channel outputs.
 // Algorithmic traffic: forward 16 B/element (x twice, opa, y), backward 24 B/element
 // (+4 for the in-place `delta *= gamma` the reference performs).
+#include <mutex>
 #include "common.cuh"
 
 namespace {
@@ -278,3 +279,84 @@ int eddlb200_bn_bwd(int dev, int b, int z, int rc, float *delta, const float *op
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// BatchNorm forward for callers that are not allowed to allocate device memory.
+//
+// eddlb200_bn_fwd keeps its per-channel partial sums in the library's growable scratch arena,
+// which it obtains with cudaMalloc the first time (and whenever a larger one is needed), and the
+// device context behind it also allocates on first use.  Some hosts cannot tolerate that: a
+// process whose device memory has been handed over in full to another allocator (a cudaMalloc
+// from a plug-in then fails or fragments that pool), or a latency-critical loop in which the
+// implicit device synchronisation of cudaMalloc / cudaFree is not acceptable.  For them this
+// entry point runs the same two kernels with the partial sums in a fixed array that is part of
+// the library image: kNoAllocPairs (sum, sum-of-squares) pairs = 2 MiB of device memory, held by
+// every GPU that loads the library until the process exits.
+//
+// * It calls no cudaMalloc / cudaFree / cudaMallocHost and does not create the library's device
+//   context; the caller supplies the stream.
+// * The array's name is only a host-side handle.  Its device address is looked up once per
+//   device with cudaGetSymbolAddress while that device is current; this happens inside the FIRST
+//   call on each device, so make that first call before any stream capture begins.
+// * Shapes that need more than kNoAllocPairs partial pairs (channels x slices) are rejected with
+//   EDDLB200_ELIMIT.
+// * All calls on a device share the one array and it keeps whatever the last call left there.
+//   Nothing has to be cleared between calls: the statistics kernel overwrites every pair the
+//   apply kernel reads.  Two calls that overlap on the GPU (different streams, no ordering) race
+//   on the array and give wrong statistics; order them.
+namespace {
+
+constexpr unsigned kNoAllocPairs = 4096u * kMaxSplit;     // 262144 float2 = 2 MiB
+static __device__ __align__(256) float2 g_noalloc_partials[kNoAllocPairs];
+
+float2 *g_noalloc_addr[EDDLB200_MAX_DEVICES] = {};
+std::mutex g_noalloc_mu;
+
+// Device address of g_noalloc_partials on `dev` (which must be current); nullptr + error text on failure.
+float2 *noalloc_scratch(int dev) {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_addr[dev]) return g_noalloc_addr[dev];
+    void *p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_partials);
+    if (e != cudaSuccess || !p) {
+        cuda_status(e == cudaSuccess ? cudaErrorInvalidSymbol : e, "eddlb200_bn_fwd_noalloc(cudaGetSymbolAddress)");
+        return nullptr;
+    }
+    g_noalloc_addr[dev] = (float2 *)p;
+    return g_noalloc_addr[dev];
+}
+
+}  // namespace
+
+extern "C" int eddlb200_bn_fwd_noalloc(int dev, int b, int z, int rc, const float *input, float *output, float *opa,
+                                       float *global_mean, float *global_variance, const float *affine_g, const float *affine_b,
+                                       float *mean, float *variance, int trmode, float epsilon, float momentum, float *relu_out,
+                                       void *cuda_stream) {
+    if (dev < 0 || dev >= EDDLB200_MAX_DEVICES) return set_error(EDDLB200_ENOINIT, "bn_fwd_noalloc: device ordinal %d out of range", dev);
+    if (!(b > 0 && z > 0 && rc > 0 && input && output && global_mean && global_variance && variance) ||
+        (affine_g && !(affine_b && opa)) || (trmode && !mean) || (size_t)b * rc >= 0xfffffff0u)
+        return set_error(EDDLB200_EINVAL, "bn_fwd_noalloc: bad argument");
+    const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
+    if ((size_t)z * S > kNoAllocPairs)
+        return set_error(EDDLB200_ELIMIT, "bn_fwd_noalloc: %d channels x %u slices need %zu partial pairs, the built-in scratch holds %u",
+                         z, S, (size_t)z * S, kNoAllocPairs);
+    cudaError_t e = cudaSetDevice(dev);
+    if (e != cudaSuccess) return cuda_status(e, "bn_fwd_noalloc(cudaSetDevice)");
+    float2 *partial = noalloc_scratch(dev);
+    if (!partial) return EDDLB200_ENOINIT;
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const bool vec = (rc % 4 == 0) && aligned16(input) && aligned16(output) && (!opa || aligned16(opa)) && (!relu_out || aligned16(relu_out));
+    dim3 grid(z, S);
+    if (trmode) {
+        if (vec) bn_stats_kernel<0, true><<<grid, kBlock, 0, st>>>(input, nullptr, partial, b, z, rc);
+        else bn_stats_kernel<0, false><<<grid, kBlock, 0, st>>>(input, nullptr, partial, b, z, rc);
+        if ((e = cudaGetLastError()) != cudaSuccess) return cuda_status(e, "bn_fwd_noalloc(stats)");
+        if (vec) bn_fwd_apply_kernel<true, true><<<grid, kBlock, 0, st>>>(input, output, opa, relu_out, partial, global_mean, global_variance, affine_g, affine_b, mean, variance, b, z, rc, epsilon, momentum);
+        else bn_fwd_apply_kernel<true, false><<<grid, kBlock, 0, st>>>(input, output, opa, relu_out, partial, global_mean, global_variance, affine_g, affine_b, mean, variance, b, z, rc, epsilon, momentum);
+    } else {
+        if (vec) bn_fwd_apply_kernel<false, true><<<grid, kBlock, 0, st>>>(input, output, opa, relu_out, nullptr, global_mean, global_variance, affine_g, affine_b, mean, variance, b, z, rc, epsilon, momentum);
+        else bn_fwd_apply_kernel<false, false><<<grid, kBlock, 0, st>>>(input, output, opa, relu_out, nullptr, global_mean, global_variance, affine_g, affine_b, mean, variance, b, z, rc, epsilon, momentum);
+    }
+    if ((e = cudaGetLastError()) != cudaSuccess) return cuda_status(e, "bn_fwd_noalloc(apply)");
+    return 0;
+}

@@ -114,6 +114,24 @@ int eddlb200_bn_fwd(int dev, int b, int z, int rc,
                     const float *affine_g, const float *affine_b,
                     float *mean, float *variance,
                     int trmode, float epsilon, float momentum, float *relu_out);
+/* Same operation as eddlb200_bn_fwd for callers that must not allocate device memory.  It has no
+ * counterpart in EDDL.  It performs no cudaMalloc / cudaFree (neither directly nor through the library's
+ * device context, which it does not create): the per-channel partial sums live in a fixed 2 MiB array
+ * inside the library image, and the work is enqueued on the caller's `cuda_stream` (a cudaStream_t; null is
+ * the default stream).  Intended for hosts whose device memory is wholly owned by another allocator, or
+ * that cannot accept the device-wide synchronisation cudaMalloc / cudaFree imply.  Limits and rules:
+ *   - channels x slices must not exceed 262144 (slices <= 64 per channel, chosen from the shape; any
+ *     z <= 4096 fits); larger shapes return EDDLB200_ELIMIT;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress): make
+ *     that call before any stream capture starts;
+ *   - all calls on a device share the array; calls that overlap on the GPU race on it, so order them.
+ * Results are identical to eddlb200_bn_fwd (same kernels, same slicing). */
+int eddlb200_bn_fwd_noalloc(int dev, int b, int z, int rc,
+                            const float *input, float *output, float *opa,
+                            float *global_mean, float *global_variance,
+                            const float *affine_g, const float *affine_b,
+                            float *mean, float *variance,
+                            int trmode, float epsilon, float momentum, float *relu_out, void *cuda_stream);
 /* gbn_g += mean(delta*opa); gbn_b += mean(delta)  (means, not sums);
  * delta *= bn_g in place; pdelta += (delta - (opa*m1 + m2)) / variance. */
 int eddlb200_bn_bwd(int dev, int b, int z, int rc,

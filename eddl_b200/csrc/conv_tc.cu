@@ -191,70 +191,89 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
 
     if (warp < 8) {
         // ============================ producers ============================
+        // Software pipeline: the global loads of K-block it+1 are issued into registers right after the
+        // stores of K-block it, so their latency overlaps the MMAs and the wait for a free stage.
+        constexpr int RB = BN_ / 8;              // B rows per warp
+        float av[16], bv[RB];
+        const int arow = tid & (BM - 1), ahalf = tid >> 7;
         int2 myRow = make_int2(0, 0);
-        if (A_ROWMAJOR) myRow = sRowA[tid & (BM - 1)];
-        for (int it = 0; it < nkb; it++) {
-            const int s = it % STAGES;
-            const uint32_t par = ((it / STAGES) & 1) ^ 1;
-            if (!mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
-            uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
-            uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
-            uint8_t *sB_hi = sA_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
-            uint8_t *sB_lo = sB_hi + L::B_BYTES;
+        if (A_ROWMAJOR) myRow = sRowA[arow];
+        const int ry = myRow.y >> 16, rx = (int)(short)(myRow.y & 0xffff);
+
+        auto load_tiles = [&](int it) {
             const int kbase = (kb_begin + it) * BK;
-            // ---- A tile: 128 rows x 32 k ----
             if (A_ROWMAJOR) {
-                const int row = tid & (BM - 1), half = tid >> 7;
-                const int ry = myRow.y >> 16, rx = (int)(short)(myRow.y & 0xffff);
                 const float *base = P.srcA + myRow.x;
 #pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    float v[4];
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const int2 ke = __ldg(P.kA + kbase + half * 16 + g * 4 + u);
-                        const int y = ry + (ke.y >> 16), x = rx + (int)(short)(ke.y & 0xffff);
-                        const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
-                        v[u] = ok ? __ldg(base + ke.x) : 0.f;
-                    }
-                    float4 hi, lo;
-                    split_tf32(v[0], hi.x, lo.x); split_tf32(v[1], hi.y, lo.y); split_tf32(v[2], hi.z, lo.z); split_tf32(v[3], hi.w, lo.w);
-                    const uint32_t off = swz(row, half * 16 + g * 4);
-                    if (SPLIT3) { *(float4 *)(sA_hi + off) = hi; *(float4 *)(sA_lo + off) = lo; }
-                    else *(float4 *)(sA_hi + off) = make_float4(v[0], v[1], v[2], v[3]);
+                for (int i = 0; i < 16; i++) {
+                    const int2 ke = __ldg(P.kA + kbase + ahalf * 16 + i);
+                    const int y = ry + (ke.y >> 16), x = rx + (int)(short)(ke.y & 0xffff);
+                    const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
+                    av[i] = ok ? __ldg(base + ke.x) : 0.f;
                 }
             } else {
                 const int2 ke = __ldg(P.kA + kbase + lane);
                 const int ky = ke.y >> 16, kx = (int)(short)(ke.y & 0xffff);
                 const float *base = P.srcA + ke.x;
-#pragma unroll 4
-                for (int r = 0; r < BM / 8; r++) {
-                    const int row = warp * (BM / 8) + r;
-                    const int2 re = sRowA[row];
+#pragma unroll
+                for (int r = 0; r < 16; r++) {
+                    const int2 re = sRowA[warp * 16 + r];
                     const int y = (re.y >> 16) + ky, x = (int)(short)(re.y & 0xffff) + kx;
                     const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
-                    const float v = ok ? __ldg(base + re.x) : 0.f;
-                    const uint32_t off = swz(row, lane);
-                    if (SPLIT3) { float hi, lo; split_tf32(v, hi, lo); *(float *)(sA_hi + off) = hi; *(float *)(sA_lo + off) = lo; }
-                    else *(float *)(sA_hi + off) = v;
+                    av[r] = ok ? __ldg(base + re.x) : 0.f;
                 }
             }
-            // ---- B tile: BN rows x 32 k, one lane per k ----
-            {
-                const int kb = __ldg(P.kB + kbase + lane);
-                const float *base = P.srcB + (kb < 0 ? 0 : kb);
-#pragma unroll 4
-                for (int r = 0; r < BN_ / 8; r++) {
-                    const int row = warp * (BN_ / 8) + r;
-                    const int ro = sRowB[row];
-                    const float v = (kb >= 0 && ro >= 0) ? __ldg(base + ro) : 0.f;
-                    const uint32_t off = swz(row, lane);
-                    if (SPLIT3) { float hi, lo; split_tf32(v, hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
-                    else *(float *)(sB_hi + off) = v;
+            const int kb = __ldg(P.kB + kbase + lane);
+            const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
+#pragma unroll
+            for (int r = 0; r < RB; r++) {
+                const int ro = sRowB[warp * RB + r];
+                bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
+            }
+        };
+        auto store_tiles = [&](int s) {
+            uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
+            uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
+            uint8_t *sB_hi = sA_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
+            uint8_t *sB_lo = sB_hi + L::B_BYTES;
+            if (A_ROWMAJOR) {
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const uint32_t off = swz(arow, ahalf * 16 + g * 4);
+                    if (SPLIT3) {
+                        float4 hi, lo;
+                        split_tf32(av[4 * g + 0], hi.x, lo.x); split_tf32(av[4 * g + 1], hi.y, lo.y);
+                        split_tf32(av[4 * g + 2], hi.z, lo.z); split_tf32(av[4 * g + 3], hi.w, lo.w);
+                        *(float4 *)(sA_hi + off) = hi; *(float4 *)(sA_lo + off) = lo;
+                    } else {
+                        *(float4 *)(sA_hi + off) = make_float4(av[4 * g], av[4 * g + 1], av[4 * g + 2], av[4 * g + 3]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < 16; r++) {
+                    const uint32_t off = swz(warp * 16 + r, lane);
+                    if (SPLIT3) { float hi, lo; split_tf32(av[r], hi, lo); *(float *)(sA_hi + off) = hi; *(float *)(sA_lo + off) = lo; }
+                    else *(float *)(sA_hi + off) = av[r];
                 }
             }
+#pragma unroll
+            for (int r = 0; r < RB; r++) {
+                const uint32_t off = swz(warp * RB + r, lane);
+                if (SPLIT3) { float hi, lo; split_tf32(bv[r], hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
+                else *(float *)(sB_hi + off) = bv[r];
+            }
+        };
+
+        if (nkb > 0) load_tiles(0);
+        for (int it = 0; it < nkb; it++) {
+            const int s = it % STAGES;
+            const uint32_t par = ((it / STAGES) & 1) ^ 1;
+            if (!mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+            store_tiles(s);
             fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
             mbar_arrive(bar_full + 8 * s);
+            if (it + 1 < nkb) load_tiles(it + 1);
         }
     } else if (lane == 0) {
         // ============================ MMA issuer (one thread) ============================

@@ -135,6 +135,23 @@ def run_allreduce(args):
         host = rng.standard_normal(size, dtype=np.float32)
         buf = L.to_device(host, local)
         p_, m_ = L.zeros((size,), local), L.zeros((size,), local)
+        if size <= (1 << 24):
+            # correctness: every rank can regenerate every rank's buffer; the result must equal the fp32
+            # rank-order sum times 1.0f/N (the arithmetic of Net::sync_weights) within rel 1e-6
+            reps = [np.random.default_rng(1234 + r).standard_normal(size, dtype=np.float32) for r in range(world)]
+            want = ebd.average_replicas_host(reps)
+            chk = L.to_device(host, local)
+            L.call("allreduce_avg", local, chk, size)
+            got = chk.numpy()
+            err = float(np.max(np.abs(got - want)) / max(float(np.max(np.abs(want))), 1e-30))
+            pc, gc, mc = L.to_device(reps[0] * 0 + 1.0, local), L.to_device(host, local), L.zeros((size,), local)
+            L.call("avg_grad_sgd", local, pc, gc, mc, 0.1, 0.9, size)
+            m_want = (np.float32(0.1) * want).astype(np.float32)
+            err2 = float(np.max(np.abs(pc.numpy() - (np.float32(1.0) - m_want))) )
+            worst = ebd.max_over_ranks(max(err, err2))
+            if rank == 0:
+                print(json.dumps({"bench": "allreduce_check", "ranks": world, "floats": size, "max_rel_err_weight_avg": err,
+                                  "max_abs_err_fused_sgd": err2, "worst_over_ranks": worst, "ok": bool(worst <= 1e-6)}), flush=True)
         for mode, fn in (("weight_avg", lambda: L.call("allreduce_avg", local, buf, size)),
                          ("grad_avg_sgd", lambda: L.call("avg_grad_sgd", local, p_, buf, m_, 0.1, 0.9, size))):
             for _ in range(3):

@@ -229,7 +229,7 @@ def run_b200_arm(args):
                 "flops_per_step": conv_fl / args.steps, "traffic": None,
                 "share_of_step": conv_ms / (ms.value if ms.value else 1.0)}
     hbm = {}
-    for nm in ("bn_fwd", "bn_bwd", "optimizer"):
+    for nm in ("bn_fwd", "bn_bwd", "elementwise", "pool", "optimizer"):
         c, t, w = prof[nm]
         if t > 0:
             hbm[nm] = {"GB/s": w / (t * 1e-3) / 1e9, "frac_of_%s_hbm" % peak_src: w / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], "calls": c,
@@ -248,6 +248,7 @@ def run_b200_arm(args):
             "e2e": {"value": imgs / e2e_s, "unit": "img/s", "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 16,
                     "ms_per_step": 1e3 * e2e_s / args.steps},
             "gpu_launches": int(launches), "roofline": roofline, "hbm_kernels": hbm,
+            "breakdown_ms_per_step": {k: round(v[1] / args.steps, 3) for k, v in prof.items()},
             "loss": {"after_warmup": loss0 if args.warmup else None, "e2e_last": loss_e2e, "resident_last_sum": loss_res}}
     if cpu is not None:
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}

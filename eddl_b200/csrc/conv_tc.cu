@@ -60,6 +60,7 @@ struct TcParams {
     int kblocks_per_split;
     long long split_stride; // elements between the partial outputs of consecutive splits
     int accumulate;
+    int nmain;              // rotating hi*hi accumulators in use: 1 for short chains, NMAIN otherwise
     int *status;
 };
 
@@ -148,7 +149,8 @@ struct Layout {
 
 // A_ROWMAJOR: consecutive rows of A are consecutive in memory (pixels) -> one thread per row, vector stores;
 // otherwise consecutive k are consecutive in memory -> one lane per k.
-template <int BN_, bool SPLIT3, bool A_ROWMAJOR>
+// B_ROWMAJOR: the same choice for B (backward-data: consecutive in-channels of w[f][c][r][s] are rs floats apart).
+template <int BN_, bool SPLIT3, bool A_ROWMAJOR, bool B_ROWMAJOR>
 __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P) {
     using L = Layout<BN_, SPLIT3>;
     constexpr int STAGES = L::STAGES;
@@ -199,6 +201,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
         int2 myRow = make_int2(0, 0);
         if (A_ROWMAJOR) myRow = sRowA[arow];
         const int ry = myRow.y >> 16, rx = (int)(short)(myRow.y & 0xffff);
+        const int brow = tid % BN_, bgrp = tid / BN_;        // B_ROWMAJOR: one thread per (row, group of RB consecutive k)
+        const int myRowB = B_ROWMAJOR ? sRowB[brow] : 0;
 
         auto load_tiles = [&](int it) {
             const int kbase = (kb_begin + it) * BK;
@@ -223,12 +227,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     av[r] = ok ? __ldg(base + re.x) : 0.f;
                 }
             }
-            const int kb = __ldg(P.kB + kbase + lane);
-            const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
+            if (B_ROWMAJOR) {
+                const float *bbase = P.srcB + (myRowB < 0 ? 0 : myRowB);
 #pragma unroll
-            for (int r = 0; r < RB; r++) {
-                const int ro = sRowB[warp * RB + r];
-                bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
+                for (int i = 0; i < RB; i++) {
+                    const int kb = __ldg(P.kB + kbase + bgrp * RB + i);
+                    bv[i] = (kb >= 0 && myRowB >= 0) ? __ldg(bbase + kb) : 0.f;
+                }
+            } else {
+                const int kb = __ldg(P.kB + kbase + lane);
+                const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
+#pragma unroll
+                for (int r = 0; r < RB; r++) {
+                    const int ro = sRowB[warp * RB + r];
+                    bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
+                }
             }
         };
         auto store_tiles = [&](int s) {
@@ -257,11 +270,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     else *(float *)(sA_hi + off) = av[r];
                 }
             }
+            if (B_ROWMAJOR) {
 #pragma unroll
-            for (int r = 0; r < RB; r++) {
-                const uint32_t off = swz(warp * RB + r, lane);
-                if (SPLIT3) { float hi, lo; split_tf32(bv[r], hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
-                else *(float *)(sB_hi + off) = bv[r];
+                for (int g = 0; g < RB / 4; g++) {
+                    const uint32_t off = swz(brow, bgrp * RB + g * 4);
+                    if (SPLIT3) {
+                        float4 hi, lo;
+                        split_tf32(bv[4 * g + 0], hi.x, lo.x); split_tf32(bv[4 * g + 1], hi.y, lo.y);
+                        split_tf32(bv[4 * g + 2], hi.z, lo.z); split_tf32(bv[4 * g + 3], hi.w, lo.w);
+                        *(float4 *)(sB_hi + off) = hi; *(float4 *)(sB_lo + off) = lo;
+                    } else {
+                        *(float4 *)(sB_hi + off) = make_float4(bv[4 * g], bv[4 * g + 1], bv[4 * g + 2], bv[4 * g + 3]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < RB; r++) {
+                    const uint32_t off = swz(warp * RB + r, lane);
+                    if (SPLIT3) { float hi, lo; split_tf32(bv[r], hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
+                    else *(float *)(sB_hi + off) = bv[r];
+                }
             }
         };
 
@@ -290,13 +318,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             for (int ks = 0; ks < BK / 8; ks++) {
                 const uint32_t o = ks * 32;      // 8 fp32 = 32 bytes along K inside the swizzle row
                 const int step = it * (BK / 8) + ks;
-                const uint32_t d_main = tmem_base + (uint32_t)((step % NMAIN) * BN_);
+                const uint32_t d_main = tmem_base + (uint32_t)((step % P.nmain) * BN_);
                 if (SPLIT3) {
                     const uint32_t d_small = tmem_base + (uint32_t)(NMAIN * BN_);
                     umma_tf32(d_small, make_desc(a_lo + o), make_desc(b_hi + o), idesc, step > 0 ? 1u : 0u);
                     umma_tf32(d_small, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
                 }
-                umma_tf32(d_main, make_desc(a_hi + o), make_desc(b_hi + o), idesc, step >= NMAIN ? 1u : 0u);
+                umma_tf32(d_main, make_desc(a_hi + o), make_desc(b_hi + o), idesc, step >= P.nmain ? 1u : 0u);
             }
             umma_commit(bar_empty + 8 * s);      // frees the stage when these MMAs have read it
         }
@@ -317,23 +345,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 uint32_t r[32], t[32];
                 const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32);
                 tmem_ld32(lane_base, r);
-                // nkb >= 1 gives at least four k-steps, so all three rotating accumulators hold data
+                // nkb >= 1 gives at least four k-steps, so every rotating accumulator in use holds data;
+                // accumulator NMAIN holds the cross terms of the 3xTF32 split
 #pragma unroll 1
-                for (int a = 1; a < (SPLIT3 ? NMAIN + 1 : NMAIN); a++) {
+                for (int a = 1; a <= NMAIN; a++) {
+                    if (a >= P.nmain && !(SPLIT3 && a == NMAIN)) continue;
                     tmem_ld32(lane_base + (uint32_t)(a * BN_), t);
 #pragma unroll
                     for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(t[j])));
                 }
                 if (m_ok) {
+                    float *col0 = obase + (long long)(n0 + c * 32) * P.out_n_stride;
+                    if (P.accumulate) {
+                        // read-modify-write: issue all 32 loads before the first store so they overlap
+                        float prev[32];
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int n = n0 + c * 32 + j;
-                        if (n < P.N_total) {
-                            float v = __uint_as_float(r[j]);
-                            if (P.bias) v = __fadd_rn(v, __ldg(P.bias + n));
-                            float *dst = obase + (long long)n * P.out_n_stride;
-                            if (P.accumulate) v = __fadd_rn(*dst, v);
-                            *dst = v;
+                        for (int j = 0; j < 32; j++)
+                            prev[j] = (n0 + c * 32 + j < P.N_total) ? __ldcg(col0 + (long long)j * P.out_n_stride) : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (n0 + c * 32 + j < P.N_total) col0[(long long)j * P.out_n_stride] = __fadd_rn(prev[j], __uint_as_float(r[j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int n = n0 + c * 32 + j;
+                            if (n < P.N_total) {
+                                float v = __uint_as_float(r[j]);
+                                if (P.bias) v = __fadd_rn(v, __ldg(P.bias + n));
+                                col0[(long long)j * P.out_n_stride] = v;
+                            }
                         }
                     }
                 }
@@ -409,26 +449,26 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
     }
 }
 
-template <int BN_, bool SPLIT3, bool A_ROWMAJOR>
+template <int BN_, bool SPLIT3, bool A_ROWMAJOR, bool B_ROWMAJOR>
 int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
     using L = Layout<BN_, SPLIT3>;
     static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
     bool &configured = configured_dev[dev];
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, SPLIT3, A_ROWMAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, SPLIT3, A_ROWMAJOR, B_ROWMAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e, "conv_tc(smem attribute)");
         configured = true;
     }
-    igemm_tc_kernel<BN_, SPLIT3, A_ROWMAJOR><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
+    igemm_tc_kernel<BN_, SPLIT3, A_ROWMAJOR, B_ROWMAJOR><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
     EB_LAUNCH_CHECK("conv_tc");
     return 0;
 }
 
-template <bool SPLIT3, bool A_ROWMAJOR>
+template <bool SPLIT3, bool A_ROWMAJOR, bool B_ROWMAJOR>
 int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn, int dev) {
-    if (bn == 32) return launch_variant<32, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
-    if (bn == 64) return launch_variant<64, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
-    return launch_variant<128, SPLIT3, A_ROWMAJOR>(cx, st, P, grid, dev);
+    if (bn == 32) return launch_variant<32, SPLIT3, A_ROWMAJOR, B_ROWMAJOR>(cx, st, P, grid, dev);
+    if (bn == 64) return launch_variant<64, SPLIT3, A_ROWMAJOR, B_ROWMAJOR>(cx, st, P, grid, dev);
+    return launch_variant<128, SPLIT3, A_ROWMAJOR, B_ROWMAJOR>(cx, st, P, grid, dev);
 }
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
@@ -485,14 +525,17 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM;
     P.M_total = T.M_total; P.N_total = T.N_total; P.K_pad = T.K_pad;
     P.kblocks_per_split = kbs;
+    // a single accumulator drifts by ~2.5e-6 at 64 k-steps (K = 512); longer chains rotate over three
+    P.nmain = (kbs * (BK / 8) > 64) ? NMAIN : 1;
     P.status = g_status[dev];
     if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
     else { P.out = out; P.split_stride = 0; P.accumulate = (mode != 0); P.bias = bias; }
     dim3 grid(tiles_m, tiles_n, splits);
     int r;
     const bool split3 = precision == 0;
-    if (mode == 2) r = split3 ? launch_bn<true, false>(cx, st, P, grid, bn, dev) : launch_bn<false, false>(cx, st, P, grid, bn, dev);
-    else r = split3 ? launch_bn<true, true>(cx, st, P, grid, bn, dev) : launch_bn<false, true>(cx, st, P, grid, bn, dev);
+    if (mode == 2) r = split3 ? launch_bn<true, false, false>(cx, st, P, grid, bn, dev) : launch_bn<false, false, false>(cx, st, P, grid, bn, dev);
+    else if (mode == 1) r = split3 ? launch_bn<true, true, true>(cx, st, P, grid, bn, dev) : launch_bn<false, true, true>(cx, st, P, grid, bn, dev);
+    else r = split3 ? launch_bn<true, true, false>(cx, st, P, grid, bn, dev) : launch_bn<false, true, false>(cx, st, P, grid, bn, dev);
     if (r) return r;
     if (splits > 1) {
         if (mode == 0) {

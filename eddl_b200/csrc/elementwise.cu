@@ -57,6 +57,7 @@ template <typename F>
 int launch1(DevCtx *cx, cudaStream_t st, const float *a, float *b, size_t n, F f, const char *what) {
     if (n == 0) return 0;
     if (!a || !b) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
+    ProfScope prof(cx, PROF_ELEMENTWISE, 8.0 * n);
     if (aligned16(a) && aligned16(b)) {
         size_t n4 = n / 4;
         map1_kernel<<<grid_for(n4 ? n4 : 1, kBlock), kBlock, 0, st>>>(a, b, n4, n, f);
@@ -71,6 +72,7 @@ template <typename F>
 int launch3(DevCtx *cx, cudaStream_t st, const float *a, const float *b, float *c, size_t n, F f, const char *what) {
     if (n == 0) return 0;
     if (!a || !b || !c) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
+    ProfScope prof(cx, PROF_ELEMENTWISE, (F::reads_c ? 16.0 : 12.0) * n);
     if (aligned16(a) && aligned16(b) && aligned16(c)) {
         size_t n4 = n / 4;
         map3_kernel<<<grid_for(n4 ? n4 : 1, kBlock), kBlock, 0, st>>>(a, b, c, n4, n, f);
@@ -183,6 +185,7 @@ int eddlb200_pad(int dev, const float *a, float *b, int n, int c, int h, int w, 
     EB_REQUIRE(a && b && n >= 0 && c >= 0 && h >= 0 && w >= 0 && top >= 0 && bottom >= 0 && left >= 0 && right >= 0, "gpu_pad");
     size_t total = (size_t)n * c * h * w;
     if (!total) return 0;
+    ProfScope prof(cx, PROF_ELEMENTWISE, 8.0 * total);
     pad_kernel<false><<<grid_for(total, kBlock), kBlock, 0, st>>>(const_cast<float *>(a), b, total, h, w, top, left, h + top + bottom, w + left + right);
     EB_LAUNCH_CHECK("gpu_pad");
     return 0;
@@ -192,6 +195,7 @@ int eddlb200_pad_bwd(int dev, float *a_delta, const float *b_delta, int n, int c
     EB_REQUIRE(a_delta && b_delta && n >= 0 && c >= 0 && h >= 0 && w >= 0 && top >= 0 && bottom >= 0 && left >= 0 && right >= 0, "gpu_pad_back");
     size_t total = (size_t)n * c * h * w;
     if (!total) return 0;
+    ProfScope prof(cx, PROF_ELEMENTWISE, 12.0 * total);
     pad_kernel<true><<<grid_for(total, kBlock), kBlock, 0, st>>>(a_delta, const_cast<float *>(b_delta), total, h, w, top, left, h + top + bottom, w + left + right);
     EB_LAUNCH_CHECK("gpu_pad_back");
     return 0;

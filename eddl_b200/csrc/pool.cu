@@ -133,6 +133,7 @@ int eddlb200_maxpool2d_fwd(int dev, const float *in, float *out, float *ind_x, f
     const size_t total = (size_t)n * c * oh * ow;
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * ih * iw + 12.0 * total);
     maxpool_fwd_kernel<<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, ind_x, ind_y, total, g);
     EB_LAUNCH_CHECK("gpu_mpool2D");
     return 0;
@@ -146,6 +147,7 @@ int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const fl
     const size_t total = (size_t)n * c * ih * iw;
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + 8.0 * total);
     pool_bwd_kernel<true><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g);
     EB_LAUNCH_CHECK("gpu_mpool2D_back");
     return 0;
@@ -159,6 +161,7 @@ int eddlb200_avgpool2d_fwd(int dev, const float *in, float *out, int n, int c, i
     const size_t total = (size_t)n * c * oh * ow;
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * ih * iw + 4.0 * total);
     avgpool_fwd_kernel<<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, total, g);
     EB_LAUNCH_CHECK("gpu_avgpool2D");
     return 0;
@@ -172,6 +175,7 @@ int eddlb200_avgpool2d_bwd(int dev, const float *d, float *id, int n, int c, int
     const size_t total = (size_t)n * c * ih * iw;
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + 8.0 * total);
     pool_bwd_kernel<false><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g);
     EB_LAUNCH_CHECK("gpu_avgpool2D_back");
     return 0;

@@ -48,7 +48,8 @@ def run_conv(args):
     L.call("init", dev)
     flush = L.empty((64 << 20,), dev)
     rng = np.random.default_rng(0)
-    for (n, c, h, w, k, kr, kc, st, pad) in CONV_SHAPES:
+    shapes = CONV_SHAPES if args.shape < 0 else [CONV_SHAPES[args.shape]]
+    for (n, c, h, w, k, kr, kc, st, pad) in shapes:
         n = max(1, int(round(n * args.batch_scale)))
         oh = (h + 2 * pad - kr) // st + 1; ow = (w + 2 * pad - kc) // st + 1
         x = L.to_device(rng.standard_normal((n, c, h, w), dtype=np.float32), dev)
@@ -180,6 +181,7 @@ def main():
     ap.add_argument("--batch-scale", type=float, default=1.0)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--only", default=None)
+    ap.add_argument("--shape", type=int, default=-1, help="index into the conv shape list (default: all)")
     args = ap.parse_args()
     {"conv": run_conv, "hbm": run_hbm, "allreduce": run_allreduce}[args.what](args)
 

@@ -26,9 +26,11 @@
 // memory: the dominant hi*hi products rotate over three of them k-step by k-step (chain length K/24)
 // and the two small cross terms go to the fourth; the epilogue adds the four in fp32 with rounding.
 //
-// The producers gather with ordinary coalesced loads rather than TMA tensor copies: the tap
-// offset (s - pad) of an NCHW row is not a multiple of 16 bytes, and the hi/lo split needs a
-// pass through registers anyway.
+// Operand feeding.  The weight operand of forward / backward-data is pre-split and pre-swizzled once per
+// call (pack_b_kernel) and every stage fetches its tile with ONE TMA bulk copy (cp.async.bulk, completion on
+// the stage's mbarrier).  The activation operand is gathered by the producer warps with ordinary coalesced
+// loads rather than TMA tensor copies: the tap offset (s - pad) of an NCHW row is not a multiple of 16
+// bytes, which a tiled TMA copy requires, and the hi/lo split needs a pass through registers anyway.
 // Every wait on an mbarrier is bounded; on time-out the kernel records a status code, leaves
 // its loops, frees its tensor memory and returns.
 #include "common.cuh"
@@ -60,6 +62,7 @@ struct TcParams {
     int kblocks_per_split;
     long long split_stride; // elements between the partial outputs of consecutive splits
     int accumulate;
+    const float *packedB;   // forward / backward-data: pre-split, pre-swizzled B tiles [kblock][n tile][hi|lo][BN x 32]
     int nmain;              // rotating hi*hi accumulators in use: 1 for short chains, NMAIN otherwise
     int *status;
 };
@@ -87,6 +90,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         for (int i = 0; i < 256; i++) if (mbar_try(bar, parity)) return true;
         if (clock64() - t0 > 4000000000LL) return false;
     }
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// TMA bulk copy global -> shared (1-D, 16-byte aligned, size a multiple of 16), completion counted on an mbarrier
+__device__ __forceinline__ void tma_bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -149,9 +160,12 @@ struct Layout {
 
 // A_ROWMAJOR: consecutive rows of A are consecutive in memory (pixels) -> one thread per row, vector stores;
 // otherwise consecutive k are consecutive in memory -> one lane per k.
-// B_ROWMAJOR: the same choice for B (backward-data: consecutive in-channels of w[f][c][r][s] are rs floats apart).
-template <int BN_, bool SPLIT3, bool A_ROWMAJOR, bool B_ROWMAJOR>
+// WGRAD = false (forward, backward-data): B is the weight operand; it is prepared once per call by pack_b_kernel and
+// fetched with one TMA bulk copy per stage.  WGRAD = true (backward-weight): B = dy is gathered like A, one lane per k.
+template <int BN_, bool SPLIT3, bool WGRAD>
 __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P) {
+    constexpr bool A_ROWMAJOR = !WGRAD;
+    constexpr bool B_TMA = !WGRAD;
     using L = Layout<BN_, SPLIT3>;
     constexpr int STAGES = L::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -172,7 +186,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_accum = smem_u32(bars + 2 * STAGES);
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD + (B_TMA ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); }
         mbar_init(bar_accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -201,8 +215,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
         int2 myRow = make_int2(0, 0);
         if (A_ROWMAJOR) myRow = sRowA[arow];
         const int ry = myRow.y >> 16, rx = (int)(short)(myRow.y & 0xffff);
-        const int brow = tid % BN_, bgrp = tid / BN_;        // B_ROWMAJOR: one thread per (row, group of RB consecutive k)
-        const int myRowB = B_ROWMAJOR ? sRowB[brow] : 0;
+        constexpr uint32_t B_IMAGE = (uint32_t)L::B_BYTES * (SPLIT3 ? 2u : 1u);
 
         auto load_tiles = [&](int it) {
             const int kbase = (kb_begin + it) * BK;
@@ -227,14 +240,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     av[r] = ok ? __ldg(base + re.x) : 0.f;
                 }
             }
-            if (B_ROWMAJOR) {
-                const float *bbase = P.srcB + (myRowB < 0 ? 0 : myRowB);
-#pragma unroll
-                for (int i = 0; i < RB; i++) {
-                    const int kb = __ldg(P.kB + kbase + bgrp * RB + i);
-                    bv[i] = (kb >= 0 && myRowB >= 0) ? __ldg(bbase + kb) : 0.f;
-                }
-            } else {
+            if (!B_TMA) {
                 const int kb = __ldg(P.kB + kbase + lane);
                 const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
 #pragma unroll
@@ -270,20 +276,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     else *(float *)(sA_hi + off) = av[r];
                 }
             }
-            if (B_ROWMAJOR) {
-#pragma unroll
-                for (int g = 0; g < RB / 4; g++) {
-                    const uint32_t off = swz(brow, bgrp * RB + g * 4);
-                    if (SPLIT3) {
-                        float4 hi, lo;
-                        split_tf32(bv[4 * g + 0], hi.x, lo.x); split_tf32(bv[4 * g + 1], hi.y, lo.y);
-                        split_tf32(bv[4 * g + 2], hi.z, lo.z); split_tf32(bv[4 * g + 3], hi.w, lo.w);
-                        *(float4 *)(sB_hi + off) = hi; *(float4 *)(sB_lo + off) = lo;
-                    } else {
-                        *(float4 *)(sB_hi + off) = make_float4(bv[4 * g], bv[4 * g + 1], bv[4 * g + 2], bv[4 * g + 3]);
-                    }
-                }
-            } else {
+            if (!B_TMA) {
 #pragma unroll
                 for (int r = 0; r < RB; r++) {
                     const uint32_t off = swz(warp * RB + r, lane);
@@ -298,6 +291,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             const int s = it % STAGES;
             const uint32_t par = ((it / STAGES) & 1) ^ 1;
             if (!mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+            if (B_TMA && tid == 0) {
+                // weights of this K-block / filter tile: one bulk copy into the stage's B_hi|B_lo area
+                const uint32_t dstB = smem_u32(stage_base + s * L::STAGE_BYTES + (SPLIT3 ? 2 : 1) * L::A_BYTES);
+                const char *srcB = (const char *)P.packedB + ((size_t)(kb_begin + it) * gridDim.y + blockIdx.y) * B_IMAGE;
+                mbar_expect_tx(bar_full + 8 * s, B_IMAGE);
+                tma_bulk_g2s(dstB, srcB, B_IMAGE, bar_full + 8 * s);
+            }
             store_tiles(s);
             fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
             mbar_arrive(bar_full + 8 * s);
@@ -449,26 +449,46 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
     }
 }
 
-template <int BN_, bool SPLIT3, bool A_ROWMAJOR, bool B_ROWMAJOR>
+// B operand of forward / backward-data (the weights), prepared once per call: for every (K-block, filter tile) the
+// [BN x 32] tile is written in the exact shared-memory image the MMA reads (K-major SWIZZLE_128B), hi plane then lo
+// plane, so the main kernel fetches it with a single 16-byte-aligned TMA bulk copy.
+template <bool SPLIT3>
+__global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ src, const int *__restrict__ rowB, const int *__restrict__ kB,
+                                                     float *__restrict__ packed, int bn, int n_total, int tiles_n) {
+    const int kb = blockIdx.x, nt = blockIdx.y;
+    const size_t image_floats = (size_t)bn * BK * (SPLIT3 ? 2 : 1);
+    char *img = (char *)(packed + ((size_t)kb * tiles_n + nt) * image_floats);
+    for (int e = threadIdx.x; e < bn * BK; e += blockDim.x) {
+        const int row = e / BK, k = e % BK;
+        const int n = nt * bn + row;
+        const int ko = kB[kb * BK + k];
+        const float v = (n < n_total && ko >= 0) ? __ldg(src + rowB[n] + ko) : 0.f;
+        const uint32_t off = swz(row, k);
+        if (SPLIT3) { float hi, lo; split_tf32(v, hi, lo); *(float *)(img + off) = hi; *(float *)(img + (size_t)bn * BK * 4 + off) = lo; }
+        else *(float *)(img + off) = v;
+    }
+}
+
+template <int BN_, bool SPLIT3, bool WGRAD>
 int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
     using L = Layout<BN_, SPLIT3>;
     static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
     bool &configured = configured_dev[dev];
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, SPLIT3, A_ROWMAJOR, B_ROWMAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, SPLIT3, WGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e, "conv_tc(smem attribute)");
         configured = true;
     }
-    igemm_tc_kernel<BN_, SPLIT3, A_ROWMAJOR, B_ROWMAJOR><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
+    igemm_tc_kernel<BN_, SPLIT3, WGRAD><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
     EB_LAUNCH_CHECK("conv_tc");
     return 0;
 }
 
-template <bool SPLIT3, bool A_ROWMAJOR, bool B_ROWMAJOR>
+template <bool SPLIT3, bool WGRAD>
 int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn, int dev) {
-    if (bn == 32) return launch_variant<32, SPLIT3, A_ROWMAJOR, B_ROWMAJOR>(cx, st, P, grid, dev);
-    if (bn == 64) return launch_variant<64, SPLIT3, A_ROWMAJOR, B_ROWMAJOR>(cx, st, P, grid, dev);
-    return launch_variant<128, SPLIT3, A_ROWMAJOR, B_ROWMAJOR>(cx, st, P, grid, dev);
+    if (bn == 32) return launch_variant<32, SPLIT3, WGRAD>(cx, st, P, grid, dev);
+    if (bn == 64) return launch_variant<64, SPLIT3, WGRAD>(cx, st, P, grid, dev);
+    return launch_variant<128, SPLIT3, WGRAD>(cx, st, P, grid, dev);
 }
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
@@ -510,7 +530,8 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     auto carve = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };
     const size_t o_rowA = carve((size_t)T.M_total * 8), o_kA = carve((size_t)T.K_pad * 8), o_rowB = carve((size_t)T.N_total * 4),
                  o_kB = carve((size_t)T.K_pad * 4), o_outM = carve((size_t)T.M_total * 4),
-                 o_part = carve(splits > 1 ? out_total * splits * sizeof(float) : 0);
+                 o_part = carve(splits > 1 ? out_total * splits * sizeof(float) : 0),
+                 o_pack = carve(mode != 2 ? (size_t)kblocks * tiles_n * bn * BK * sizeof(float) * (precision == 0 ? 2 : 1) : 0);
     char *ws = (char *)scratch(cx, off);
     if (!ws) return cudaErrorMemoryAllocation;
     if (!g_status[dev]) {
@@ -521,6 +542,14 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     const long long entries = (long long)T.M_total + T.K_pad + T.N_total;
     build_tables_kernel<<<grid_for((size_t)entries, 256), 256, 0, st>>>(T);
     EB_LAUNCH_CHECK("conv_tc(tables)");
+    P.packedB = nullptr;
+    if (mode != 2) {
+        dim3 pgrid(kblocks, tiles_n);
+        if (precision == 0) pack_b_kernel<true><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
+        else pack_b_kernel<false><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
+        EB_LAUNCH_CHECK("conv_tc(pack weights)");
+        P.packedB = (const float *)(ws + o_pack);
+    }
     P.srcA = srcA; P.srcB = srcB;
     P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM;
     P.M_total = T.M_total; P.N_total = T.N_total; P.K_pad = T.K_pad;
@@ -533,9 +562,8 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     dim3 grid(tiles_m, tiles_n, splits);
     int r;
     const bool split3 = precision == 0;
-    if (mode == 2) r = split3 ? launch_bn<true, false, false>(cx, st, P, grid, bn, dev) : launch_bn<false, false, false>(cx, st, P, grid, bn, dev);
-    else if (mode == 1) r = split3 ? launch_bn<true, true, true>(cx, st, P, grid, bn, dev) : launch_bn<false, true, true>(cx, st, P, grid, bn, dev);
-    else r = split3 ? launch_bn<true, true, false>(cx, st, P, grid, bn, dev) : launch_bn<false, true, false>(cx, st, P, grid, bn, dev);
+    if (mode == 2) r = split3 ? launch_bn<true, true>(cx, st, P, grid, bn, dev) : launch_bn<false, true>(cx, st, P, grid, bn, dev);
+    else r = split3 ? launch_bn<true, false>(cx, st, P, grid, bn, dev) : launch_bn<false, false>(cx, st, P, grid, bn, dev);
     if (r) return r;
     if (splits > 1) {
         if (mode == 0) {

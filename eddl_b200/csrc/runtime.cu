@@ -281,6 +281,23 @@ int eddlb200_profile_read(int dev, int kind, unsigned long long *calls, double *
     return 0;
 }
 
+int eddlb200_profile_records(int dev, int kind, double *ms, double *work, int capacity, int *count) {
+    EB_CTX(dev);
+    if (kind < 0 || kind >= PROF_NKINDS || !count) return set_error(EDDLB200_EINVAL, "profile_records: bad argument");
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_status(e, "profile_records");
+    int n = 0;
+    for (auto &r : cx->prof_recs) {
+        if (r.kind != kind) continue;
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, r.a, r.b) != cudaSuccess) continue;
+        if (n < capacity && ms && work) { ms[n] = t; work[n] = r.work; }
+        n++;
+    }
+    *count = n;
+    return 0;
+}
+
 int eddlb200_profile_reset(int dev) {
     EB_CTX(dev);
     cudaStreamSynchronize(st);

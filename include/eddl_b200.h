@@ -61,6 +61,8 @@ int eddlb200_timer_elapsed_ms(int dev, int slot, float *ms);  /* blocking */
  * the calls' algorithmic work (FLOPs for 0-2 and 7, bytes otherwise).  read is blocking. */
 int eddlb200_profile_enable(int dev, int on);
 int eddlb200_profile_read(int dev, int kind, unsigned long long *calls, double *total_ms, double *total_work);
+/* Individual records of one family, in call order: duration (ms) and work of up to `capacity` calls; *count = calls recorded. */
+int eddlb200_profile_records(int dev, int kind, double *ms, double *work, int capacity, int *count);
 int eddlb200_profile_reset(int dev);
 /* Number of kernels this library has launched on `dev` since init. */
 int eddlb200_launch_count(int dev, unsigned long long *n);

@@ -99,6 +99,7 @@ def cpu_reference_run(steps, warmup, hw, classes, batch):
     if not ref.available():
         return None
     cores = os.cpu_count() or 1
+    ref.set_threads(cores)
     net = harness.NetHarness(ref.lib(), "resnet50", device=-1, hw=hw, classes=classes, threads=cores, optimizer="sgd", lr=0.1, mu=0.9)
     net.set_params(harness.init_weights(net.param_info(), seed=1234, mode="he_normal"))
     x, y = synth_batch(batch, hw, classes, seed=1)

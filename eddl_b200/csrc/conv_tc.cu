@@ -42,8 +42,9 @@ using namespace eb;
 
 constexpr int BM = 128;             // UMMA M (TMEM lanes)
 constexpr int BK = 32;              // fp32 per 128-byte swizzle row
-constexpr int NPROD = 256;          // producer threads (warps 0-7); warp 8 issues the MMAs
-constexpr int NTHREADS = NPROD + 32;
+constexpr int NPROD = 256;          // producer threads (warps 0-7); warp 8 issues the MMAs; warps 9-12 run the epilogue
+constexpr int NEPI = 128;           // epilogue threads (warps 9-12)
+constexpr int NTHREADS = NPROD + 32 + NEPI;
 constexpr int INVALID_Y = -20000;
 constexpr int NMAIN = 3;             // rotating hi*hi accumulators; a fourth holds the cross terms
 
@@ -58,6 +59,7 @@ struct TcParams {
     const int *outM;        // [M_total]
     int out_n_stride;
     int M_total, N_total, K_pad;
+    int tiles_m, tiles_n, splits;
     int limY, limX;
     int kblocks_per_split;
     long long split_stride; // elements between the partial outputs of consecutive splits
@@ -154,72 +156,87 @@ struct Layout {
     static constexpr int B_BYTES = BN_ * BK * 4;
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (SPLIT3 ? 2 : 1);
     static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 4 ? 4 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int TABLE_BYTES = BM * 8 + BN_ * 4;
+    static constexpr int TABLE_BYTES = BM * 8 + BN_ * 4;     // backward-weight row tables
     static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + TABLE_BYTES + 256;
 };
 
-// A_ROWMAJOR: consecutive rows of A are consecutive in memory (pixels) -> one thread per row, vector stores;
-// otherwise consecutive k are consecutive in memory -> one lane per k.
-// WGRAD = false (forward, backward-data): B is the weight operand; it is prepared once per call by pack_b_kernel and
-// fetched with one TMA bulk copy per stage.  WGRAD = true (backward-weight): B = dy is gathered like A, one lane per k.
+// Persistent, warp-specialised kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the
+// (split, filter tile, row tile) space.
+//   warps 0-7   producers: gather / split / store the A tile (and B for backward-weight); thread 0 also issues the TMA
+//               bulk copy of the packed weight tile.  The shared-memory ring keeps running across tile boundaries.
+//   warp  8     one lane issues the MMAs of a tile into one of the accumulator SETS in tensor memory.
+//   warps 9-12  epilogue: drain a finished set (tcgen05.ld), add its accumulators, store -- overlapped with the MMAs of
+//               the next tile whenever tensor memory holds two sets (BN <= 64, or short chains at BN = 128).
+// WGRAD = false (forward, backward-data): A rows are pixels (one thread per row, vector stores); B is the weight operand,
+// prepared once per call by pack_b_kernel.  WGRAD = true (backward-weight): A and B are gathered with one lane per k.
 template <int BN_, bool SPLIT3, bool WGRAD>
 __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P) {
-    constexpr bool A_ROWMAJOR = !WGRAD;
-    constexpr bool B_TMA = !WGRAD;
     using L = Layout<BN_, SPLIT3>;
     constexpr int STAGES = L::STAGES;
+    constexpr bool A_ROWMAJOR = !WGRAD;
+    constexpr bool B_TMA = !WGRAD;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *stage_base = smem;
-    int2 *sRowA = (int2 *)(smem + STAGES * L::STAGE_BYTES);
+    int2 *sRowA = (int2 *)(smem + STAGES * L::STAGE_BYTES);          // backward-weight: row entries of the current tile
     int *sRowB = (int *)(sRowA + BM);
-    uint64_t *bars = (uint64_t *)(sRowB + BN_);             // full[STAGES], empty[STAGES], accum
-    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 1);
+    uint64_t *bars = (uint64_t *)(sRowB + BN_);                      // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN_;
-    const int kb_begin = blockIdx.z * P.kblocks_per_split;
     const int kb_total = P.K_pad / BK;
-    const int kb_end = min(kb_total, kb_begin + P.kblocks_per_split);
-    const int nkb = kb_end - kb_begin;
+    const int tiles_mn = P.tiles_m * P.tiles_n;
+    const int total_tiles = tiles_mn * P.splits;
+    // accumulators per set: the rotating hi*hi ones plus (3xTF32) the cross-term one
+    const int nacc = P.nmain + (SPLIT3 ? 1 : 0);
+    const int nsets = (512 / (nacc * BN_)) >= 2 ? 2 : 1;
+    const int small_off = P.nmain * BN_;                 // column offset of the cross-term accumulator inside a set
+    const int set_cols = nacc * BN_;
 
-    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_accum = smem_u32(bars + 2 * STAGES);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
+    const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD + (B_TMA ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); }
-        mbar_init(bar_accum, 1);
+        for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, NEPI); }
+        *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < BM; i += NTHREADS) {
-        const int m = m0 + i;
-        sRowA[i] = m < P.M_total ? P.rowA[m] : make_int2(0, (INVALID_Y << 16));
-    }
-    for (int i = tid; i < BN_; i += NTHREADS) {
-        const int n = n0 + i;
-        sRowB[i] = n < P.N_total ? P.rowB[n] : -1;
-    }
-    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), 4 * BN_);
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
 
+    // K-block range of a tile's split
+    auto kb_range = [&](int t, int &kb0, int &nkb) {
+        const int split = t / tiles_mn;
+        kb0 = split * P.kblocks_per_split;
+        nkb = min(kb_total, kb0 + P.kblocks_per_split) - kb0;
+    };
+
     if (warp < 8) {
         // ============================ producers ============================
-        // Software pipeline: the global loads of K-block it+1 are issued into registers right after the
-        // stores of K-block it, so their latency overlaps the MMAs and the wait for a free stage.
-        constexpr int RB = BN_ / 8;              // B rows per warp
+        constexpr int RB = BN_ / 8;              // B rows per warp (backward-weight gather)
+        constexpr uint32_t B_IMAGE = (uint32_t)L::B_BYTES * (SPLIT3 ? 2u : 1u);
         float av[16], bv[RB];
         const int arow = tid & (BM - 1), ahalf = tid >> 7;
-        int2 myRow = make_int2(0, 0);
-        if (A_ROWMAJOR) myRow = sRowA[arow];
-        const int ry = myRow.y >> 16, rx = (int)(short)(myRow.y & 0xffff);
-        constexpr uint32_t B_IMAGE = (uint32_t)L::B_BYTES * (SPLIT3 ? 2u : 1u);
+        int2 myRow = make_int2(0, INVALID_Y << 16);
+        int ry = INVALID_Y, rx = 0;
 
-        auto load_tiles = [&](int it) {
-            const int kbase = (kb_begin + it) * BK;
+        // issue the global loads of K-block `it` of tile `t` into registers
+        auto load_tiles = [&](int t, int kb0, int it) {
+            const int mn = t % tiles_mn;
+            const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
+            const int kbase = (kb0 + it) * BK;
             if (A_ROWMAJOR) {
+                if (it == 0) {
+                    const int m = m0 + arow;
+                    myRow = m < P.M_total ? __ldg(P.rowA + m) : make_int2(0, INVALID_Y << 16);
+                    ry = myRow.y >> 16; rx = (int)(short)(myRow.y & 0xffff);
+                }
                 const float *base = P.srcA + myRow.x;
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
@@ -229,6 +246,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     av[i] = ok ? __ldg(base + ke.x) : 0.f;
                 }
             } else {
+                if (it == 0) {
+                    // new tile: refresh the shared row tables (all 256 producer threads take this branch together)
+                    asm volatile("bar.sync 1, 256;" ::: "memory");          // nobody still reads the previous tile's tables
+                    if (tid < BM) sRowA[tid] = (m0 + tid < P.M_total) ? __ldg(P.rowA + m0 + tid) : make_int2(0, INVALID_Y << 16);
+                    else if (tid - BM < BN_) sRowB[tid - BM] = (n0 + tid - BM < P.N_total) ? __ldg(P.rowB + n0 + tid - BM) : -1;
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                }
                 const int2 ke = __ldg(P.kA + kbase + lane);
                 const int ky = ke.y >> 16, kx = (int)(short)(ke.y & 0xffff);
                 const float *base = P.srcA + ke.x;
@@ -239,8 +263,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
                     av[r] = ok ? __ldg(base + re.x) : 0.f;
                 }
-            }
-            if (!B_TMA) {
                 const int kb = __ldg(P.kB + kbase + lane);
                 const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
 #pragma unroll
@@ -275,8 +297,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     if (SPLIT3) { float hi, lo; split_tf32(av[r], hi, lo); *(float *)(sA_hi + off) = hi; *(float *)(sA_lo + off) = lo; }
                     else *(float *)(sA_hi + off) = av[r];
                 }
-            }
-            if (!B_TMA) {
 #pragma unroll
                 for (int r = 0; r < RB; r++) {
                     const uint32_t off = swz(warp * RB + r, lane);
@@ -286,73 +306,93 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             }
         };
 
-        if (nkb > 0) load_tiles(0);
-        for (int it = 0; it < nkb; it++) {
-            const int s = it % STAGES;
-            const uint32_t par = ((it / STAGES) & 1) ^ 1;
-            if (!mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+        int t = blockIdx.x, kb0 = 0, nkb = 0, it = 0;
+        if (t < total_tiles) { kb_range(t, kb0, nkb); load_tiles(t, kb0, 0); }
+        for (int g = 0; t < total_tiles; g++) {
+            const int s = g % STAGES;
+            const uint32_t par = ((g / STAGES) & 1) ^ 1;
+            if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
             if (B_TMA && tid == 0) {
-                // weights of this K-block / filter tile: one bulk copy into the stage's B_hi|B_lo area
+                // packed weights of this K-block / filter tile: one bulk copy into the stage's B_hi|B_lo area
+                const int n_tile = (t % tiles_mn) / P.tiles_m;
                 const uint32_t dstB = smem_u32(stage_base + s * L::STAGE_BYTES + (SPLIT3 ? 2 : 1) * L::A_BYTES);
-                const char *srcB = (const char *)P.packedB + ((size_t)(kb_begin + it) * gridDim.y + blockIdx.y) * B_IMAGE;
+                const char *srcB = (const char *)P.packedB + ((size_t)(kb0 + it) * P.tiles_n + n_tile) * B_IMAGE;
                 mbar_expect_tx(bar_full + 8 * s, B_IMAGE);
                 tma_bulk_g2s(dstB, srcB, B_IMAGE, bar_full + 8 * s);
             }
             store_tiles(s);
             fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
             mbar_arrive(bar_full + 8 * s);
-            if (it + 1 < nkb) load_tiles(it + 1);
+            // advance to the next K-block (possibly of the next tile) and start its loads
+            if (++it == nkb) { t += gridDim.x; it = 0; if (t < total_tiles) kb_range(t, kb0, nkb); }
+            if (t < total_tiles) load_tiles(t, kb0, it);
         }
-    } else if (lane == 0) {
+    } else if (warp == 8) {
         // ============================ MMA issuer (one thread) ============================
-        const uint32_t idesc = make_idesc(BN_);
-        for (int it = 0; it < nkb; it++) {
-            const int s = it % STAGES;
-            if (!mbar_wait(bar_full + 8 * s, (it / STAGES) & 1)) { failed = true; break; }
-            tc_fence_after();
-            const uint32_t a_hi = smem_u32(stage_base + s * L::STAGE_BYTES);
-            const uint32_t a_lo = a_hi + L::A_BYTES;
-            const uint32_t b_hi = a_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
-            const uint32_t b_lo = b_hi + L::B_BYTES;
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(BN_);
+            int g = 0, local = 0;
+            for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x, local++) {
+                int kb0, nkb; kb_range(t, kb0, nkb);
+                const int set = local % nsets;
+                if (*abort_flag || !mbar_wait(bar_acc_empty + 8 * set, ((local / nsets) & 1) ^ 1)) { failed = true; break; }
+                tc_fence_after();
+                const uint32_t set_base = tmem_base + (uint32_t)(set * set_cols);
+                for (int it = 0; it < nkb; it++, g++) {
+                    const int s = g % STAGES;
+                    if (*abort_flag || !mbar_wait(bar_full + 8 * s, (g / STAGES) & 1)) { failed = true; break; }
+                    tc_fence_after();
+                    const uint32_t a_hi = smem_u32(stage_base + s * L::STAGE_BYTES);
+                    const uint32_t a_lo = a_hi + L::A_BYTES;
+                    const uint32_t b_hi = a_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
+                    const uint32_t b_lo = b_hi + L::B_BYTES;
 #pragma unroll
-            for (int ks = 0; ks < BK / 8; ks++) {
-                const uint32_t o = ks * 32;      // 8 fp32 = 32 bytes along K inside the swizzle row
-                const int step = it * (BK / 8) + ks;
-                const uint32_t d_main = tmem_base + (uint32_t)((step % P.nmain) * BN_);
-                if (SPLIT3) {
-                    const uint32_t d_small = tmem_base + (uint32_t)(NMAIN * BN_);
-                    umma_tf32(d_small, make_desc(a_lo + o), make_desc(b_hi + o), idesc, step > 0 ? 1u : 0u);
-                    umma_tf32(d_small, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
+                    for (int ks = 0; ks < BK / 8; ks++) {
+                        const uint32_t o = ks * 32;      // 8 fp32 = 32 bytes along K inside the swizzle row
+                        const int step = it * (BK / 8) + ks;
+                        const uint32_t d_main = set_base + (uint32_t)((step % P.nmain) * BN_);
+                        if (SPLIT3) {
+                            const uint32_t d_small = set_base + (uint32_t)small_off;
+                            umma_tf32(d_small, make_desc(a_lo + o), make_desc(b_hi + o), idesc, step > 0 ? 1u : 0u);
+                            umma_tf32(d_small, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
+                        }
+                        umma_tf32(d_main, make_desc(a_hi + o), make_desc(b_hi + o), idesc, step >= P.nmain ? 1u : 0u);
+                    }
+                    umma_commit(bar_empty + 8 * s);      // frees the stage when these MMAs have read it
                 }
-                umma_tf32(d_main, make_desc(a_hi + o), make_desc(b_hi + o), idesc, step >= P.nmain ? 1u : 0u);
+                if (!failed) umma_commit(bar_acc_full + 8 * set);     // this tile's accumulators are complete
             }
-            umma_commit(bar_empty + 8 * s);      // frees the stage when these MMAs have read it
         }
-        umma_commit(bar_accum);                  // accumulator complete
-    }
-    __syncwarp();
-
-    // ============================ epilogue (warps 0-3: TMEM lanes 32*warp ..) ============================
-    if (warp < 4 && nkb > 0) {
-        if (!failed && !mbar_wait(bar_accum, 0)) failed = true;
-        tc_fence_after();
-        if (!failed) {
-            const int m = m0 + warp * 32 + lane;
+        __syncwarp();
+    } else {
+        // ============================ epilogue (warps 9-12) ============================
+        const int quarter = warp & 3;                     // the TMEM lane quarter this warp may access
+        int local = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, local++) {
+            const int mn = t % tiles_mn, split = t / tiles_mn;
+            const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
+            const int set = local % nsets;
+            if (*abort_flag || !mbar_wait(bar_acc_full + 8 * set, (local / nsets) & 1)) { failed = true; break; }
+            tc_fence_after();
+            const int m = m0 + quarter * 32 + lane;
             const bool m_ok = m < P.M_total;
-            float *obase = P.out + (long long)blockIdx.z * P.split_stride + (m_ok ? (long long)P.outM[m] : 0);
+            float *obase = P.out + (long long)split * P.split_stride + (m_ok ? (long long)__ldg(P.outM + m) : 0);
+            const uint32_t set_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(set * set_cols);
 #pragma unroll 1
             for (int c = 0; c < (BN_ + 31) / 32; c++) {
-                uint32_t r[32], t[32];
-                const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32);
-                tmem_ld32(lane_base, r);
-                // nkb >= 1 gives at least four k-steps, so every rotating accumulator in use holds data;
-                // accumulator NMAIN holds the cross terms of the 3xTF32 split
+                uint32_t r[32], tt[32];
+                tmem_ld32(set_base + (uint32_t)(c * 32), r);
+                // every accumulator in use holds data: a tile has at least four k-steps
 #pragma unroll 1
-                for (int a = 1; a <= NMAIN; a++) {
-                    if (a >= P.nmain && !(SPLIT3 && a == NMAIN)) continue;
-                    tmem_ld32(lane_base + (uint32_t)(a * BN_), t);
+                for (int a = 1; a < nacc; a++) {
+                    tmem_ld32(set_base + (uint32_t)(a * BN_ + c * 32), tt);
 #pragma unroll
-                    for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(t[j])));
+                    for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(tt[j])));
+                }
+                if (c == (BN_ + 31) / 32 - 1) {
+                    // all of this set has been read: hand it back to the MMA warp before the global stores
+                    tc_fence_before();
+                    mbar_arrive(bar_acc_empty + 8 * set);
                 }
                 if (m_ok) {
                     float *col0 = obase + (long long)(n0 + c * 32) * P.out_n_stride;
@@ -380,10 +420,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             }
         }
     }
-    if (failed) atomicExch(P.status, 1);
+    if (failed) { *abort_flag = 1; atomicExch(P.status, 1); }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) tmem_dealloc(tmem_base, 4 * BN_);
+    if (warp == 8) tmem_dealloc(tmem_base, 512);
 }
 
 // ---- index tables ----------------------------------------------------------------------------------
@@ -554,12 +594,14 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM;
     P.M_total = T.M_total; P.N_total = T.N_total; P.K_pad = T.K_pad;
     P.kblocks_per_split = kbs;
+    P.tiles_m = tiles_m; P.tiles_n = tiles_n; P.splits = splits;
     // a single accumulator drifts by ~2.5e-6 at 64 k-steps (K = 512); longer chains rotate over three
     P.nmain = (kbs * (BK / 8) > 64) ? NMAIN : 1;
     P.status = g_status[dev];
     if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
     else { P.out = out; P.split_stride = 0; P.accumulate = (mode != 0); P.bias = bias; }
-    dim3 grid(tiles_m, tiles_n, splits);
+    const long long total_tiles = (long long)tiles_m * tiles_n * splits;
+    dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
     int r;
     const bool split3 = precision == 0;
     if (mode == 2) r = split3 ? launch_bn<true, true>(cx, st, P, grid, bn, dev) : launch_bn<false, true>(cx, st, P, grid, bn, dev);

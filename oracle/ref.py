@@ -178,3 +178,8 @@ def adam_step(p, g, m, v, lr, b1, b2, eps, t):
 def sync_weights(reps):
     reps = _f(reps); out = np.empty(reps.shape[1], np.float32)
     _ck(lib().ref_sync_weights(_p(reps), reps.shape[0], _p(out), ctypes.c_longlong(reps.shape[1]))); return out
+
+
+def set_threads(n):
+    """OpenMP threads for the reference's CPU loops (0 = all cores).  Use 1 for reproducible BatchNorm sums."""
+    lib().ref_set_omp_threads(int(n))

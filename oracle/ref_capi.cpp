@@ -223,3 +223,9 @@ int ref_sync_weights(const float *reps, int nrep, float *out, long long n) {
 }
 
 }  // extern "C"
+
+// OpenMP team size used by the reference's cpu_* loops (omp_set_num_threads).  Parity runs use 1: the
+// reference's BatchNorm reductions accumulate per-channel sums from a parallel loop without atomics
+// (src/hardware/cpu/nn/cpu_bn.cpp:130-141, 193-205), so their results are only reproducible single-threaded.
+#include <omp.h>
+extern "C" int ref_set_omp_threads(int n) { omp_set_num_threads(n > 0 ? n : omp_get_num_procs()); return 0; }

@@ -69,7 +69,7 @@ def test_bn_nets_match_live_reference(gpu_lib, ref, cfg, hw, classes, batch, ste
     under 1e-6 relative weight perturbations (or within 1e-4, whichever is larger)."""
     if ref is None:
         pytest.skip("oracle/_ref not built")
-    os.environ["OMP_NUM_THREADS"] = "1"
+    ref.set_threads(1)          # the reference's BatchNorm sums race under OpenMP; one thread makes them reproducible
     probe = harness.NetHarness(ref.lib(), cfg, device=-1, hw=hw, classes=classes, threads=1)
     info = probe.param_info(); probe.close()
     w0 = harness.init_weights(info, seed=99, mode="he_normal")

@@ -173,6 +173,7 @@ def run_b200_arm(args):
             net.avg_weights(i + 1, 1)
         return loss
 
+    sampler = ClockSampler(local); sampler.start()      # samples SM clocks / throttle reasons across both timed regions
     for i in range(args.warmup):
         loss0 = e2e_step(i)
     net.sync(); ebd.barrier()
@@ -192,7 +193,6 @@ def run_b200_arm(args):
     # ---- value: batch resident in HBM -------------------------------------------------------------------------
     net.train_resident(1)
     net.sync(); ebd.barrier()
-    sampler = ClockSampler(local); sampler.start()
     L.call("profile_reset", local); L.call("profile_enable", local, 1)
     launches0 = L.launches(local)
     L.call("timer_start", local, 1)

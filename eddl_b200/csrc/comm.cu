@@ -118,6 +118,7 @@ int eddlb200_allreduce_avg(int dev, float *buf, size_t n) {
     EB_CTX(dev);
     if (n == 0) return 0;
     EB_REQUIRE(buf, "allreduce_avg");
+    ProfScope prof(cx, PROF_COMM, 4.0 * n);
     const int N = comm_nranks(cx);
     if (comm_of(cx)) {
         if (int r = nccl_status(ncclAllReduce(buf, buf, n, ncclFloat, ncclSum, comm_of(cx), st), "ncclAllReduce")) return r;
@@ -139,6 +140,7 @@ int eddlb200_allreduce_avg_multi(int dev, float *const *bufs, const size_t *size
         if (sizes[i] > largest) largest = sizes[i];
     }
     if (segs.empty()) return 0;
+    ProfScope prof(cx, PROF_COMM, 4.0 * total);
     const size_t seg_bytes = (segs.size() * sizeof(Seg) + 255) & ~size_t(255);
     char *ws = (char *)scratch(cx, seg_bytes + total * sizeof(float));
     if (!ws) return cudaErrorMemoryAllocation;

@@ -6,6 +6,8 @@
 // grid is a multiple of the 148 SMs.  Arithmetic is written with explicit
 // round-to-nearest intrinsics where the reference evaluates a*b+c in two roundings,
 // so that results are bit-identical to its CPU code (no FMA contraction).
+#include <cstring>
+#include <vector>
 #include "common.cuh"
 
 namespace {
@@ -134,11 +136,62 @@ __global__ void __launch_bounds__(kBlock) pad_kernel(float *a, float *b, size_t 
     }
 }
 
+// Many fills in one launch: segment table in the scratch arena, one block-chunk of 16K elements per table entry.
+struct FillSeg { float *p; unsigned long long n; float v; unsigned pad; };
+struct FillChunk { unsigned seg; unsigned offset_k; };
+constexpr unsigned kFillChunk = 16384;
+__global__ void __launch_bounds__(kBlock) fill_multi_kernel(const FillSeg *__restrict__ segs, const FillChunk *__restrict__ chunks, int nchunks) {
+    for (int c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const FillChunk ch = chunks[c];
+        const FillSeg sg = segs[ch.seg];
+        const size_t beg = (size_t)ch.offset_k * kFillChunk;
+        const size_t end = beg + kFillChunk < sg.n ? beg + kFillChunk : (size_t)sg.n;
+        if ((((uintptr_t)sg.p) & 15u) == 0) {
+            const size_t end4 = beg + ((end - beg) & ~size_t(3));
+            const float4 v4 = make_float4(sg.v, sg.v, sg.v, sg.v);
+            for (size_t j = beg + threadIdx.x * 4; j < end4; j += kBlock * 4) *reinterpret_cast<float4 *>(sg.p + j) = v4;
+            for (size_t j = end4 + threadIdx.x; j < end; j += kBlock) sg.p[j] = sg.v;
+        } else {
+            for (size_t j = beg + threadIdx.x; j < end; j += kBlock) sg.p[j] = sg.v;
+        }
+    }
+}
+
 }  // namespace
 
 using namespace eb;
 
 extern "C" {
+
+int eddlb200_fill_multi(int dev, float *const *ptrs, const size_t *sizes, const float *values, int ntensors) {
+    EB_CTX(dev);
+    EB_REQUIRE(ntensors >= 0 && (ntensors == 0 || (ptrs && sizes && values)), "fill_multi");
+    std::vector<FillSeg> segs; std::vector<FillChunk> chunks;
+    double total = 0;
+    for (int i = 0; i < ntensors; i++) {
+        if (!sizes[i]) continue;
+        EB_REQUIRE(ptrs[i], "fill_multi");
+        segs.push_back(FillSeg{ptrs[i], (unsigned long long)sizes[i], values[i], 0u});
+        const size_t nch = ceil_div(sizes[i], (size_t)kFillChunk);
+        for (size_t c = 0; c < nch; c++) chunks.push_back(FillChunk{(unsigned)(segs.size() - 1), (unsigned)c});
+        total += (double)sizes[i];
+    }
+    if (chunks.empty()) return 0;
+    const size_t bytes_s = segs.size() * sizeof(FillSeg), off_c = (bytes_s + 255) & ~size_t(255), bytes_c = chunks.size() * sizeof(FillChunk);
+    char *tab = (char *)scratch(cx, off_c + bytes_c);
+    if (!tab) return cudaErrorMemoryAllocation;
+    std::vector<char> host(off_c + bytes_c);
+    memcpy(host.data(), segs.data(), bytes_s);
+    memcpy(host.data() + off_c, chunks.data(), bytes_c);
+    cudaError_t e = cudaMemcpyAsync(tab, host.data(), host.size(), cudaMemcpyHostToDevice, st);   // pageable source: staged before return
+    if (e != cudaSuccess) return cuda_status(e, "fill_multi(table)");
+    ProfScope prof(cx, PROF_ELEMENTWISE, 4.0 * total);
+    int blocks = (int)chunks.size();
+    if (blocks > EDDLB200_NUM_SMS * 8) blocks = EDDLB200_NUM_SMS * 8;
+    fill_multi_kernel<<<blocks, kBlock, 0, st>>>((const FillSeg *)tab, (const FillChunk *)(tab + off_c), (int)chunks.size());
+    EB_LAUNCH_CHECK("gpu_fill_(batched)");
+    return 0;
+}
 
 int eddlb200_fill(int dev, float *a, size_t n, float v) {
     EB_CTX(dev);

@@ -52,8 +52,25 @@ void launch_bn(int dev, PendingBN &p, float *relu_out) {
     ok(eddlb200_bn_fwd(dev, p.b, p.z, p.rc, p.input, p.output, p.opa, p.gmean, p.gvar, p.g, p.bb, p.mean, p.var,
                        p.trmode, p.eps, p.momentum, relu_out), "gpu_batchnorm_forward");
 }
+// Pending gpu_fill_ calls (per device).  Net::do_reset / do_reset_grads zero every delta and every gradient tensor with
+// one call each -- several hundred back-to-back launches per step for a ResNet-50; they are collected here and issued as
+// one multi-tensor launch as soon as any other backend call arrives.
+struct FillQueue { std::vector<float *> ptrs; std::vector<size_t> sizes; std::vector<float> values; };
+FillQueue g_fills[64];
+bool fill_batching_enabled() {
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("EDDL_B200_BATCH_FILLS"); v = (e && e[0] == '0') ? 0 : 1; }
+    return v == 1;
+}
 inline void flush(int dev) {
-    if (dev >= 0 && dev < 64 && g_pending[dev].active) launch_bn(dev, g_pending[dev], nullptr);
+    if (dev < 0 || dev >= 64) return;
+    FillQueue &q = g_fills[dev];
+    if (!q.ptrs.empty()) {
+        std::vector<float *> p; std::vector<size_t> s; std::vector<float> v;
+        p.swap(q.ptrs); s.swap(q.sizes); v.swap(q.values);
+        ok(eddlb200_fill_multi(dev, p.data(), s.data(), v.data(), (int)p.size()), "gpu_fill_");
+    }
+    if (g_pending[dev].active) launch_bn(dev, g_pending[dev], nullptr);
 }
 inline int dev_of(const Tensor *t) { flush(t->gpu_device); return t->gpu_device; }
 
@@ -97,7 +114,18 @@ void gpu_copy_gpu(Tensor *A, Tensor *B) {
     }
     ok(eddlb200_memcpy_d2d(dev_of(A), B->ptr, A->ptr, A->size * sizeof(float)), "gpu_copy_gpu");
 }
-void gpu_fill_(Tensor *A, float v) { ok(eddlb200_fill(dev_of(A), A->ptr, A->size, v), "gpu_fill_"); }
+void gpu_fill_(Tensor *A, float v) {
+    const int dev = A->gpu_device;
+    if (fill_batching_enabled() && dev >= 0 && dev < 64 && !g_pending[dev].active) {
+        FillQueue &q = g_fills[dev];
+        // a tensor filled twice before the flush keeps only the last value (two queued fills would race)
+        for (size_t i = 0; i < q.ptrs.size(); i++)
+            if (q.ptrs[i] == A->ptr && q.sizes[i] == A->size) { q.values[i] = v; return; }
+        q.ptrs.push_back(A->ptr); q.sizes.push_back(A->size); q.values.push_back(v);
+        return;
+    }
+    ok(eddlb200_fill(dev_of(A), A->ptr, A->size, v), "gpu_fill_");
+}
 
 // Device-side initialisers (the reference uses cuRAND MRG32K3A with a fixed seed per device,
 // gpu_tensor.cu:179-185): values are drawn on the host with a fixed-seed generator and copied.

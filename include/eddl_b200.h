@@ -70,6 +70,9 @@ int eddlb200_launch_count(int dev, unsigned long long *n);
 /* ---- elementwise (src/hardware/gpu/gpu_math.cu:108-116,148-156,275-284,390-410,
  *      446-455,493-503; gpu_core.cu:139-147; cpu twins in src/hardware/cpu/cpu_math.cpp) */
 int eddlb200_fill(int dev, float *a, size_t n, float v);                      /* gpu_fill_ */
+/* ntensors fills in ONE launch (Net::do_reset / do_reset_grads issue one gpu_fill_ per delta and per gradient tensor:
+ * src/layers/layer.cpp:190-205). */
+int eddlb200_fill_multi(int dev, float *const *ptrs, const size_t *sizes, const float *values, int ntensors);
 /* gpu_add(scA,A,scB,B,C,incC): C = (incC ? C : 0) + scA*A + scB*B */
 int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b, float *c, int inc_c, size_t n);
 int eddlb200_inc(int dev, const float *a, float *b, size_t n);                /* gpu_inc: B += A */

@@ -60,7 +60,7 @@ def _trajectory(lib_, cfg, hw, classes, device, opt, w0, x, y, steps, threads=-1
 
 
 @pytest.mark.parametrize("opt", ["sgd", "sgd_fused"])
-@pytest.mark.parametrize("cfg,hw,classes,batch,steps", [("vgg16bn", 32, 10, 16, 3), ("resnet50", 64, 100, 8, 3), ("resnet50", 224, 1000, 2, 2)])
+@pytest.mark.parametrize("cfg,hw,classes,batch,steps", [("vgg16bn", 32, 10, 16, 3), ("resnet50", 64, 100, 8, 3), ("resnet50", 224, 1000, 2, 1)])
 def test_bn_nets_match_live_reference(gpu_lib, ref, cfg, hw, classes, batch, steps, opt):
     """First step (pure forward + loss): within 1e-4 relative of the reference's CS_CPU path, the stated requirement.
     Later steps: these randomly initialised BatchNorm nets are chaotic -- the reference itself moves its step-2 loss by
@@ -76,7 +76,7 @@ def test_bn_nets_match_live_reference(gpu_lib, ref, cfg, hw, classes, batch, ste
     x, y = synth((3, hw, hw), classes, batch, seed=5)
     base, pc = _trajectory(ref.lib(), cfg, hw, classes, -1, "sgd", w0, x, y, steps, threads=1)
     spread = np.zeros(steps)
-    for t in (1, 2):
+    for t in ((1, 2) if steps > 1 else ()):
         wp = (w0 * (1 + 1e-6 * np.random.default_rng(t).standard_normal(w0.size))).astype(F)
         pert, _ = _trajectory(ref.lib(), cfg, hw, classes, -1, "sgd", wp, x, y, steps, threads=1)
         spread = np.maximum(spread, np.abs(pert - base))

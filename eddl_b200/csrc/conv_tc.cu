@@ -458,6 +458,10 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
                 const int yc = (y + g.pt - T.ca) / g.sr, xc = (x + g.pl - T.cb) / g.sc;
                 T.rowA[m] = make_int2(n * g.k * pq + yc * g.ow + xc, pack_yx(yc, xc));
                 T.outM[m] = n * g.c * hw + y * g.iw + x;
+            } else if (T.mode == 3) {       // output pixel of dy; result column plane T[n][(c,r,s)][p][q]
+                const int n = m / pq, t = m - n * pq;
+                T.rowA[m] = make_int2(n * g.k * pq + t, pack_yx(0, 0));
+                T.outM[m] = n * g.c * rs * pq + t;
             } else {                        // (c, r, s)
                 const int c = m / rs, t = m - c * rs, r = t / g.kc, s = t - r * g.kc;
                 T.rowA[m] = make_int2(c * hw + (r - g.pt) * g.iw + (s - g.pl), pack_yx(r - g.pt, s - g.pl));
@@ -475,6 +479,9 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
                 const int f = k / taps, t = k - f * taps, r2 = t / T.st_, s2 = t - r2 * T.st_;
                 T.kA[k] = make_int2(f * pq - r2 * g.ow - s2, pack_yx(-r2, -s2));
                 T.kB[k] = f * g.c * rs + (T.ca + r2 * g.sr) * g.kc + (T.cb + s2 * g.sc);
+            } else if (T.mode == 3) {       // filter f
+                T.kA[k] = make_int2(k * pq, pack_yx(0, 0));
+                T.kB[k] = k * g.c * rs;
             } else {                        // (n, p, q)
                 const int n = k / pq, t = k - n * pq, p = t / g.ow, q = t - p * g.ow;
                 T.kA[k] = make_int2(n * g.c * hw + p * g.sr * g.iw + q * g.sc, pack_yx(p * g.sr, q * g.sc));
@@ -484,6 +491,7 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
             const int n = (int)(i - T.M_total - T.K_pad);
             if (T.mode == 0) T.rowB[n] = n * T.K_total;         // filter row of w[f][c*r*s]
             else if (T.mode == 1) T.rowB[n] = n * rs;           // in-channel c of w[f][c][r][s]
+            else if (T.mode == 3) T.rowB[n] = n;                // (c,r,s) column of w[f][c*r*s]
             else T.rowB[n] = n * pq;                            // filter plane of dy[n][f][p*q]
         }
     }
@@ -599,7 +607,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     P.nmain = (kbs * (BK / 8) > 64) ? NMAIN : 1;
     P.status = g_status[dev];
     if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
-    else { P.out = out; P.split_stride = 0; P.accumulate = (mode != 0); P.bias = bias; }
+    else { P.out = out; P.split_stride = 0; P.accumulate = (mode == 1 || mode == 2); P.bias = bias; }
     const long long total_tiles = (long long)tiles_m * tiles_n * splits;
     dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
     int r;
@@ -650,6 +658,55 @@ int run(DevCtx *cx, cudaStream_t st, int dev, int mode, const ConvGeom &g, const
     return 0;
 }
 
+// Gather-form col2im for the GEMM route of backward-data: dx[n,c,y,x] += sum over the taps (r,s) of the pixel's stride
+// residue class of T[n][(c,r,s)][p][q], p = (y+pt-r)/sr, q = (x+pl-s)/sc.  One thread per dx element, no atomics.
+__global__ void __launch_bounds__(256) col2im_gather_kernel(ConvGeom g, const float *__restrict__ T, float *__restrict__ dx) {
+    const int hw = g.ih * g.iw, pq = g.oh * g.ow, rs = g.kr * g.kc;
+    const long long total = (long long)g.n * g.c * hw;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int x = (int)(i % g.iw);
+        long long t = i / g.iw;
+        const int y = (int)(t % g.ih); t /= g.ih;          // t = n*C + c
+        const int r0 = (y + g.pt) % g.sr, s0 = (x + g.pl) % g.sc;
+        const int p0 = (y + g.pt - r0) / g.sr, q0 = (x + g.pl - s0) / g.sc;
+        const float *plane = T + (size_t)t * rs * pq;
+        float acc = 0.f;
+        for (int r = r0, p = p0; r < g.kr && p >= 0; r += g.sr, p--) {
+            if (p >= g.oh) continue;
+            for (int s = s0, q = q0; s < g.kc && q >= 0; s += g.sc, q--) {
+                if (q >= g.ow) continue;
+                acc += __ldg(plane + (size_t)(r * g.kc + s) * pq + p * g.ow + q);
+            }
+        }
+        dx[i] = __fadd_rn(dx[i], acc);
+    }
+}
+
+// Backward-data for layers with very few input channels (the 7x7 stem: C = 3).  With pixels on M and channels on N the
+// GEMM would gather every dy value for 3 useful columns out of 32; instead T[(n,p,q)][(c,r,s)] = sum_f dy * w is one dense
+// GEMM that reads dy exactly once (K = filters), followed by the gather-form col2im above.
+int run_small_c_bwd_data(DevCtx *cx, cudaStream_t st, int dev, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision) {
+    const int pq = g.oh * g.ow, rs = g.kr * g.kc;
+    const size_t t_elems = (size_t)g.n * g.c * rs * pq;
+    // T lives in a buffer of its own: run_one() re-carves the scratch arena
+    static float *tbuf[EDDLB200_MAX_DEVICES] = {}; static size_t tcap[EDDLB200_MAX_DEVICES] = {};
+    if (tcap[dev] < t_elems) {
+        cudaStreamSynchronize(st);
+        if (tbuf[dev]) cudaFree(tbuf[dev]);
+        tbuf[dev] = nullptr; tcap[dev] = 0;
+        if (cudaMalloc((void **)&tbuf[dev], t_elems * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return 1; }
+        tcap[dev] = t_elems;
+    }
+    TableArgs T{};
+    T.g = g; T.mode = 3;
+    TcParams P{};
+    T.M_total = g.n * pq; T.N_total = g.c * rs; T.K_total = g.k; P.limY = 1; P.limX = 1; P.out_n_stride = pq;
+    if (int r = run_one(cx, st, dev, T, P, dy, w, tbuf[dev], nullptr, precision, t_elems, false)) return r;
+    col2im_gather_kernel<<<grid_for((size_t)g.n * g.c * g.ih * g.iw, 256), 256, 0, st>>>(g, tbuf[dev], dx);
+    EB_LAUNCH_CHECK("conv_tc(col2im gather)");
+    return 0;
+}
+
 bool fits(const ConvGeom &g) {
     // index tables hold 16-bit coordinates and 32-bit offsets
     return g.ih < 16000 && g.iw < 16000 && g.oh < 16000 && g.ow < 16000;
@@ -668,6 +725,10 @@ int conv_tc_fwd(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, 
 int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision) {
     if (!fits(g)) return 1;
     int dev = 0; cudaGetDevice(&dev);
+    if (g.c <= 8 && (size_t)g.n * g.c * g.kr * g.kc * g.oh * g.ow < (size_t(1) << 29)) {
+        const int r = run_small_c_bwd_data(cx, st, dev, g, dy, w, dx, precision);
+        if (r != 1) return r;
+    }
     return run(cx, st, dev, 1, g, dy, w, dx, nullptr, precision);
 }
 

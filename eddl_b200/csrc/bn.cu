@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(kBlock) bn_stats_kernel(const float *__restric
     const Slice sl = slice_of(b * rc, nsplit, s);
     float a0 = 0.f, a1 = 0.f;
     if (VEC) {
+#pragma unroll 4
         for (unsigned t = sl.begin + threadIdx.x * 4; t < sl.end; t += kBlock * 4) {
             const size_t off = item_offset(t, rc, z, j);
             const float4 v = ld_stream4(x + off);
@@ -132,6 +133,7 @@ __global__ void __launch_bounds__(kBlock) bn_fwd_apply_kernel(const float *__res
     const float gj = affine ? g[j] : 1.f, bj = affine ? beta[j] : 0.f;
     const Slice sl = slice_of(b * rc, nsplit, s);
     if (VEC) {
+#pragma unroll 4
         for (unsigned t = sl.begin + threadIdx.x * 4; t < sl.end; t += kBlock * 4) {
             const size_t off = item_offset(t, rc, z, j);
             const float4 v = ld_stream4(x + off);
@@ -187,6 +189,7 @@ __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(float *__restrict_
     const float sigma = variance[j];
     const Slice sl = slice_of(b * rc, nsplit, s);
     if (VEC) {
+#pragma unroll 4
         for (unsigned t = sl.begin + threadIdx.x * 4; t < sl.end; t += kBlock * 4) {
             const size_t off = item_offset(t, rc, z, j);
             float4 d = *reinterpret_cast<const float4 *>(delta + off);

@@ -64,6 +64,7 @@ struct TcParams {
     int kblocks_per_split;
     long long split_stride; // elements between the partial outputs of consecutive splits
     int accumulate;
+    int check;              // padding test of the gathered operand: 0 none needed, 1 per-row tap bitmask, 2 coordinates
     const float *packedB;   // forward / backward-data: pre-split, pre-swizzled B tiles [kblock][n tile][hi|lo][BN x 32]
     int nmain;              // rotating hi*hi accumulators in use: 1 for short chains, NMAIN otherwise
     int *status;
@@ -234,16 +235,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             if (A_ROWMAJOR) {
                 if (it == 0) {
                     const int m = m0 + arow;
-                    myRow = m < P.M_total ? __ldg(P.rowA + m) : make_int2(0, INVALID_Y << 16);
+                    myRow = m < P.M_total ? __ldg(P.rowA + m) : make_int2(0, P.check == 1 ? 0 : (INVALID_Y << 16));
                     ry = myRow.y >> 16; rx = (int)(short)(myRow.y & 0xffff);
                 }
                 const float *base = P.srcA + myRow.x;
+                if (P.check == 0) {
+                    // every tap of every row is inside the image (1x1 and other unpadded shapes)
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int2 ke = __ldg(P.kA + kbase + ahalf * 16 + i);
-                    const int y = ry + (ke.y >> 16), x = rx + (int)(short)(ke.y & 0xffff);
-                    const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
-                    av[i] = ok ? __ldg(base + ke.x) : 0.f;
+                    for (int i = 0; i < 16; i++) av[i] = __ldg(base + __ldg(&P.kA[kbase + ahalf * 16 + i].x));
+                } else if (P.check == 1) {
+                    // myRow.y holds one bit per filter tap; the k entry holds the tap number (31 = beyond K)
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int2 ke = __ldg(P.kA + kbase + ahalf * 16 + i);
+                        av[i] = ((unsigned)myRow.y >> ke.y) & 1u ? __ldg(base + ke.x) : 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int2 ke = __ldg(P.kA + kbase + ahalf * 16 + i);
+                        const int y = ry + (ke.y >> 16), x = rx + (int)(short)(ke.y & 0xffff);
+                        const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
+                        av[i] = ok ? __ldg(base + ke.x) : 0.f;
+                    }
                 }
             } else {
                 if (it == 0) {
@@ -435,6 +449,7 @@ struct TableArgs {
     // class receive contributions only from the taps r = ca + r'*sr, s = cb + s'*sc, which turns a strided
     // backward pass into sr*sc dense stride-1 problems with no wasted taps.
     int ca, cb, y0, x0, hc, wc, rt, st_;
+    int check, limY, limX;   // check == 1: rowA.y = bitmask over taps, kA.y = tap number
     int2 *rowA, *kA; int *rowB, *kB, *outM;
     int M_total, N_total, K_total, K_pad;
 };
@@ -449,14 +464,26 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
             if (T.mode == 0) {              // output pixel
                 const int n = m / pq, t = m - n * pq, p = t / g.ow, q = t - p * g.ow;
                 const int y = p * g.sr - g.pt, x = q * g.sc - g.pl;
-                T.rowA[m] = make_int2(n * g.c * hw + y * g.iw + x, pack_yx(y, x));
+                int tag = pack_yx(y, x);
+                if (T.check == 1) {
+                    tag = 0;
+                    for (int r = 0; r < g.kr; r++) for (int s2 = 0; s2 < g.kc; s2++)
+                        if ((unsigned)(y + r) < (unsigned)T.limY && (unsigned)(x + s2) < (unsigned)T.limX) tag |= 1 << (r * g.kc + s2);
+                }
+                T.rowA[m] = make_int2(n * g.c * hw + y * g.iw + x, tag);
                 T.outM[m] = n * g.k * pq + t;
             } else if (T.mode == 1) {       // input pixel of the residue class
                 const int per = T.hc * T.wc;
                 const int n = m / per, t = m - n * per, i = t / T.wc, j = t - i * T.wc;
                 const int y = T.y0 + i * g.sr, x = T.x0 + j * g.sc;
                 const int yc = (y + g.pt - T.ca) / g.sr, xc = (x + g.pl - T.cb) / g.sc;
-                T.rowA[m] = make_int2(n * g.k * pq + yc * g.ow + xc, pack_yx(yc, xc));
+                int tag = pack_yx(yc, xc);
+                if (T.check == 1) {
+                    tag = 0;
+                    for (int r2 = 0; r2 < T.rt; r2++) for (int s2 = 0; s2 < T.st_; s2++)
+                        if ((unsigned)(yc - r2) < (unsigned)T.limY && (unsigned)(xc - s2) < (unsigned)T.limX) tag |= 1 << (r2 * T.st_ + s2);
+                }
+                T.rowA[m] = make_int2(n * g.k * pq + yc * g.ow + xc, tag);
                 T.outM[m] = n * g.c * hw + y * g.iw + x;
             } else if (T.mode == 3) {       // output pixel of dy; result column plane T[n][(c,r,s)][p][q]
                 const int n = m / pq, t = m - n * pq;
@@ -469,15 +496,15 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
             }
         } else if (i < (long long)T.M_total + T.K_pad) {
             const int k = (int)(i - T.M_total);
-            if (k >= T.K_total) { T.kA[k] = make_int2(0, pack_yx(INVALID_Y, 0)); T.kB[k] = -1; continue; }
+            if (k >= T.K_total) { T.kA[k] = make_int2(0, T.check == 1 ? 31 : pack_yx(INVALID_Y, 0)); T.kB[k] = -1; continue; }
             if (T.mode == 0) {              // (c, r, s)
                 const int c = k / rs, t = k - c * rs, r = t / g.kc, s = t - r * g.kc;
-                T.kA[k] = make_int2(c * hw + r * g.iw + s, pack_yx(r, s));
+                T.kA[k] = make_int2(c * hw + r * g.iw + s, T.check == 1 ? t : pack_yx(r, s));
                 T.kB[k] = k;
             } else if (T.mode == 1) {       // (f, r', s') with r = ca + r'*sr, s = cb + s'*sc
                 const int taps = T.rt * T.st_;
                 const int f = k / taps, t = k - f * taps, r2 = t / T.st_, s2 = t - r2 * T.st_;
-                T.kA[k] = make_int2(f * pq - r2 * g.ow - s2, pack_yx(-r2, -s2));
+                T.kA[k] = make_int2(f * pq - r2 * g.ow - s2, T.check == 1 ? t : pack_yx(-r2, -s2));
                 T.kB[k] = f * g.c * rs + (T.ca + r2 * g.sr) * g.kc + (T.cb + s2 * g.sc);
             } else if (T.mode == 3) {       // filter f
                 T.kA[k] = make_int2(k * pq, pack_yx(0, 0));
@@ -560,6 +587,18 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     const ConvGeom &g = T.g;
     const int mode = T.mode;
     T.K_pad = (T.K_total + BK - 1) / BK * BK;
+    // how the gathered operand is tested against the zero padding
+    T.limY = P.limY; T.limX = P.limX;
+    T.check = 2;
+    if (mode == 3) T.check = (T.K_total % BK == 0) ? 0 : 2;
+    else if (mode == 0) {
+        const bool inside = g.pt == 0 && g.pl == 0 && (g.oh - 1) * g.sr + g.kr <= g.ih && (g.ow - 1) * g.sc + g.kc <= g.iw;
+        T.check = (inside && T.K_total % BK == 0) ? 0 : (g.kr * g.kc <= 31 ? 1 : 2);
+    } else if (mode == 1) {
+        const bool inside = g.kr == 1 && g.kc == 1 && g.pt == 0 && g.pl == 0 && (g.ih - 1) / g.sr < g.oh && (g.iw - 1) / g.sc < g.ow;
+        T.check = (inside && T.K_total % BK == 0) ? 0 : (T.rt * T.st_ <= 31 ? 1 : 2);
+    }
+    P.check = T.check;
     const int bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);
     const int tiles_m = (T.M_total + BM - 1) / BM, tiles_n = (T.N_total + bn - 1) / bn;
     const int kblocks = T.K_pad / BK;

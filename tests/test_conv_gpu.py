@@ -131,3 +131,14 @@ def test_tensor_core_path_against_fma_path_and_tf32_mode(lib, shape):
         assert relerr(b[key], a[key]) <= 1e-5, key
         assert relerr(t[key], a[key]) <= 1e-3, key
     lib.call("sync", 0)     # also reports a pipeline time-out of the tensor-core kernel, if any
+
+
+def test_conv_empty_batch_and_long_reduction(lib):
+    """n = 0 is a no-op; a K = 9216 reduction (1024 channels x 3x3) stays within 1e-5 -- the tensor core's truncating
+    accumulation would drift to ~7e-5 there with a single accumulator."""
+    e = lib.empty((1,))
+    lib.call("conv2d_fwd", 0, e, e, None, e, 0, 4, 8, 8, 4, 3, 3, 8, 8, 1, 1, 1, 1, 0)
+    rng = np.random.default_rng(23)
+    x = rng.standard_normal((2, 1024, 6, 6)).astype(F); w = rng.standard_normal((32, 1024, 3, 3)).astype(F)
+    got = run_conv(lib, x, w, None, None, None, None, None, (1, 1), (1, 1, 1, 1))
+    assert relerr(got["y"], orc.conv2d_fwd(x, w, None, (1, 1), (1, 1, 1, 1))) <= 1e-5

@@ -351,3 +351,29 @@ def test_allocator_reuse_and_errors(lib):
         lib.call("free", 0, ctypes.c_void_p(12345))
     with pytest.raises(capi.Error):
         lib.call("conv2d_fwd", 0, b, b, None, b, 1, 0, 4, 4, 1, 3, 3, 2, 2, 1, 1, 0, 0, 0)   # c = 0 is rejected
+
+
+def test_fill_multi_and_profile_records(lib):
+    """Batched fills (one launch for many tensors, different values, ragged and unaligned sizes) and the per-call profile."""
+    rng = np.random.default_rng(9)
+    sizes = [1, 5, 4096, 16384, 16385, 100003, 0, 7]
+    vals = [0.0, 1.5, -2.0, 0.0, 3.25, 0.0, 9.0, -0.5]
+    bufs = [dev(lib, rnd(rng, s)) for s in sizes]
+    before = lib.launches()
+    lib.call("fill_multi", 0, (ctypes.c_void_p * len(bufs))(*[b.ptr.value for b in bufs]), (ctypes.c_size_t * len(sizes))(*sizes),
+             (ctypes.c_float * len(vals))(*vals), len(sizes))
+    assert lib.launches() - before == 1
+    for b, s, v in zip(bufs, sizes, vals):
+        np.testing.assert_array_equal(b.numpy(), np.full(s, v, F))
+    lib.call("profile_reset", 0); lib.call("profile_enable", 0, 1)
+    a = dev(lib, rnd(rng, 64, 32)); b = dev(lib, rnd(rng, 32, 16)); c = lib.empty((64, 16))
+    for _ in range(3):
+        lib.call("mult2d", 0, a, 0, b, 0, c, 0, 64, 16, 32)
+    lib.call("profile_enable", 0, 0)
+    n, ms, wk = ctypes.c_int(), (ctypes.c_double * 8)(), (ctypes.c_double * 8)()
+    lib.call("profile_records", 0, 7, ms, wk, 8, ctypes.byref(n))
+    assert n.value == 3 and all(wk[i] == 2.0 * 64 * 16 * 32 for i in range(3)) and all(ms[i] > 0 for i in range(3))
+    calls, tot, work = ctypes.c_ulonglong(), ctypes.c_double(), ctypes.c_double()
+    lib.call("profile_read", 0, 7, ctypes.byref(calls), ctypes.byref(tot), ctypes.byref(work))
+    assert calls.value == 3 and abs(tot.value - sum(ms[i] for i in range(3))) < 1e-9
+    lib.call("profile_reset", 0)

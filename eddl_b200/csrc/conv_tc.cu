@@ -33,6 +33,7 @@
 // bytes, which a tiled TMA copy requires, and the hi/lo split needs a pass through registers anyway.
 // Every wait on an mbarrier is bounded; on time-out the kernel records a status code, leaves
 // its loops, frees its tensor memory and returns.
+#include <cuda_bf16.h>
 #include "common.cuh"
 #include "conv_common.cuh"
 
@@ -54,6 +55,7 @@ struct TcParams {
     const float *bias;      // per n (forward only), may be null
     const int2 *rowA;       // [M_total]  .x = offset part, .y = (y << 16) | (x & 0xffff)
     const int2 *kA;         // [K_pad]
+    const int *kC;          // [K_pad]  compact form of kA for check 0 (offset) and check 1 ((offset << 5) | tap)
     const int *rowB;        // [N_total]
     const int *kB;          // [K_pad]    -1 = beyond K_total
     const int *outM;        // [M_total]
@@ -116,6 +118,10 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -141,6 +147,18 @@ __host__ __device__ constexpr uint32_t make_idesc(int bn) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+// fp32 accumulate, BF16 x BF16 (kind::f16), both operands K-major, M = 128, N = bn, K = 16 per instruction
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// byte offset of 16-byte chunk `chunk` of row `row` inside a [rows][128 bytes] SWIZZLE_128B tile
+__device__ __forceinline__ uint32_t swz_chunk(uint32_t row, uint32_t chunk) { return row * 128u + (((chunk ^ row) & 7u) << 4); }
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);          // a in the low half = the lower address
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
 __device__ __forceinline__ void split_tf32(float v, float &hi, float &lo) {
     hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
     lo = __fsub_rn(v, hi);
@@ -163,8 +181,9 @@ struct Layout {
 
 // Persistent, warp-specialised kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the
 // (split, filter tile, row tile) space.
-//   warps 0-7   producers: gather / split / store the A tile (and B for backward-weight); thread 0 also issues the TMA
-//               bulk copy of the packed weight tile.  The shared-memory ring keeps running across tile boundaries.
+//   warps 0-7   producers: gather / split / store the A tile (and B for backward-weight).  Forward / backward-data: two
+//               groups of four warps take alternate K-blocks, and the first thread of a group issues the TMA bulk copy
+//               of that block's packed weight tile.  The shared-memory ring keeps running across tile boundaries.
 //   warp  8     one lane issues the MMAs of a tile into one of the accumulator SETS in tensor memory.
 //   warps 9-12  epilogue: drain a finished set (tcgen05.ld), add its accumulators, store -- overlapped with the MMAs of
 //               the next tile whenever tensor memory holds two sets (BN <= 64, or short chains at BN = 128).
@@ -199,8 +218,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
     const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD + (B_TMA ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, NEPI); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, B_TMA ? NPROD / 64 + 1 : NPROD / 32); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, NEPI / 32); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -220,46 +239,121 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
 
     if (warp < 8) {
         // ============================ producers ============================
-        constexpr int RB = BN_ / 8;              // B rows per warp (backward-weight gather)
         constexpr uint32_t B_IMAGE = (uint32_t)L::B_BYTES * (SPLIT3 ? 2u : 1u);
-        float av[16], bv[RB];
-        const int arow = tid & (BM - 1), ahalf = tid >> 7;
-        int2 myRow = make_int2(0, INVALID_Y << 16);
-        int ry = INVALID_Y, rx = 0;
+        if constexpr (A_ROWMAJOR) {
+            // Two groups of four warps work on alternate K-blocks (group 0 the even ones of the CTA's K-block
+            // sequence, group 1 the odd ones), one thread per tile row and all 32 k of the block per thread.
+            // The groups drift out of phase, so one group's loads are in flight while the other splits and stores.
+            const int group = warp >> 2;
+            const int arow = tid & (BM - 1);
+            float av[BK];
+            int2 myRow = make_int2(0, INVALID_Y << 16);
+            int ry = INVALID_Y, rx = 0, row_tile = -1;
 
-        // issue the global loads of K-block `it` of tile `t` into registers
-        auto load_tiles = [&](int t, int kb0, int it) {
-            const int mn = t % tiles_mn;
-            const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
-            const int kbase = (kb0 + it) * BK;
-            if (A_ROWMAJOR) {
-                if (it == 0) {
-                    const int m = m0 + arow;
+            auto load_row = [&](int t, int kb0, int it) {
+                const int mn = t % tiles_mn;
+                if (mn != row_tile) {
+                    row_tile = mn;
+                    const int m = (mn % P.tiles_m) * BM + arow;
                     myRow = m < P.M_total ? __ldg(P.rowA + m) : make_int2(0, P.check == 1 ? 0 : (INVALID_Y << 16));
                     ry = myRow.y >> 16; rx = (int)(short)(myRow.y & 0xffff);
                 }
+                const int2 *kt = P.kA + (kb0 + it) * BK;
+                const int4 *kc = (const int4 *)(P.kC + (kb0 + it) * BK);     // warp-uniform: four k entries per load
                 const float *base = P.srcA + myRow.x;
                 if (P.check == 0) {
                     // every tap of every row is inside the image (1x1 and other unpadded shapes)
 #pragma unroll
-                    for (int i = 0; i < 16; i++) av[i] = __ldg(base + __ldg(&P.kA[kbase + ahalf * 16 + i].x));
+                    for (int i = 0; i < BK / 4; i++) {
+                        const int4 ke = __ldg(kc + i);
+                        av[4 * i + 0] = __ldg(base + ke.x); av[4 * i + 1] = __ldg(base + ke.y);
+                        av[4 * i + 2] = __ldg(base + ke.z); av[4 * i + 3] = __ldg(base + ke.w);
+                    }
                 } else if (P.check == 1) {
-                    // myRow.y holds one bit per filter tap; the k entry holds the tap number (31 = beyond K)
+                    // myRow.y holds one bit per filter tap; the k entry holds (offset << 5) | tap number (31 = beyond K)
+                    const unsigned taps = (unsigned)myRow.y;
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const int2 ke = __ldg(P.kA + kbase + ahalf * 16 + i);
-                        av[i] = ((unsigned)myRow.y >> ke.y) & 1u ? __ldg(base + ke.x) : 0.f;
+                    for (int i = 0; i < BK / 4; i++) {
+                        const int4 ke = __ldg(kc + i);
+                        av[4 * i + 0] = (taps >> (ke.x & 31)) & 1u ? __ldg(base + (ke.x >> 5)) : 0.f;
+                        av[4 * i + 1] = (taps >> (ke.y & 31)) & 1u ? __ldg(base + (ke.y >> 5)) : 0.f;
+                        av[4 * i + 2] = (taps >> (ke.z & 31)) & 1u ? __ldg(base + (ke.z >> 5)) : 0.f;
+                        av[4 * i + 3] = (taps >> (ke.w & 31)) & 1u ? __ldg(base + (ke.w >> 5)) : 0.f;
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const int2 ke = __ldg(P.kA + kbase + ahalf * 16 + i);
+                    for (int i = 0; i < BK; i++) {
+                        const int2 ke = __ldg(kt + i);
                         const int y = ry + (ke.y >> 16), x = rx + (int)(short)(ke.y & 0xffff);
                         const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
                         av[i] = ok ? __ldg(base + ke.x) : 0.f;
                     }
                 }
-            } else {
+            };
+            auto store_row = [&](int s) {
+                uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
+                uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
+                if (SPLIT3) {
+                    // plane 0: hi as TF32.  plane 1 (the cross-term operand, bf16, 64 values = one 128-byte row):
+                    // columns 0-31 = lo(k), columns 32-63 = hi(k); the weight image holds [hi | lo], so one chain of
+                    // bf16 MMAs over the 64 columns accumulates lo*hi + hi*lo.
+#pragma unroll
+                    for (int g = 0; g < BK / 8; g++) {
+                        float hi[8], lo[8];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) split_tf32(av[8 * g + j], hi[j], lo[j]);
+                        *(float4 *)(sA_hi + swz(arow, g * 8)) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+                        *(float4 *)(sA_hi + swz(arow, g * 8 + 4)) = make_float4(hi[4], hi[5], hi[6], hi[7]);
+                        *(uint4 *)(sA_lo + swz_chunk(arow, g)) =
+                            make_uint4(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]), pack_bf16(lo[4], lo[5]), pack_bf16(lo[6], lo[7]));
+                        *(uint4 *)(sA_lo + swz_chunk(arow, 4 + g)) =
+                            make_uint4(pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]), pack_bf16(hi[4], hi[5]), pack_bf16(hi[6], hi[7]));
+                    }
+                } else {
+#pragma unroll
+                    for (int g = 0; g < BK / 4; g++)
+                        *(float4 *)(sA_hi + swz(arow, g * 4)) = make_float4(av[4 * g], av[4 * g + 1], av[4 * g + 2], av[4 * g + 3]);
+                }
+            };
+
+            int t = blockIdx.x, kb0 = 0, nkb = 0, it = group;
+            // carry `it` over tile boundaries until it names a K-block of tile t
+            auto settle = [&]() {
+                while (t < total_tiles) {
+                    kb_range(t, kb0, nkb);
+                    if (it < nkb) return;
+                    it -= nkb; t += gridDim.x;
+                }
+            };
+            settle();
+            if (t < total_tiles) load_row(t, kb0, it);
+            for (int g = group; t < total_tiles; g += 2) {
+                const int s = g % STAGES;
+                const uint32_t par = ((g / STAGES) & 1) ^ 1;
+                if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+                if (arow == 0) {
+                    // packed weights of this K-block / filter tile: one bulk copy into the stage's B_hi|B_lo area
+                    const int n_tile = (t % tiles_mn) / P.tiles_m;
+                    const uint32_t dstB = smem_u32(stage_base + s * L::STAGE_BYTES + (SPLIT3 ? 2 : 1) * L::A_BYTES);
+                    const char *srcB = (const char *)P.packedB + ((size_t)(kb0 + it) * P.tiles_n + n_tile) * B_IMAGE;
+                    mbar_expect_tx(bar_full + 8 * s, B_IMAGE);
+                    tma_bulk_g2s(dstB, srcB, B_IMAGE, bar_full + 8 * s);
+                }
+                store_row(s);
+                fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
+                __syncwarp();                       // orders the other lanes' stores and fences before lane 0's arrive
+                if (lane == 0) mbar_arrive(bar_full + 8 * s);      // one arrive per warp: 32 lanes on one barrier word serialise
+                it += 2; settle();
+                if (t < total_tiles) load_row(t, kb0, it);
+            }
+        } else {
+            // backward-weight: all eight warps gather every K-block, one lane per k, 16 A rows and BN/8 B rows per warp
+            constexpr int RB = BN_ / 8;
+            float av[16], bv[RB];
+            auto load_tiles = [&](int t, int kb0, int it) {
+                const int mn = t % tiles_mn;
+                const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
+                const int kbase = (kb0 + it) * BK;
                 if (it == 0) {
                     // new tile: refresh the shared row tables (all 256 producer threads take this branch together)
                     asm volatile("bar.sync 1, 256;" ::: "memory");          // nobody still reads the previous tile's tables
@@ -284,27 +378,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     const int ro = sRowB[warp * RB + r];
                     bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
                 }
-            }
-        };
-        auto store_tiles = [&](int s) {
-            uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
-            uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
-            uint8_t *sB_hi = sA_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
-            uint8_t *sB_lo = sB_hi + L::B_BYTES;
-            if (A_ROWMAJOR) {
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    const uint32_t off = swz(arow, ahalf * 16 + g * 4);
-                    if (SPLIT3) {
-                        float4 hi, lo;
-                        split_tf32(av[4 * g + 0], hi.x, lo.x); split_tf32(av[4 * g + 1], hi.y, lo.y);
-                        split_tf32(av[4 * g + 2], hi.z, lo.z); split_tf32(av[4 * g + 3], hi.w, lo.w);
-                        *(float4 *)(sA_hi + off) = hi; *(float4 *)(sA_lo + off) = lo;
-                    } else {
-                        *(float4 *)(sA_hi + off) = make_float4(av[4 * g], av[4 * g + 1], av[4 * g + 2], av[4 * g + 3]);
-                    }
-                }
-            } else {
+            };
+            auto store_tiles = [&](int s) {
+                uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
+                uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
+                uint8_t *sB_hi = sA_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
+                uint8_t *sB_lo = sB_hi + L::B_BYTES;
 #pragma unroll
                 for (int r = 0; r < 16; r++) {
                     const uint32_t off = swz(warp * 16 + r, lane);
@@ -317,29 +396,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     if (SPLIT3) { float hi, lo; split_tf32(bv[r], hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
                     else *(float *)(sB_hi + off) = bv[r];
                 }
-            }
-        };
+            };
 
-        int t = blockIdx.x, kb0 = 0, nkb = 0, it = 0;
-        if (t < total_tiles) { kb_range(t, kb0, nkb); load_tiles(t, kb0, 0); }
-        for (int g = 0; t < total_tiles; g++) {
-            const int s = g % STAGES;
-            const uint32_t par = ((g / STAGES) & 1) ^ 1;
-            if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
-            if (B_TMA && tid == 0) {
-                // packed weights of this K-block / filter tile: one bulk copy into the stage's B_hi|B_lo area
-                const int n_tile = (t % tiles_mn) / P.tiles_m;
-                const uint32_t dstB = smem_u32(stage_base + s * L::STAGE_BYTES + (SPLIT3 ? 2 : 1) * L::A_BYTES);
-                const char *srcB = (const char *)P.packedB + ((size_t)(kb0 + it) * P.tiles_n + n_tile) * B_IMAGE;
-                mbar_expect_tx(bar_full + 8 * s, B_IMAGE);
-                tma_bulk_g2s(dstB, srcB, B_IMAGE, bar_full + 8 * s);
+            int t = blockIdx.x, kb0 = 0, nkb = 0, it = 0;
+            if (t < total_tiles) { kb_range(t, kb0, nkb); load_tiles(t, kb0, 0); }
+            for (int g = 0; t < total_tiles; g++) {
+                const int s = g % STAGES;
+                const uint32_t par = ((g / STAGES) & 1) ^ 1;
+                if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+                store_tiles(s);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                // advance to the next K-block (possibly of the next tile) and start its loads
+                if (++it == nkb) { t += gridDim.x; it = 0; if (t < total_tiles) kb_range(t, kb0, nkb); }
+                if (t < total_tiles) load_tiles(t, kb0, it);
             }
-            store_tiles(s);
-            fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
-            mbar_arrive(bar_full + 8 * s);
-            // advance to the next K-block (possibly of the next tile) and start its loads
-            if (++it == nkb) { t += gridDim.x; it = 0; if (t < total_tiles) kb_range(t, kb0, nkb); }
-            if (t < total_tiles) load_tiles(t, kb0, it);
         }
     } else if (warp == 8) {
         // ============================ MMA issuer (one thread) ============================
@@ -367,8 +439,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                         const uint32_t d_main = set_base + (uint32_t)((step % P.nmain) * BN_);
                         if (SPLIT3) {
                             const uint32_t d_small = set_base + (uint32_t)small_off;
-                            umma_tf32(d_small, make_desc(a_lo + o), make_desc(b_hi + o), idesc, step > 0 ? 1u : 0u);
-                            umma_tf32(d_small, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
+                            if (WGRAD) {
+                                umma_tf32(d_small, make_desc(a_lo + o), make_desc(b_hi + o), idesc, step > 0 ? 1u : 0u);
+                                umma_tf32(d_small, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
+                            } else {
+                                // cross terms in bf16: 16 of the 64 [lo | hi] x [hi | lo] columns per instruction
+                                umma_bf16(d_small, make_desc(a_lo + o), make_desc(b_lo + o), make_idesc_bf16(BN_), step > 0 ? 1u : 0u);
+                            }
                         }
                         umma_tf32(d_main, make_desc(a_hi + o), make_desc(b_hi + o), idesc, step >= P.nmain ? 1u : 0u);
                     }
@@ -406,7 +483,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 if (c == (BN_ + 31) / 32 - 1) {
                     // all of this set has been read: hand it back to the MMA warp before the global stores
                     tc_fence_before();
-                    mbar_arrive(bar_acc_empty + 8 * set);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_acc_empty + 8 * set);
                 }
                 if (m_ok) {
                     float *col0 = obase + (long long)(n0 + c * 32) * P.out_n_stride;
@@ -450,7 +528,7 @@ struct TableArgs {
     // backward pass into sr*sc dense stride-1 problems with no wasted taps.
     int ca, cb, y0, x0, hc, wc, rt, st_;
     int check, limY, limX;   // check == 1: rowA.y = bitmask over taps, kA.y = tap number
-    int2 *rowA, *kA; int *rowB, *kB, *outM;
+    int2 *rowA, *kA; int *rowB, *kB, *outM, *kC;
     int M_total, N_total, K_total, K_pad;
 };
 
@@ -496,7 +574,7 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
             }
         } else if (i < (long long)T.M_total + T.K_pad) {
             const int k = (int)(i - T.M_total);
-            if (k >= T.K_total) { T.kA[k] = make_int2(0, T.check == 1 ? 31 : pack_yx(INVALID_Y, 0)); T.kB[k] = -1; continue; }
+            if (k >= T.K_total) { T.kA[k] = make_int2(0, T.check == 1 ? 31 : pack_yx(INVALID_Y, 0)); T.kC[k] = 31; T.kB[k] = -1; continue; }
             if (T.mode == 0) {              // (c, r, s)
                 const int c = k / rs, t = k - c * rs, r = t / g.kc, s = t - r * g.kc;
                 T.kA[k] = make_int2(c * hw + r * g.iw + s, T.check == 1 ? t : pack_yx(r, s));
@@ -514,6 +592,8 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
                 T.kA[k] = make_int2(n * g.c * hw + p * g.sr * g.iw + q * g.sc, pack_yx(p * g.sr, q * g.sc));
                 T.kB[k] = n * g.k * pq + t;
             }
+            const int2 ka = T.kA[k];
+            T.kC[k] = T.check == 0 ? ka.x : T.check == 1 ? (int)(((unsigned)ka.x << 5) | (unsigned)ka.y) : 0;
         } else {
             const int n = (int)(i - T.M_total - T.K_pad);
             if (T.mode == 0) T.rowB[n] = n * T.K_total;         // filter row of w[f][c*r*s]
@@ -539,8 +619,14 @@ __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ s
         const int ko = kB[kb * BK + k];
         const float v = (n < n_total && ko >= 0) ? __ldg(src + rowB[n] + ko) : 0.f;
         const uint32_t off = swz(row, k);
-        if (SPLIT3) { float hi, lo; split_tf32(v, hi, lo); *(float *)(img + off) = hi; *(float *)(img + (size_t)bn * BK * 4 + off) = lo; }
-        else *(float *)(img + off) = v;
+        if (SPLIT3) {
+            // plane 0: hi as TF32; plane 1: bf16 row of 64 = [hi(0..31) | lo(0..31)], the partner of the A rows' [lo | hi]
+            float hi, lo; split_tf32(v, hi, lo);
+            *(float *)(img + off) = hi;
+            char *x = img + (size_t)bn * BK * 4;
+            *(__nv_bfloat16 *)(x + swz_chunk(row, k >> 3) + (k & 7) * 2) = __float2bfloat16_rn(hi);
+            *(__nv_bfloat16 *)(x + swz_chunk(row, 4 + (k >> 3)) + (k & 7) * 2) = __float2bfloat16_rn(lo);
+        } else *(float *)(img + off) = v;
     }
 }
 
@@ -598,6 +684,8 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         const bool inside = g.kr == 1 && g.kc == 1 && g.pt == 0 && g.pl == 0 && (g.ih - 1) / g.sr < g.oh && (g.iw - 1) / g.sc < g.ow;
         T.check = (inside && T.K_total % BK == 0) ? 0 : (T.rt * T.st_ <= 31 ? 1 : 2);
     }
+    // the compact k table keeps 27 bits of offset beside the 5-bit tap number
+    if (T.check == 1 && (long long)(g.c > g.k ? g.c : g.k) * (g.ih * g.iw > g.oh * g.ow ? g.ih * g.iw : g.oh * g.ow) + (long long)(g.kr + 1) * (g.iw + g.ow) >= (1ll << 26)) T.check = 2;
     P.check = T.check;
     const int bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);
     const int tiles_m = (T.M_total + BM - 1) / BM, tiles_n = (T.N_total + bn - 1) / bn;
@@ -616,7 +704,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     size_t off = 0;
     auto carve = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };
     const size_t o_rowA = carve((size_t)T.M_total * 8), o_kA = carve((size_t)T.K_pad * 8), o_rowB = carve((size_t)T.N_total * 4),
-                 o_kB = carve((size_t)T.K_pad * 4), o_outM = carve((size_t)T.M_total * 4),
+                 o_kB = carve((size_t)T.K_pad * 4), o_kC = carve((size_t)T.K_pad * 4), o_outM = carve((size_t)T.M_total * 4),
                  o_part = carve(splits > 1 ? out_total * splits * sizeof(float) : 0),
                  o_pack = carve(mode != 2 ? (size_t)kblocks * tiles_n * bn * BK * sizeof(float) * (precision == 0 ? 2 : 1) : 0);
     char *ws = (char *)scratch(cx, off);
@@ -625,7 +713,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         if (cudaMalloc((void **)&g_status[dev], sizeof(int)) != cudaSuccess) return cudaErrorMemoryAllocation;
         cudaMemsetAsync(g_status[dev], 0, sizeof(int), st);
     }
-    T.rowA = (int2 *)(ws + o_rowA); T.kA = (int2 *)(ws + o_kA); T.rowB = (int *)(ws + o_rowB); T.kB = (int *)(ws + o_kB); T.outM = (int *)(ws + o_outM);
+    T.rowA = (int2 *)(ws + o_rowA); T.kA = (int2 *)(ws + o_kA); T.rowB = (int *)(ws + o_rowB); T.kB = (int *)(ws + o_kB); T.outM = (int *)(ws + o_outM); T.kC = (int *)(ws + o_kC);
     const long long entries = (long long)T.M_total + T.K_pad + T.N_total;
     build_tables_kernel<<<grid_for((size_t)entries, 256), 256, 0, st>>>(T);
     EB_LAUNCH_CHECK("conv_tc(tables)");
@@ -638,7 +726,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         P.packedB = (const float *)(ws + o_pack);
     }
     P.srcA = srcA; P.srcB = srcB;
-    P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM;
+    P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM; P.kC = T.kC;
     P.M_total = T.M_total; P.N_total = T.N_total; P.K_pad = T.K_pad;
     P.kblocks_per_split = kbs;
     P.tiles_m = tiles_m; P.tiles_n = tiles_n; P.splits = splits;

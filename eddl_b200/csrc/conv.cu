@@ -76,7 +76,7 @@ int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bi
     EB_CTX(dev);
     ConvGeom g{n, c, ih, iw, k, kr, kc, oh, ow, sr, sc, pad_top, pad_left};
     if (int r = check("gpu_conv2D", g)) return r;
-    EB_REQUIRE(x && w && y, "gpu_conv2D");
+    EB_REQUIRE(x && w && y && precision >= 0 && precision <= 2, "gpu_conv2D");
     if (n == 0) return 0;
     ProfScope prof(cx, PROF_CONV_FWD, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
@@ -92,7 +92,7 @@ int eddlb200_conv2d_bwd_data(int dev, const float *dy, const float *w, float *dx
     EB_CTX(dev);
     ConvGeom g{n, c, ih, iw, k, kr, kc, oh, ow, sr, sc, pad_top, pad_left};
     if (int r = check("gpu_conv2D_back", g)) return r;
-    EB_REQUIRE(dy && w && dx, "gpu_conv2D_back");
+    EB_REQUIRE(dy && w && dx && precision >= 0 && precision <= 2, "gpu_conv2D_back");
     if (n == 0) return 0;
     ProfScope prof(cx, PROF_CONV_BWD_DATA, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
@@ -108,7 +108,7 @@ int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *
     EB_CTX(dev);
     ConvGeom g{n, c, ih, iw, k, kr, kc, oh, ow, sr, sc, pad_top, pad_left};
     if (int r = check("gpu_conv2D_grad", g)) return r;
-    EB_REQUIRE(x && dy && gw, "gpu_conv2D_grad");
+    EB_REQUIRE(x && dy && gw && precision >= 0 && precision <= 2, "gpu_conv2D_grad");
     if (n == 0) return 0;
     ProfScope prof(cx, PROF_CONV_BWD_WEIGHT, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (gbias) {

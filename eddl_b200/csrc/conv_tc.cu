@@ -18,7 +18,10 @@
 //
 // fp32-equivalent mode (precision 0) is the 3xTF32 split: every operand value v is staged as
 // hi = v with the 13 low mantissa bits cleared and lo = v - hi (exact), and each k-step issues
-// hi*hi + lo*hi + hi*lo into the same fp32 accumulator.  precision 1 issues hi*hi only.
+// hi*hi + lo*hi + hi*lo into the same fp32 accumulator.  precision 1 issues hi*hi only.  precision 2 keeps the
+// TF32 hi*hi chain and computes the two cross terms as ONE bf16 MMA chain ([lo | hi] x [hi | lo] concatenated along k,
+// a third fewer tensor-core and shared-memory cycles); its error is about four times that of precision 0 (bf16 rounding
+// of the cross-term operands, ~2^-20 per product), still inside 1e-5, and it is opt-in.
 //
 // The tensor core adds each MMA into the fp32 accumulator with truncation, so a long chain of
 // accumulations drifts toward zero in proportion to its length (measured: 3e-5 relative at K = 4096
@@ -175,7 +178,7 @@ struct Layout {
     static constexpr int B_BYTES = BN_ * BK * 4;
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (SPLIT3 ? 2 : 1);
     static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 4 ? 4 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int TABLE_BYTES = BM * 8 + BN_ * 4;     // backward-weight row tables
+    static constexpr int TABLE_BYTES = 2 * (BM * 8 + BN_ * 4);     // backward-weight row tables, one copy per producer group
     static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + TABLE_BYTES + 256;
 };
 
@@ -189,8 +192,10 @@ struct Layout {
 //               the next tile whenever tensor memory holds two sets (BN <= 64, or short chains at BN = 128).
 // WGRAD = false (forward, backward-data): A rows are pixels (one thread per row, vector stores); B is the weight operand,
 // prepared once per call by pack_b_kernel.  WGRAD = true (backward-weight): A and B are gathered with one lane per k.
-template <int BN_, bool SPLIT3, bool WGRAD>
+template <int BN_, int PREC, bool WGRAD>
 __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P) {
+    constexpr bool SPLIT3 = PREC != 1;                   // operands staged as hi / lo planes
+    constexpr bool CROSS_BF16 = PREC == 2 && !WGRAD;     // cross terms as one bf16 MMA chain
     using L = Layout<BN_, SPLIT3>;
     constexpr int STAGES = L::STAGES;
     constexpr bool A_ROWMAJOR = !WGRAD;
@@ -199,8 +204,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *stage_base = smem;
     int2 *sRowA = (int2 *)(smem + STAGES * L::STAGE_BYTES);          // backward-weight: row entries of the current tile
-    int *sRowB = (int *)(sRowA + BM);
-    uint64_t *bars = (uint64_t *)(sRowB + BN_);                      // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    int *sRowB = (int *)(sRowA + 2 * BM);
+    uint64_t *bars = (uint64_t *)(sRowB + 2 * BN_);                      // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
@@ -218,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
     const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, B_TMA ? NPROD / 64 + 1 : NPROD / 32); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD / 64 + (B_TMA ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); }
         for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, NEPI / 32); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -293,7 +298,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             auto store_row = [&](int s) {
                 uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
                 uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
-                if (SPLIT3) {
+                if (CROSS_BF16) {
                     // plane 0: hi as TF32.  plane 1 (the cross-term operand, bf16, 64 values = one 128-byte row):
                     // columns 0-31 = lo(k), columns 32-63 = hi(k); the weight image holds [hi | lo], so one chain of
                     // bf16 MMAs over the 64 columns accumulates lo*hi + hi*lo.
@@ -308,6 +313,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                             make_uint4(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]), pack_bf16(lo[4], lo[5]), pack_bf16(lo[6], lo[7]));
                         *(uint4 *)(sA_lo + swz_chunk(arow, 4 + g)) =
                             make_uint4(pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]), pack_bf16(hi[4], hi[5]), pack_bf16(hi[6], hi[7]));
+                    }
+                } else if (SPLIT3) {
+#pragma unroll
+                    for (int g = 0; g < BK / 4; g++) {
+                        const uint32_t off = swz(arow, g * 4);
+                        float4 hi, lo;
+                        split_tf32(av[4 * g + 0], hi.x, lo.x); split_tf32(av[4 * g + 1], hi.y, lo.y);
+                        split_tf32(av[4 * g + 2], hi.z, lo.z); split_tf32(av[4 * g + 3], hi.w, lo.w);
+                        *(float4 *)(sA_hi + off) = hi; *(float4 *)(sA_lo + off) = lo;
                     }
                 } else {
 #pragma unroll
@@ -347,26 +361,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 if (t < total_tiles) load_row(t, kb0, it);
             }
         } else {
-            // backward-weight: all eight warps gather every K-block, one lane per k, 16 A rows and BN/8 B rows per warp
-            constexpr int RB = BN_ / 8;
-            float av[16], bv[RB];
-            auto load_tiles = [&](int t, int kb0, int it) {
-                const int mn = t % tiles_mn;
-                const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
-                const int kbase = (kb0 + it) * BK;
-                if (it == 0) {
-                    // new tile: refresh the shared row tables (all 256 producer threads take this branch together)
-                    asm volatile("bar.sync 1, 256;" ::: "memory");          // nobody still reads the previous tile's tables
-                    if (tid < BM) sRowA[tid] = (m0 + tid < P.M_total) ? __ldg(P.rowA + m0 + tid) : make_int2(0, INVALID_Y << 16);
-                    else if (tid - BM < BN_) sRowB[tid - BM] = (n0 + tid - BM < P.N_total) ? __ldg(P.rowB + n0 + tid - BM) : -1;
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
+            // backward-weight: one lane per k.  As above, two groups of four warps take alternate K-blocks; a warp gathers
+            // 32 A rows and BN/4 B rows of its group's block.  Each group keeps its own copy of the tile's row tables.
+            constexpr int RA = BM / 4, RB = BN_ / 4;
+            const int group = warp >> 2, wq = warp & 3, gtid = tid & 127;
+            int2 *rowsA = sRowA + group * BM;
+            int *rowsB = sRowB + group * BN_;
+            float av[RA], bv[RB];
+            int row_tile = -1;
+            auto load_tiles = [&](int mn, int kblock) {
+                if (mn != row_tile) {
+                    // new tile: refresh the group's row tables (all 128 threads of the group take this branch together)
+                    row_tile = mn;
+                    const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
+                    asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");      // nobody still reads the previous tile's tables
+                    rowsA[gtid] = (m0 + gtid < P.M_total) ? __ldg(P.rowA + m0 + gtid) : make_int2(0, INVALID_Y << 16);
+                    if (gtid < BN_) rowsB[gtid] = (n0 + gtid < P.N_total) ? __ldg(P.rowB + n0 + gtid) : -1;
+                    asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
                 }
+                const int kbase = kblock * BK;
                 const int2 ke = __ldg(P.kA + kbase + lane);
                 const int ky = ke.y >> 16, kx = (int)(short)(ke.y & 0xffff);
                 const float *base = P.srcA + ke.x;
 #pragma unroll
-                for (int r = 0; r < 16; r++) {
-                    const int2 re = sRowA[warp * 16 + r];
+                for (int r = 0; r < RA; r++) {
+                    const int2 re = rowsA[wq * RA + r];
                     const int y = (re.y >> 16) + ky, x = (int)(short)(re.y & 0xffff) + kx;
                     const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
                     av[r] = ok ? __ldg(base + re.x) : 0.f;
@@ -375,7 +394,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
 #pragma unroll
                 for (int r = 0; r < RB; r++) {
-                    const int ro = sRowB[warp * RB + r];
+                    const int ro = rowsB[wq * RB + r];
                     bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
                 }
             };
@@ -385,22 +404,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 uint8_t *sB_hi = sA_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
                 uint8_t *sB_lo = sB_hi + L::B_BYTES;
 #pragma unroll
-                for (int r = 0; r < 16; r++) {
-                    const uint32_t off = swz(warp * 16 + r, lane);
+                for (int r = 0; r < RA; r++) {
+                    const uint32_t off = swz(wq * RA + r, lane);
                     if (SPLIT3) { float hi, lo; split_tf32(av[r], hi, lo); *(float *)(sA_hi + off) = hi; *(float *)(sA_lo + off) = lo; }
                     else *(float *)(sA_hi + off) = av[r];
                 }
 #pragma unroll
                 for (int r = 0; r < RB; r++) {
-                    const uint32_t off = swz(warp * RB + r, lane);
+                    const uint32_t off = swz(wq * RB + r, lane);
                     if (SPLIT3) { float hi, lo; split_tf32(bv[r], hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
                     else *(float *)(sB_hi + off) = bv[r];
                 }
             };
 
-            int t = blockIdx.x, kb0 = 0, nkb = 0, it = 0;
-            if (t < total_tiles) { kb_range(t, kb0, nkb); load_tiles(t, kb0, 0); }
-            for (int g = 0; t < total_tiles; g++) {
+            int t = blockIdx.x, kb0 = 0, nkb = 0, it = group;
+            auto settle = [&]() {
+                while (t < total_tiles) {
+                    kb_range(t, kb0, nkb);
+                    if (it < nkb) return;
+                    it -= nkb; t += gridDim.x;
+                }
+            };
+            settle();
+            if (t < total_tiles) load_tiles(t % tiles_mn, kb0 + it);
+            for (int g = group; t < total_tiles; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
                 if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
@@ -408,9 +435,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);
-                // advance to the next K-block (possibly of the next tile) and start its loads
-                if (++it == nkb) { t += gridDim.x; it = 0; if (t < total_tiles) kb_range(t, kb0, nkb); }
-                if (t < total_tiles) load_tiles(t, kb0, it);
+                it += 2; settle();
+                if (t < total_tiles) load_tiles(t % tiles_mn, kb0 + it);
             }
         }
     } else if (warp == 8) {
@@ -439,7 +465,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                         const uint32_t d_main = set_base + (uint32_t)((step % P.nmain) * BN_);
                         if (SPLIT3) {
                             const uint32_t d_small = set_base + (uint32_t)small_off;
-                            if (WGRAD) {
+                            if (!CROSS_BF16) {
                                 umma_tf32(d_small, make_desc(a_lo + o), make_desc(b_hi + o), idesc, step > 0 ? 1u : 0u);
                                 umma_tf32(d_small, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
                             } else {
@@ -607,10 +633,11 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
 // B operand of forward / backward-data (the weights), prepared once per call: for every (K-block, filter tile) the
 // [BN x 32] tile is written in the exact shared-memory image the MMA reads (K-major SWIZZLE_128B), hi plane then lo
 // plane, so the main kernel fetches it with a single 16-byte-aligned TMA bulk copy.
-template <bool SPLIT3>
+template <int PREC>
 __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ src, const int *__restrict__ rowB, const int *__restrict__ kB,
                                                      float *__restrict__ packed, int bn, int n_total, int tiles_n) {
     const int kb = blockIdx.x, nt = blockIdx.y;
+    constexpr bool SPLIT3 = PREC != 1;
     const size_t image_floats = (size_t)bn * BK * (SPLIT3 ? 2 : 1);
     char *img = (char *)(packed + ((size_t)kb * tiles_n + nt) * image_floats);
     for (int e = threadIdx.x; e < bn * BK; e += blockDim.x) {
@@ -619,7 +646,8 @@ __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ s
         const int ko = kB[kb * BK + k];
         const float v = (n < n_total && ko >= 0) ? __ldg(src + rowB[n] + ko) : 0.f;
         const uint32_t off = swz(row, k);
-        if (SPLIT3) {
+        if (PREC == 0) { float hi, lo; split_tf32(v, hi, lo); *(float *)(img + off) = hi; *(float *)(img + (size_t)bn * BK * 4 + off) = lo; }
+        else if (PREC == 2) {
             // plane 0: hi as TF32; plane 1: bf16 row of 64 = [hi(0..31) | lo(0..31)], the partner of the A rows' [lo | hi]
             float hi, lo; split_tf32(v, hi, lo);
             *(float *)(img + off) = hi;
@@ -630,26 +658,26 @@ __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ s
     }
 }
 
-template <int BN_, bool SPLIT3, bool WGRAD>
+template <int BN_, int PREC, bool WGRAD>
 int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
-    using L = Layout<BN_, SPLIT3>;
+    using L = Layout<BN_, PREC != 1>;
     static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
     bool &configured = configured_dev[dev];
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, SPLIT3, WGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, PREC, WGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e, "conv_tc(smem attribute)");
         configured = true;
     }
-    igemm_tc_kernel<BN_, SPLIT3, WGRAD><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
+    igemm_tc_kernel<BN_, PREC, WGRAD><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
     EB_LAUNCH_CHECK("conv_tc");
     return 0;
 }
 
-template <bool SPLIT3, bool WGRAD>
+template <int PREC, bool WGRAD>
 int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn, int dev) {
-    if (bn == 32) return launch_variant<32, SPLIT3, WGRAD>(cx, st, P, grid, dev);
-    if (bn == 64) return launch_variant<64, SPLIT3, WGRAD>(cx, st, P, grid, dev);
-    return launch_variant<128, SPLIT3, WGRAD>(cx, st, P, grid, dev);
+    if (bn == 32) return launch_variant<32, PREC, WGRAD>(cx, st, P, grid, dev);
+    if (bn == 64) return launch_variant<64, PREC, WGRAD>(cx, st, P, grid, dev);
+    return launch_variant<128, PREC, WGRAD>(cx, st, P, grid, dev);
 }
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
@@ -690,13 +718,24 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     const int bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);
     const int tiles_m = (T.M_total + BM - 1) / BM, tiles_n = (T.N_total + bn - 1) / bn;
     const int kblocks = T.K_pad / BK;
+    // Split the reduction so that the persistent CTAs finish together: the makespan of `tiles * splits` work items dealt
+    // round-robin to the SMs is ceil(items / SMs) rounds of (K-blocks per split + one epilogue); splitting also costs a
+    // write and a read of every partial output.  Pick the split count with the smallest estimate (microseconds).
     int splits = 1;
     const int tiles = tiles_m * tiles_n;
-    if (allow_split && tiles < EDDLB200_NUM_SMS * 2) {
-        splits = (EDDLB200_NUM_SMS * 2 + tiles - 1) / tiles;
-        if (splits > kblocks / 4) splits = kblocks / 4;
-        if (splits > 128) splits = 128;
-        if (splits < 1) splits = 1;
+    if (allow_split && kblocks >= 8) {
+        const double t_kblock = mode == 2 ? 2.5 : 1.0, t_epilogue = 3.0;
+        const int max_splits = kblocks / 4 < 128 ? kblocks / 4 : 128;
+        double best = 1e30;
+        for (int sp = 1; sp <= max_splits; sp++) {
+            const int kb = (kblocks + sp - 1) / sp;
+            const int sp_eff = (kblocks + kb - 1) / kb;
+            if (sp_eff != sp) continue;
+            const long long rounds = ((long long)tiles * sp + EDDLB200_NUM_SMS - 1) / EDDLB200_NUM_SMS;
+            double cost = (double)rounds * (kb * t_kblock + t_epilogue);
+            if (sp > 1) cost += 3.0 + 2.0 * (double)out_total * sizeof(float) * sp / 6.0e6;
+            if (cost < best * 0.97) { best = cost; splits = sp; }      // prefer fewer splits unless the gain is clear
+        }
     }
     const int kbs = (kblocks + splits - 1) / splits;
     splits = (kblocks + kbs - 1) / kbs;
@@ -706,7 +745,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     const size_t o_rowA = carve((size_t)T.M_total * 8), o_kA = carve((size_t)T.K_pad * 8), o_rowB = carve((size_t)T.N_total * 4),
                  o_kB = carve((size_t)T.K_pad * 4), o_kC = carve((size_t)T.K_pad * 4), o_outM = carve((size_t)T.M_total * 4),
                  o_part = carve(splits > 1 ? out_total * splits * sizeof(float) : 0),
-                 o_pack = carve(mode != 2 ? (size_t)kblocks * tiles_n * bn * BK * sizeof(float) * (precision == 0 ? 2 : 1) : 0);
+                 o_pack = carve(mode != 2 ? (size_t)kblocks * tiles_n * bn * BK * sizeof(float) * (precision != 1 ? 2 : 1) : 0);
     char *ws = (char *)scratch(cx, off);
     if (!ws) return cudaErrorMemoryAllocation;
     if (!g_status[dev]) {
@@ -720,8 +759,9 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     P.packedB = nullptr;
     if (mode != 2) {
         dim3 pgrid(kblocks, tiles_n);
-        if (precision == 0) pack_b_kernel<true><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
-        else pack_b_kernel<false><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
+        if (precision == 0) pack_b_kernel<0><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
+        else if (precision == 2) pack_b_kernel<2><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
+        else pack_b_kernel<1><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
         EB_LAUNCH_CHECK("conv_tc(pack weights)");
         P.packedB = (const float *)(ws + o_pack);
     }
@@ -738,9 +778,11 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     const long long total_tiles = (long long)tiles_m * tiles_n * splits;
     dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
     int r;
-    const bool split3 = precision == 0;
-    if (mode == 2) r = split3 ? launch_bn<true, true>(cx, st, P, grid, bn, dev) : launch_bn<false, true>(cx, st, P, grid, bn, dev);
-    else r = split3 ? launch_bn<true, false>(cx, st, P, grid, bn, dev) : launch_bn<false, false>(cx, st, P, grid, bn, dev);
+    // backward-weight has no bf16 variant: precision 2 runs it as precision 0
+    if (mode == 2) r = precision != 1 ? launch_bn<0, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true>(cx, st, P, grid, bn, dev);
+    else if (precision == 0) r = launch_bn<0, false>(cx, st, P, grid, bn, dev);
+    else if (precision == 2) r = launch_bn<2, false>(cx, st, P, grid, bn, dev);
+    else r = launch_bn<1, false>(cx, st, P, grid, bn, dev);
     if (r) return r;
     if (splits > 1) {
         if (mode == 0) {

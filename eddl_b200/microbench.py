@@ -1,6 +1,6 @@
 """Kernel microbenchmarks through the C ABI (CUDA-event timed, L2 flushed between timed launches).
 
-    python -m eddl_b200.microbench conv [--precision 0|1] [--batch-scale 1.0] [--iters 5]
+    python -m eddl_b200.microbench conv [--precision 0|1|2] [--batch-scale 1.0] [--iters 5]
     python -m eddl_b200.microbench hbm
     python -m eddl_b200.microbench allreduce          (under torchrun for N > 1)
 
@@ -67,7 +67,7 @@ def run_conv(args):
             fn(); fn(); fn(); L.sync(dev)
             med, best = _timed(L, dev, fn, args.iters, flush)
             print(json.dumps({"bench": "conv", "pass": name, "shape": {"n": n, "c": c, "h": h, "w": w, "k": k, "kr": kr, "kc": kc, "stride": st, "pad": pad},
-                              "precision": "3xTF32" if args.precision == 0 else "TF32", "gflop": flops / 1e9, "ms": med, "ms_best": best,
+                              "precision": {0: "3xTF32", 1: "TF32", 2: "TF32+bf16 cross terms"}[args.precision], "gflop": flops / 1e9, "ms": med, "ms_best": best,
                               "tflops": flops / (med * 1e-3) / 1e12}), flush=True)
         L.sync(dev)
 

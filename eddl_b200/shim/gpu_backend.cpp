@@ -221,7 +221,7 @@ void gpu_accuracy(Tensor *A, Tensor *B, int *acc) {
 namespace {
 int conv_precision() {
     static int v = -1;
-    if (v < 0) { const char *e = getenv("EDDL_B200_CONV_PRECISION"); v = (e && (e[0] == 't' || e[0] == 'T' || e[0] == '1')) ? 1 : 0; }
+    if (v < 0) { const char *e = getenv("EDDL_B200_CONV_PRECISION"); v = (e && (e[0] == 't' || e[0] == 'T' || e[0] == '1')) ? 1 : (e && (e[0] == 'b' || e[0] == 'B' || e[0] == '2')) ? 2 : 0; }
     return v;
 }
 }

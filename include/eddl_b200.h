@@ -181,7 +181,9 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
 /* ---- Conv2D (src/hardware/gpu/nn/gpu_conv.cu:159-372;
  *      src/hardware/cpu/nn/cpu_conv.cpp:114-280,316-527).  Cross-correlation, zero padding,
  *      x [n,c,ih,iw], w [k,c,kr,kc], y [n,k,oh,ow].  precision: 0 = fp32-equivalent
- *      (3xTF32 split on the tensor cores or fp32 FMA), 1 = plain TF32. */
+ *      (3xTF32 split on the tensor cores or fp32 FMA), 1 = plain TF32, 2 = TF32 main product plus
+ *      bf16 cross terms of the split (forward and backward-data; about four times the rounding error
+ *      of 0, still below 1e-5 relative; backward-weight runs as 0).  Any other value is EINVAL. */
 /* Options: "conv_path" 0 = tensor-core kernel where it applies (default), 1 = fp32 FMA kernel only. */
 int eddlb200_set_option(const char *name, int value);
 int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias /* may be null */, float *y,

@@ -114,7 +114,8 @@ def test_conv_linearity_at_benchmark_size(lib):
 
 @pytest.mark.parametrize("shape", [(4, 64, 14, 14, 96, 3, 3, 1, (1, 1, 1, 1)), (2, 48, 9, 9, 40, 1, 1, 1, (0, 0, 0, 0)), (2, 16, 20, 20, 24, 3, 3, 2, (1, 1, 1, 1))])
 def test_tensor_core_path_against_fma_path_and_tf32_mode(lib, shape):
-    """The tcgen05 kernel (3xTF32) and the fp32 FMA kernel agree to 1e-5; plain TF32 (precision 1) stays within 1e-3."""
+    """The tcgen05 kernel (3xTF32) and the fp32 FMA kernel agree to 1e-5, and so does precision 2 (bf16 cross terms of the
+    split, coarser but inside the same bound); plain TF32 (precision 1) stays within 1e-3."""
     n, c, h, w, k, kr, kc, st, pads = shape
     rng = np.random.default_rng(17)
     x = rng.standard_normal((n, c, h, w)).astype(F); wt = rng.standard_normal((k, c, kr, kc)).astype(F)
@@ -127,9 +128,14 @@ def test_tensor_core_path_against_fma_path_and_tf32_mode(lib, shape):
         lib.call("set_option", b"conv_path", 0)
     b = run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads)
     t = run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads, precision=1)
+    h = run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads, precision=2)
     for key in ("y", "gw", "dx"):
+        print(key, "3xTF32 %.2e  bf16-cross %.2e  TF32 %.2e" % (relerr(b[key], a[key]), relerr(h[key], a[key]), relerr(t[key], a[key])))
         assert relerr(b[key], a[key]) <= 1e-5, key
+        assert relerr(h[key], a[key]) <= 1e-5, key
         assert relerr(t[key], a[key]) <= 1e-3, key
+    with pytest.raises(Exception):
+        run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads, precision=3)
     lib.call("sync", 0)     # also reports a pipeline time-out of the tensor-core kernel, if any
 
 

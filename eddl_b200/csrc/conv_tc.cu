@@ -494,10 +494,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             const int m = m0 + quarter * 32 + lane;
             const bool m_ok = m < P.M_total;
             float *obase = P.out + (long long)split * P.split_stride + (m_ok ? (long long)__ldg(P.outM + m) : 0);
+            if (P.accumulate) {
+                // The read-modify-write below waits on the old output values.  While this tile's MMAs are still running,
+                // pull the lines of the NEXT tile of this CTA into L2 (the first tile prefetches its own): lane j of the
+                // warp takes columns j, j + 32, ... of the warp's 32 rows (one 128-byte line each).
+                const int tn = (local == 0) ? t : t + (int)gridDim.x;
+                if (tn < total_tiles) {
+                    const int mn2 = tn % tiles_mn;
+                    const int mrow = (mn2 % P.tiles_m) * BM + quarter * 32, ncol0 = (mn2 / P.tiles_m) * BN_;
+                    if (mrow < P.M_total) {
+                        const float *line = P.out + (long long)(tn / tiles_mn) * P.split_stride + (long long)__ldg(P.outM + mrow);
+#pragma unroll
+                        for (int j = lane; j < BN_; j += 32)
+                            if (ncol0 + j < P.N_total)
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(line + (long long)(ncol0 + j) * P.out_n_stride));
+                    }
+                }
+            }
             const uint32_t set_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(set * set_cols);
 #pragma unroll 1
             for (int c = 0; c < (BN_ + 31) / 32; c++) {
                 uint32_t r[32], tt[32];
+                float *p = obase + (long long)(n0 + c * 32) * P.out_n_stride;
+                const long long stride = P.out_n_stride;
+                const int ncols = P.N_total - (n0 + c * 32);           // columns of this chunk inside the problem
+                // read-modify-write: the 32 loads of the old values go out first and overlap the tensor-memory reads
+                float prev[32];
+                const bool rmw = P.accumulate && m_ok && ncols >= 32;
+                if (rmw) {
+                    const float *q = p;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) { prev[j] = __ldcg(q); q += stride; }
+                }
                 tmem_ld32(set_base + (uint32_t)(c * 32), r);
                 // every accumulator in use holds data: a tile has at least four k-steps
 #pragma unroll 1
@@ -513,25 +541,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     if (lane == 0) mbar_arrive(bar_acc_empty + 8 * set);
                 }
                 if (m_ok) {
-                    float *col0 = obase + (long long)(n0 + c * 32) * P.out_n_stride;
-                    if (P.accumulate) {
-                        // read-modify-write: issue all 32 loads before the first store so they overlap
-                        float prev[32];
+                    // The four epilogue warps are a serial instruction stream per tile, so the store loop is kept free of
+                    // branches and index arithmetic: full 32-column chunks take a straight-line path with a running pointer.
+                    if (ncols >= 32) {
+                        if (rmw) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            prev[j] = (n0 + c * 32 + j < P.N_total) ? __ldcg(col0 + (long long)j * P.out_n_stride) : 0.f;
+                            for (int j = 0; j < 32; j++) { *p = __fadd_rn(prev[j], __uint_as_float(r[j])); p += stride; }
+                        } else if (P.bias) {
+                            const float *bq = P.bias + n0 + c * 32;
+                            float bj[32];
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (n0 + c * 32 + j < P.N_total) col0[(long long)j * P.out_n_stride] = __fadd_rn(prev[j], __uint_as_float(r[j]));
+                            for (int j = 0; j < 32; j++) bj[j] = __ldg(bq + j);
+#pragma unroll
+                            for (int j = 0; j < 32; j++) { *p = __fadd_rn(__uint_as_float(r[j]), bj[j]); p += stride; }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) { *p = __uint_as_float(r[j]); p += stride; }
+                        }
                     } else {
+#pragma unroll 1
+                        for (int j = 0; j < ncols; j++) {
+                            // r[] must stay in registers: select the j-th value without dynamic indexing
+                            float v = 0.f;
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int n = n0 + c * 32 + j;
-                            if (n < P.N_total) {
-                                float v = __uint_as_float(r[j]);
-                                if (P.bias) v = __fadd_rn(v, __ldg(P.bias + n));
-                                col0[(long long)j * P.out_n_stride] = v;
-                            }
+                            for (int i = 0; i < 32; i++) if (i == j) v = __uint_as_float(r[i]);
+                            if (P.accumulate) v = __fadd_rn(__ldcg(p), v);
+                            else if (P.bias) v = __fadd_rn(v, __ldg(P.bias + n0 + c * 32 + j));
+                            *p = v; p += stride;
                         }
                     }
                 }

@@ -4,7 +4,7 @@
     python -m eddl_b200.microbench hbm
     python -m eddl_b200.microbench allreduce          (under torchrun for N > 1)
 
-conv      forward / backward-data / backward-weight at the four Conv2D microbenchmark shapes
+conv      forward / backward-data / backward-weight at the four Conv2D microbenchmark shapes (--set resnet: ResNet-50's layers)
           (N=64 C=K=256 56x56 3x3; N=64 C=1024 K=256 14x14 1x1; N=64 C=3 K=64 224x224 7x7 s2 p3; N=32 C=K=512 7x7 3x3),
           TFLOP/s = 2*N*K*C*kr*kc*P*Q / time.
 hbm       BatchNorm forward/backward, ReLU forward/backward, max-pool, axpby, fused SGD at ResNet-50 sizes,
@@ -28,6 +28,17 @@ CONV_SHAPES = [  # n, c, h, w, k, kr, kc, stride, pad
 ]
 
 
+RESNET_SHAPES = [  # the distinct Conv2D layers of ResNet-50 at batch 64 (bottleneck blocks; stage entry layers have stride 2)
+    (64, 64, 56, 56, 64, 1, 1, 1, 0), (64, 64, 56, 56, 64, 3, 3, 1, 1), (64, 64, 56, 56, 256, 1, 1, 1, 0), (64, 256, 56, 56, 64, 1, 1, 1, 0),
+    (64, 256, 56, 56, 128, 1, 1, 1, 0), (64, 128, 56, 56, 128, 3, 3, 2, 1), (64, 128, 28, 28, 512, 1, 1, 1, 0), (64, 512, 28, 28, 128, 1, 1, 1, 0),
+    (64, 128, 28, 28, 128, 3, 3, 1, 1), (64, 256, 56, 56, 512, 1, 1, 2, 0),
+    (64, 512, 28, 28, 256, 1, 1, 1, 0), (64, 256, 28, 28, 256, 3, 3, 2, 1), (64, 256, 14, 14, 1024, 1, 1, 1, 0), (64, 1024, 14, 14, 256, 1, 1, 1, 0),
+    (64, 256, 14, 14, 256, 3, 3, 1, 1), (64, 512, 28, 28, 1024, 1, 1, 2, 0),
+    (64, 1024, 14, 14, 512, 1, 1, 1, 0), (64, 512, 14, 14, 512, 3, 3, 2, 1), (64, 512, 7, 7, 2048, 1, 1, 1, 0), (64, 2048, 7, 7, 512, 1, 1, 1, 0),
+    (64, 512, 7, 7, 512, 3, 3, 1, 1), (64, 1024, 14, 14, 2048, 1, 1, 2, 0),
+]
+
+
 def _timed(L, dev, fn, iters, flush):
     ms_all = []
     for _ in range(iters):
@@ -48,7 +59,8 @@ def run_conv(args):
     L.call("init", dev)
     flush = L.empty((64 << 20,), dev)
     rng = np.random.default_rng(0)
-    shapes = CONV_SHAPES if args.shape < 0 else [CONV_SHAPES[args.shape]]
+    table = RESNET_SHAPES if args.set == "resnet" else CONV_SHAPES
+    shapes = table if args.shape < 0 else [table[args.shape]]
     for (n, c, h, w, k, kr, kc, st, pad) in shapes:
         n = max(1, int(round(n * args.batch_scale)))
         oh = (h + 2 * pad - kr) // st + 1; ow = (w + 2 * pad - kc) // st + 1
@@ -58,6 +70,7 @@ def run_conv(args):
         y, gw, dx = L.empty((n, k, oh, ow), dev), L.zeros((k, c, kr, kc), dev), L.zeros((n, c, h, w), dev)
         geo = (n, c, h, w, k, kr, kc, oh, ow, st, st, pad, pad, args.precision)
         flops = 2.0 * n * k * c * kr * kc * oh * ow
+        nbytes = 4.0 * (n * c * h * w + k * c * kr * kc + n * k * oh * ow)     # each tensor once
         passes = {"fwd": lambda: L.call("conv2d_fwd", dev, x, wt, None, y, *geo),
                   "bwd_data": lambda: L.call("conv2d_bwd_data", dev, dy, wt, dx, *geo),
                   "bwd_weight": lambda: L.call("conv2d_bwd_weight", dev, x, dy, gw, None, *geo)}
@@ -68,7 +81,7 @@ def run_conv(args):
             med, best = _timed(L, dev, fn, args.iters, flush)
             print(json.dumps({"bench": "conv", "pass": name, "shape": {"n": n, "c": c, "h": h, "w": w, "k": k, "kr": kr, "kc": kc, "stride": st, "pad": pad},
                               "precision": {0: "3xTF32", 1: "TF32", 2: "TF32+bf16 cross terms"}[args.precision], "gflop": flops / 1e9, "ms": med, "ms_best": best,
-                              "tflops": flops / (med * 1e-3) / 1e12}), flush=True)
+                              "tflops": flops / (med * 1e-3) / 1e12, "GB/s_each_tensor_once": nbytes / (med * 1e-3) / 1e9}), flush=True)
         L.sync(dev)
 
 
@@ -178,6 +191,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["conv", "hbm", "allreduce"])
     ap.add_argument("--precision", type=int, default=0)
+    ap.add_argument("--set", choices=["micro", "resnet"], default="micro", help="conv shape list: the four microbenchmark shapes or ResNet-50's layers")
     ap.add_argument("--batch-scale", type=float, default=1.0)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--only", default=None)

@@ -37,6 +37,9 @@
 // Every wait on an mbarrier is bounded; on time-out the kernel records a status code, leaves
 // its loops, frees its tensor memory and returns.
 #include <cuda_bf16.h>
+#include <array>
+#include <map>
+#include <mutex>
 #include "common.cuh"
 #include "conv_common.cuh"
 
@@ -671,13 +674,15 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
 // plane, so the main kernel fetches it with a single 16-byte-aligned TMA bulk copy.
 template <int PREC>
 __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ src, const int *__restrict__ rowB, const int *__restrict__ kB,
-                                                     float *__restrict__ packed, int bn, int n_total, int tiles_n) {
+                                                     float *__restrict__ packed, int bn, int n_total, int tiles_n, int row_fastest) {
     const int kb = blockIdx.x, nt = blockIdx.y;
     constexpr bool SPLIT3 = PREC != 1;
     const size_t image_floats = (size_t)bn * BK * (SPLIT3 ? 2 : 1);
     char *img = (char *)(packed + ((size_t)kb * tiles_n + nt) * image_floats);
     for (int e = threadIdx.x; e < bn * BK; e += blockDim.x) {
-        const int row = e / BK, k = e % BK;
+        // consecutive threads follow the dimension that is contiguous in the weight tensor: k for forward
+        // (w[f][c*r*s]), the in-channel row for backward-data (w[f][c][r][s] with k = (f, r, s))
+        const int row = row_fastest ? e % bn : e / BK, k = row_fastest ? e / bn : e % BK;
         const int n = nt * bn + row;
         const int ko = kB[kb * BK + k];
         const float v = (n < n_total && ko >= 0) ? __ldg(src + rowB[n] + ko) : 0.f;
@@ -717,6 +722,23 @@ int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn,
 }
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
+
+// The index tables are a pure function of the problem geometry, so they are built once per distinct geometry and kept
+// in device memory (a few MB per ResNet-50 layer shape); past the budget, tables go to the scratch arena and are
+// rebuilt every call.
+struct TableCache {
+    std::mutex mu;
+    std::map<std::array<int, 24>, char *> entries;
+    size_t bytes = 0;
+};
+TableCache g_tables[EDDLB200_MAX_DEVICES];
+constexpr size_t kTableCacheBudget = size_t(1) << 30;
+
+std::array<int, 24> table_key(const TableArgs &T) {
+    const ConvGeom &g = T.g;
+    return {T.mode, g.n, g.c, g.ih, g.iw, g.k, g.kr, g.kc, g.oh, g.ow, g.sr, g.sc, g.pt, g.pl,
+            T.ca, T.cb, T.y0, T.x0, T.hc, T.wc, T.rt, T.st_, T.check, T.K_pad};
+}
 
 // out[i] = sum_s part[s][i] (+ bias[(i / plane) % nbias])      (split-K forward)
 __global__ void __launch_bounds__(256) splitk_store_kernel(const float *__restrict__ part, float *__restrict__ out, size_t count, int splits,
@@ -779,25 +801,42 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     size_t off = 0;
     auto carve = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };
     const size_t o_rowA = carve((size_t)T.M_total * 8), o_kA = carve((size_t)T.K_pad * 8), o_rowB = carve((size_t)T.N_total * 4),
-                 o_kB = carve((size_t)T.K_pad * 4), o_kC = carve((size_t)T.K_pad * 4), o_outM = carve((size_t)T.M_total * 4),
-                 o_part = carve(splits > 1 ? out_total * splits * sizeof(float) : 0),
+                 o_kB = carve((size_t)T.K_pad * 4), o_kC = carve((size_t)T.K_pad * 4), o_outM = carve((size_t)T.M_total * 4);
+    const size_t table_bytes = off;
+    // cached tables live in their own allocation; the scratch arena then holds only partials and packed weights
+    char *tb = nullptr; bool build = true;
+    {
+        TableCache &tc = g_tables[dev];
+        std::lock_guard<std::mutex> lock(tc.mu);
+        const auto key = table_key(T);
+        auto it = tc.entries.find(key);
+        if (it != tc.entries.end()) { tb = it->second; build = false; }
+        else if (tc.bytes + table_bytes <= kTableCacheBudget && cudaMalloc((void **)&tb, table_bytes) == cudaSuccess) {
+            tc.entries.emplace(key, tb); tc.bytes += table_bytes;
+        } else { tb = nullptr; cudaGetLastError(); }
+    }
+    if (tb) off = 0;
+    const size_t o_part = carve(splits > 1 ? out_total * splits * sizeof(float) : 0),
                  o_pack = carve(mode != 2 ? (size_t)kblocks * tiles_n * bn * BK * sizeof(float) * (precision != 1 ? 2 : 1) : 0);
-    char *ws = (char *)scratch(cx, off);
+    char *ws = (char *)scratch(cx, off ? off : 256);
     if (!ws) return cudaErrorMemoryAllocation;
+    if (!tb) tb = ws;
     if (!g_status[dev]) {
         if (cudaMalloc((void **)&g_status[dev], sizeof(int)) != cudaSuccess) return cudaErrorMemoryAllocation;
         cudaMemsetAsync(g_status[dev], 0, sizeof(int), st);
     }
-    T.rowA = (int2 *)(ws + o_rowA); T.kA = (int2 *)(ws + o_kA); T.rowB = (int *)(ws + o_rowB); T.kB = (int *)(ws + o_kB); T.outM = (int *)(ws + o_outM); T.kC = (int *)(ws + o_kC);
-    const long long entries = (long long)T.M_total + T.K_pad + T.N_total;
-    build_tables_kernel<<<grid_for((size_t)entries, 256), 256, 0, st>>>(T);
-    EB_LAUNCH_CHECK("conv_tc(tables)");
+    T.rowA = (int2 *)(tb + o_rowA); T.kA = (int2 *)(tb + o_kA); T.rowB = (int *)(tb + o_rowB); T.kB = (int *)(tb + o_kB); T.outM = (int *)(tb + o_outM); T.kC = (int *)(tb + o_kC);
+    if (build) {
+        const long long entries = (long long)T.M_total + T.K_pad + T.N_total;
+        build_tables_kernel<<<grid_for((size_t)entries, 256), 256, 0, st>>>(T);
+        EB_LAUNCH_CHECK("conv_tc(tables)");
+    }
     P.packedB = nullptr;
     if (mode != 2) {
         dim3 pgrid(kblocks, tiles_n);
-        if (precision == 0) pack_b_kernel<0><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
-        else if (precision == 2) pack_b_kernel<2><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
-        else pack_b_kernel<1><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n);
+        if (precision == 0) pack_b_kernel<0><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, mode == 1);
+        else if (precision == 2) pack_b_kernel<2><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, mode == 1);
+        else pack_b_kernel<1><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, mode == 1);
         EB_LAUNCH_CHECK("conv_tc(pack weights)");
         P.packedB = (const float *)(ws + o_pack);
     }

@@ -5,7 +5,8 @@
 // cpu_reduce_sum2D (src/hardware/cpu/cpu_math.cpp:302-325,369-380; cpu_reduction.cpp:91-112).
 // The dense layers of the convnets are small (<= 64x2048x1000), so this is an fp32
 // FMA kernel: 64x64 block tile, 16-deep k slices staged in shared memory, 4x4
-// accumulators per thread, exact fp32 accumulation.
+// accumulators per thread, exact fp32 accumulation.  When the output has fewer tiles than the GPU has SMs (batch 64:
+// 16 or 32 tiles) the k range is split across blockIdx.z and the partials are combined in a fixed order.
 #include "common.cuh"
 
 namespace {
@@ -16,20 +17,24 @@ constexpr int BM = 64, BN = 64, BK = 16, TB = 256;
 
 // Row-major storage.  A: ta ? [k,m] : [m,k]; B: tb ? [n,k] : [k,n]; C: [m,n].
 __global__ void __launch_bounds__(TB) sgemm_kernel(const float *__restrict__ A, int ta, const float *__restrict__ B, int tb,
-                                                   float *__restrict__ C, int inc_c, int m, int n, int k) {
+                                                   float *__restrict__ C, int inc_c, int m, int n, int k, int k_per_split,
+                                                   float *__restrict__ part) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     float acc[4][4] = {};
-    for (int k0 = 0; k0 < k; k0 += BK) {
+    const int kbeg = blockIdx.z * k_per_split;
+    int kend = k;
+    if (part) { kend = min(k, kbeg + k_per_split); C = part + (size_t)blockIdx.z * m * n; inc_c = 0; }
+    for (int k0 = kbeg; k0 < kend; k0 += BK) {
         for (int e = threadIdx.x; e < BM * BK; e += TB) {
             // choose the traversal that is contiguous in memory
             int mi, ki;
             if (ta) { mi = e % BM; ki = e / BM; } else { ki = e % BK; mi = e / BK; }
             const int gm = m0 + mi, gk = k0 + ki;
             float v = 0.f;
-            if (gm < m && gk < k) v = ta ? A[(size_t)gk * m + gm] : A[(size_t)gm * k + gk];
+            if (gm < m && gk < kend) v = ta ? A[(size_t)gk * m + gm] : A[(size_t)gm * k + gk];
             As[ki][mi] = v;
         }
         for (int e = threadIdx.x; e < BN * BK; e += TB) {
@@ -37,7 +42,7 @@ __global__ void __launch_bounds__(TB) sgemm_kernel(const float *__restrict__ A, 
             if (tb) { ki = e % BK; ni = e / BK; } else { ni = e % BN; ki = e / BN; }
             const int gn = n0 + ni, gk = k0 + ki;
             float v = 0.f;
-            if (gn < n && gk < k) v = tb ? B[(size_t)gn * k + gk] : B[(size_t)gk * n + gn];
+            if (gn < n && gk < kend) v = tb ? B[(size_t)gn * k + gk] : B[(size_t)gk * n + gn];
             Bs[ki][ni] = v;
         }
         __syncthreads();
@@ -66,6 +71,16 @@ __global__ void __launch_bounds__(TB) sgemm_kernel(const float *__restrict__ A, 
             float *c = C + (size_t)gm * n + gn;
             *c = inc_c ? __fadd_rn(*c, acc[i][j]) : acc[i][j];
         }
+    }
+}
+
+// c[i] = (inc_c ? c[i] : 0) + part[0][i] + part[1][i] + ...   (fixed order)
+__global__ void __launch_bounds__(256) sgemm_combine_kernel(const float *__restrict__ part, float *__restrict__ c, size_t count, int splits, int inc_c) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float v = inc_c ? c[i] : 0.f;
+        for (int z = 0; z < splits; z++) v = __fadd_rn(v, part[(size_t)z * count + i]);
+        c[i] = v;
     }
 }
 
@@ -105,8 +120,29 @@ int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, flo
     if (m == 0 || n == 0) return 0;
     ProfScope prof(cx, PROF_GEMM, 2.0 * m * (double)n * k);
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
-    sgemm_kernel<<<grid, TB, 0, st>>>(a, ta, b, tb, c, inc_c, m, n, k);
+    const int tiles = (int)(grid.x * grid.y);
+    int splits = 1;
+    if (tiles < EDDLB200_NUM_SMS) {
+        splits = (2 * EDDLB200_NUM_SMS + tiles - 1) / tiles;
+        if (splits > k / (4 * BK)) splits = k / (4 * BK);
+        if (splits < 1) splits = 1;
+    }
+    if (splits == 1) {
+        sgemm_kernel<<<grid, TB, 0, st>>>(a, ta, b, tb, c, inc_c, m, n, k, k, nullptr);
+        EB_LAUNCH_CHECK("gpu_mult2D");
+        return 0;
+    }
+    int kps = (k + splits - 1) / splits;
+    kps = (kps + BK - 1) / BK * BK;
+    splits = (k + kps - 1) / kps;
+    const size_t count = (size_t)m * n;
+    float *part = (float *)scratch(cx, count * splits * sizeof(float));
+    if (!part) return cudaErrorMemoryAllocation;
+    grid.z = splits;
+    sgemm_kernel<<<grid, TB, 0, st>>>(a, ta, b, tb, c, inc_c, m, n, k, kps, part);
     EB_LAUNCH_CHECK("gpu_mult2D");
+    sgemm_combine_kernel<<<grid_for(count, 256), 256, 0, st>>>(part, c, count, splits, inc_c);
+    EB_LAUNCH_CHECK("gpu_mult2D(combine)");
     return 0;
 }
 

@@ -81,23 +81,52 @@ __device__ __forceinline__ void covering(int v, int k, int s, int pad, int on, i
     lo = num <= 0 ? 0 : (num + s - 1) / s;
 }
 
-template <bool MAX>
+// IDX = unsigned when the tensor has fewer than 2^32 elements (32-bit divisions), size_t otherwise.
+template <bool MAX, typename IDX>
 __global__ void __launch_bounds__(kBlock) pool_bwd_kernel(const float *__restrict__ d, const float *__restrict__ ind_x,
                                                           const float *__restrict__ ind_y, float *__restrict__ id,
                                                           size_t total_in, PoolGeom g) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const float ksize = (float)(g.kr * g.kc);
     for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < total_in; q += stride) {
-        const int x = (int)(q % g.iw);
-        const size_t t = q / g.iw;
-        const int y = (int)(t % g.ih);
-        const size_t plane = t / g.ih;
+        const IDX qi = (IDX)q;
+        const int x = (int)(qi % (IDX)g.iw);
+        const IDX t = qi / (IDX)g.iw;
+        const int y = (int)(t % (IDX)g.ih);
+        const size_t plane = t / (IDX)g.ih;
         int oi0, oi1, oj0, oj1;
         covering(y, g.kr, g.sr, g.pt, g.oh, oi0, oi1);
         covering(x, g.kc, g.sc, g.pl, g.ow, oj0, oj1);
         float acc = id[q];
         bool touched = false;
         const size_t obase = plane * (size_t)g.oh * g.ow;
+        if (oi1 - oi0 <= 1 && oj1 - oj0 <= 1) {
+            // at most 2 x 2 covering windows (kernel <= 2 * stride, the usual case): all loads go out together, with no
+            // data-dependent branches between them; the adds keep the reference's window order
+            float vd[4], vx[4], vy[4]; bool in[4];
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const int oi = oi0 + (w >> 1), oj = oj0 + (w & 1);
+                in[w] = oi <= oi1 && oj <= oj1;
+                const size_t p = obase + (size_t)(in[w] ? oi : oi0) * g.ow + (in[w] ? oj : oj0);
+                in[w] = in[w] && oi0 <= oi1 && oj0 <= oj1;
+                if (in[w]) {
+                    vd[w] = __ldg(d + p);
+                    if (MAX) { vx[w] = __ldg(ind_x + p); vy[w] = __ldg(ind_y + p); }
+                }
+            }
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                if (!in[w]) continue;
+                if (MAX) {
+                    // int x = D->indX->ptr[p]  (float -> int conversion in the reference)
+                    if ((int)vx[w] == x && (int)vy[w] == y) { acc = __fadd_rn(acc, vd[w]); touched = true; }
+                } else {
+                    acc = __fadd_rn(acc, __fdiv_rn(vd[w], ksize));
+                    touched = true;
+                }
+            }
+        } else
         for (int oi = oi0; oi <= oi1; oi++)
             for (int oj = oj0; oj <= oj1; oj++) {
                 const size_t p = obase + (size_t)oi * g.ow + oj;
@@ -148,7 +177,8 @@ int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const fl
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
     ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + 8.0 * total);
-    pool_bwd_kernel<true><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g);
+    if (total < (size_t(1) << 32)) pool_bwd_kernel<true, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g);
+    else pool_bwd_kernel<true, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g);
     EB_LAUNCH_CHECK("gpu_mpool2D_back");
     return 0;
 }
@@ -176,7 +206,8 @@ int eddlb200_avgpool2d_bwd(int dev, const float *d, float *id, int n, int c, int
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
     ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + 8.0 * total);
-    pool_bwd_kernel<false><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g);
+    if (total < (size_t(1) << 32)) pool_bwd_kernel<false, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g);
+    else pool_bwd_kernel<false, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g);
     EB_LAUNCH_CHECK("gpu_avgpool2D_back");
     return 0;
 }

@@ -166,7 +166,9 @@ __global__ void __launch_bounds__(kBlock) bn_fwd_apply_kernel(const float *__res
 }
 
 // ---- backward apply ---------------------------------------------------------------
-template <bool VEC>
+// PD_ZERO: the parent delta is known to hold zeros, so it is written without being read (0 + x keeps the bits of the
+// read-modify-write form).
+template <bool VEC, bool PD_ZERO>
 __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(float *__restrict__ delta, const float *__restrict__ opa, float *__restrict__ pdelta,
                                                               const float2 *__restrict__ partial,
                                                               float *gbn_g, float *gbn_b, const float *__restrict__ bn_g,
@@ -194,7 +196,7 @@ __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(float *__restrict_
             const size_t off = item_offset(t, rc, z, j);
             float4 d = *reinterpret_cast<const float4 *>(delta + off);
             const float4 o = ld_stream4(opa + off);
-            float4 p = *reinterpret_cast<const float4 *>(pdelta + off);
+            float4 p = PD_ZERO ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4 *>(pdelta + off);
             if (affine) {
                 d.x = __fmul_rn(d.x, gj); d.y = __fmul_rn(d.y, gj); d.z = __fmul_rn(d.z, gj); d.w = __fmul_rn(d.w, gj);
                 *reinterpret_cast<float4 *>(delta + off) = d;            // delta[p] *= bn_g[j]
@@ -210,7 +212,7 @@ __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(float *__restrict_
             const size_t off = item_offset(t, rc, z, j);
             float d = delta[off];
             if (affine) { d = __fmul_rn(d, gj); delta[off] = d; }
-            pdelta[off] = __fadd_rn(pdelta[off], __fdiv_rn(__fsub_rn(d, __fadd_rn(__fmul_rn(opa[off], m1), m2)), sigma));
+            pdelta[off] = __fadd_rn(PD_ZERO ? 0.f : pdelta[off], __fdiv_rn(__fsub_rn(d, __fadd_rn(__fmul_rn(opa[off], m1), m2)), sigma));
         }
     }
 }
@@ -239,6 +241,12 @@ int eddlb200_bn_fwd(int dev, int b, int z, int rc, const float *input, float *ou
     EB_REQUIRE((size_t)b * rc < 0xfffffff0u, "gpu_batchnorm_forward");
     EB_REQUIRE(!affine_g || (affine_b && opa), "gpu_batchnorm_forward");
     EB_REQUIRE(!trmode || mean, "gpu_batchnorm_forward");
+    {
+        const size_t tb = (size_t)b * z * rc * sizeof(float), zb = (size_t)z * sizeof(float);
+        EB_READS(input, tb); EB_WRITES(output, tb); EB_WRITES(opa, tb); EB_WRITES(relu_out, tb);
+        EB_READS(global_mean, zb); EB_READS(global_variance, zb); EB_READS(affine_g, zb); EB_READS(affine_b, zb);
+        EB_READS(mean, zb); EB_READS(variance, zb);
+    }
     ProfScope prof(cx, PROF_BN_FWD, 16.0 * b * (double)z * rc);
     const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
     const bool vec = (rc % 4 == 0) && aligned16(input) && aligned16(output) && (!opa || aligned16(opa)) && (!relu_out || aligned16(relu_out));
@@ -266,7 +274,18 @@ int eddlb200_bn_bwd(int dev, int b, int z, int rc, float *delta, const float *op
     EB_REQUIRE(b > 0 && z > 0 && rc > 0 && delta && opa && pdelta && variance && mean1 && mean2, "gpu_batchnorm_backward");
     EB_REQUIRE((size_t)b * rc < 0xfffffff0u, "gpu_batchnorm_backward");
     EB_REQUIRE(!bn_g || (gbn_g && gbn_b), "gpu_batchnorm_backward");
-    ProfScope prof(cx, PROF_BN_BWD, 24.0 * b * (double)z * rc);
+    bool pd_zero = false;
+    {
+        const size_t tb = (size_t)b * z * rc * sizeof(float), zb = (size_t)z * sizeof(float);
+        EB_READS(delta, tb); EB_READS(opa, tb);
+        EB_READS(gbn_g, zb); EB_READS(gbn_b, zb); EB_READS(bn_g, zb); EB_READS(variance, zb); EB_READS(mean1, zb); EB_READS(mean2, zb);
+        if (lz_any(cx) && pdelta != delta && pdelta != opa) {
+            int status = 0;
+            pd_zero = lz_take(cx, st, pdelta, tb, &status);
+            if (status) return status;
+        }
+    }
+    ProfScope prof(cx, PROF_BN_BWD, (pd_zero ? 20.0 : 24.0) * b * (double)z * rc);
     const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
     const bool vec = (rc % 4 == 0) && aligned16(delta) && aligned16(opa) && aligned16(pdelta);
     dim3 grid(z, S);
@@ -275,8 +294,10 @@ int eddlb200_bn_bwd(int dev, int b, int z, int rc, float *delta, const float *op
     if (vec) bn_stats_kernel<1, true><<<grid, kBlock, 0, st>>>(delta, opa, partial, b, z, rc);
     else bn_stats_kernel<1, false><<<grid, kBlock, 0, st>>>(delta, opa, partial, b, z, rc);
     EB_LAUNCH_CHECK("gpu_batchnorm_backward(stats)");
-    if (vec) bn_bwd_apply_kernel<true><<<grid, kBlock, 0, st>>>(delta, opa, pdelta, partial, gbn_g, gbn_b, bn_g, variance, mean1, mean2, b, z, rc);
-    else bn_bwd_apply_kernel<false><<<grid, kBlock, 0, st>>>(delta, opa, pdelta, partial, gbn_g, gbn_b, bn_g, variance, mean1, mean2, b, z, rc);
+    if (vec && pd_zero) bn_bwd_apply_kernel<true, true><<<grid, kBlock, 0, st>>>(delta, opa, pdelta, partial, gbn_g, gbn_b, bn_g, variance, mean1, mean2, b, z, rc);
+    else if (vec) bn_bwd_apply_kernel<true, false><<<grid, kBlock, 0, st>>>(delta, opa, pdelta, partial, gbn_g, gbn_b, bn_g, variance, mean1, mean2, b, z, rc);
+    else if (pd_zero) bn_bwd_apply_kernel<false, true><<<grid, kBlock, 0, st>>>(delta, opa, pdelta, partial, gbn_g, gbn_b, bn_g, variance, mean1, mean2, b, z, rc);
+    else bn_bwd_apply_kernel<false, false><<<grid, kBlock, 0, st>>>(delta, opa, pdelta, partial, gbn_g, gbn_b, bn_g, variance, mean1, mean2, b, z, rc);
     EB_LAUNCH_CHECK("gpu_batchnorm_backward(apply)");
     return 0;
 }
@@ -348,6 +369,13 @@ extern "C" int eddlb200_bn_fwd_noalloc(int dev, int b, int z, int rc, const floa
     float2 *partial = noalloc_scratch(dev);
     if (!partial) return EDDLB200_ENOINIT;
     cudaStream_t st = (cudaStream_t)cuda_stream;
+    if (DevCtx *cx = ctx_peek(dev)) {
+        // a device context exists and may owe zeros to one of these buffers (deferred fills): settle them on this stream
+        const size_t tb = (size_t)b * z * rc * sizeof(float), zb = (size_t)z * sizeof(float);
+        EB_READS(input, tb); EB_WRITES(output, tb); EB_WRITES(opa, tb); EB_WRITES(relu_out, tb);
+        EB_READS(global_mean, zb); EB_READS(global_variance, zb); EB_READS(affine_g, zb); EB_READS(affine_b, zb);
+        EB_READS(mean, zb); EB_READS(variance, zb);
+    }
     const bool vec = (rc % 4 == 0) && aligned16(input) && aligned16(output) && (!opa || aligned16(opa)) && (!relu_out || aligned16(relu_out));
     dim3 grid(z, S);
     if (trmode) {

@@ -17,6 +17,8 @@ struct DevCtx;
 // Returns the initialised context of `dev` (creating it on first use) or nullptr
 // with last_error set.  Makes `dev` the current device of the calling thread.
 DevCtx *ctx(int dev);
+// The context of `dev` if one has been created, else nullptr; creates and allocates nothing.
+DevCtx *ctx_peek(int dev);
 cudaStream_t stream_of(DevCtx *c);
 // Stream-ordered scratch of at least `bytes` bytes, reused by every kernel that
 // runs on the device's compute stream (valid until the next scratch() call).
@@ -43,7 +45,30 @@ struct ProfScope {
 };
 int cuda_status(cudaError_t e, const char *what);
 
+// Deferred zero fills.  With the option "lazy_zero" on, a fill of a large buffer with 0.0f only records the range.
+// The zeros are written when an entry point READS any part of the range (lz_read), dropped when one OVERWRITES the
+// whole range (lz_write), or consumed by an accumulating kernel that owns the whole range and runs its
+// "destination is zero" variant instead of a read-modify-write (lz_take).  Every entry point of the library declares
+// each device pointer it is given through one of the three before launching.
+bool lz_any(DevCtx *c);                                                  // anything deferred on this device?
+bool lz_defer(DevCtx *c, cudaStream_t st, void *p, size_t bytes);        // true = recorded, caller skips its fill
+int lz_read(DevCtx *c, cudaStream_t st, const void *p, size_t bytes);
+int lz_write(DevCtx *c, cudaStream_t st, const void *p, size_t bytes);
+bool lz_take(DevCtx *c, cudaStream_t st, const void *p, size_t bytes, int *status);
+void lz_forget(DevCtx *c, const void *p, size_t bytes);                  // the memory is being released
+int lz_set_all(int on);                                                  // every device; turning it off writes every deferred fill
+int launch_zero_fill(DevCtx *c, cudaStream_t st, float *p, size_t n);    // defined with the elementwise kernels
+
 }  // namespace eb
+
+#define EB_READS(p, bytes)                                                              \
+    do {                                                                                \
+        if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_read(cx, st, (p), (bytes))) return r__; } \
+    } while (0)
+#define EB_WRITES(p, bytes)                                                             \
+    do {                                                                                \
+        if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_write(cx, st, (p), (bytes))) return r__; } \
+    } while (0)
 
 #define EB_CTX(dev)                                   \
     eb::DevCtx *cx = eb::ctx(dev);                    \

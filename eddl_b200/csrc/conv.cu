@@ -67,6 +67,7 @@ extern "C" {
 
 int eddlb200_set_option(const char *name, int value) {
     if (name && !strcmp(name, "conv_path") && (value == 0 || value == 1)) { g_conv_path = value; return 0; }
+    if (name && !strcmp(name, "lazy_zero") && (value == 0 || value == 1)) return lz_set_all(value);
     return set_error(EDDLB200_EINVAL, "set_option: unknown option or value");
 }
 
@@ -78,6 +79,8 @@ int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bi
     if (int r = check("gpu_conv2D", g)) return r;
     EB_REQUIRE(x && w && y && precision >= 0 && precision <= 2, "gpu_conv2D");
     if (n == 0) return 0;
+    EB_READS(x, (size_t)n * c * ih * iw * sizeof(float)); EB_READS(w, (size_t)k * c * kr * kc * sizeof(float)); EB_READS(bias, (size_t)k * sizeof(float));
+    EB_WRITES(y, (size_t)n * k * oh * ow * sizeof(float));
     ProfScope prof(cx, PROF_CONV_FWD, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
         int r = conv_tc_fwd(cx, st, g, x, w, bias, y, precision);
@@ -94,11 +97,16 @@ int eddlb200_conv2d_bwd_data(int dev, const float *dy, const float *w, float *dx
     if (int r = check("gpu_conv2D_back", g)) return r;
     EB_REQUIRE(dy && w && dx && precision >= 0 && precision <= 2, "gpu_conv2D_back");
     if (n == 0) return 0;
+    EB_READS(dy, (size_t)n * k * oh * ow * sizeof(float)); EB_READS(w, (size_t)k * c * kr * kc * sizeof(float));
+    const size_t dx_elems = (size_t)n * c * ih * iw;
+    bool dx_zero = false;
+    if (lz_any(cx)) { int status = 0; dx_zero = lz_take(cx, st, dx, dx_elems * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_CONV_BWD_DATA, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
-        int r = conv_tc_bwd_data(cx, st, g, dy, w, dx, precision);
+        int r = conv_tc_bwd_data(cx, st, g, dy, w, dx, precision, dx_zero);
         if (r != 1) return r;
     }
+    if (dx_zero) { if (int r = launch_zero_fill(cx, st, dx, dx_elems)) return r; }     // the FMA kernel adds into dx
     return conv_simt_bwd_data(cx, st, g, dy, w, dx);
 }
 
@@ -110,15 +118,21 @@ int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *
     if (int r = check("gpu_conv2D_grad", g)) return r;
     EB_REQUIRE(x && dy && gw && precision >= 0 && precision <= 2, "gpu_conv2D_grad");
     if (n == 0) return 0;
+    EB_READS(x, (size_t)n * c * ih * iw * sizeof(float)); EB_READS(dy, (size_t)n * k * oh * ow * sizeof(float));
+    EB_READS(gbias, (size_t)k * sizeof(float));
+    const size_t gw_elems = (size_t)k * c * kr * kc;
+    bool gw_zero = false;
+    if (lz_any(cx)) { int status = 0; gw_zero = lz_take(cx, st, gw, gw_elems * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_CONV_BWD_WEIGHT, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (gbias) {
         bias_grad_kernel<<<k, 256, 0, st>>>(dy, gbias, n, k, oh * ow);
         EB_LAUNCH_CHECK("gpu_conv2D_grad(bias)");
     }
     if (tc_enabled()) {
-        int r = conv_tc_bwd_weight(cx, st, g, x, dy, gw, precision);
+        int r = conv_tc_bwd_weight(cx, st, g, x, dy, gw, precision, gw_zero);
         if (r != 1) return r;
     }
+    if (gw_zero) { if (int r = launch_zero_fill(cx, st, gw, gw_elems)) return r; }     // the FMA path adds into gw
     return conv_simt_bwd_weight(cx, st, g, x, dy, gw);
 }
 

@@ -19,8 +19,10 @@ int conv_simt_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const f
 // Tensor-core implicit GEMM (conv_tc.cu).  Each returns 1 when the shape is outside what
 // the kernel takes (the caller then uses the FMA path), 0 on success, or an error code.
 int conv_tc_fwd(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *w, const float *bias, float *y, int precision);
-int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision);
-int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *dy, float *gw, int precision);
+// dx_zero: dx is known to hold zeros (the caller took over a deferred zero fill of it), so the result may be stored
+// instead of added; routes that cannot use this write the zeros first.
+int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision, bool dx_zero);
+int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *dy, float *gw, int precision, bool gw_zero);
 
 // Reads and clears the device's time-out flag of the tensor-core kernels (blocking).
 int conv_tc_status(int dev, cudaStream_t st, int *out);

@@ -72,6 +72,7 @@ struct TcParams {
     int kblocks_per_split;
     long long split_stride; // elements between the partial outputs of consecutive splits
     int accumulate;
+    int add_zero;           // plain stores write 0 + v (the bits a read-modify-write into zeros would leave)
     int check;              // padding test of the gathered operand: 0 none needed, 1 per-row tap bitmask, 2 coordinates
     const float *packedB;   // forward / backward-data: pre-split, pre-swizzled B tiles [kblock][n tile][hi|lo][BN x 32]
     int nmain;              // rotating hi*hi accumulators in use: 1 for short chains, NMAIN otherwise
@@ -557,6 +558,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                             for (int j = 0; j < 32; j++) bj[j] = __ldg(bq + j);
 #pragma unroll
                             for (int j = 0; j < 32; j++) { *p = __fadd_rn(__uint_as_float(r[j]), bj[j]); p += stride; }
+                        } else if (P.add_zero) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) { *p = __fadd_rn(0.f, __uint_as_float(r[j])); p += stride; }
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; j++) { *p = __uint_as_float(r[j]); p += stride; }
@@ -570,6 +574,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                             for (int i = 0; i < 32; i++) if (i == j) v = __uint_as_float(r[i]);
                             if (P.accumulate) v = __fadd_rn(__ldcg(p), v);
                             else if (P.bias) v = __fadd_rn(v, __ldg(P.bias + n0 + c * 32 + j));
+                            else if (P.add_zero) v = __fadd_rn(0.f, v);
                             *p = v; p += stride;
                         }
                     }
@@ -755,7 +760,7 @@ __global__ void __launch_bounds__(256) splitk_store_kernel(const float *__restri
 // One GEMM launch (tables + main kernel + optional split-K combine).  T carries mode / class fields and the
 // problem extents; out_total is the element count of the output tensor (the unit of a split-K partial).
 int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const float *srcA, const float *srcB, float *out,
-            const float *bias, int precision, size_t out_total, bool allow_split) {
+            const float *bias, int precision, size_t out_total, bool allow_split, bool out_zero = false) {
     const ConvGeom &g = T.g;
     const int mode = T.mode;
     T.K_pad = (T.K_total + BK - 1) / BK * BK;
@@ -849,7 +854,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     P.nmain = (kbs * (BK / 8) > 64) ? NMAIN : 1;
     P.status = g_status[dev];
     if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
-    else { P.out = out; P.split_stride = 0; P.accumulate = (mode == 1 || mode == 2); P.bias = bias; }
+    else { P.out = out; P.split_stride = 0; P.accumulate = (mode == 1 || mode == 2) && !out_zero; P.add_zero = out_zero; P.bias = bias; }
     const long long total_tiles = (long long)tiles_m * tiles_n * splits;
     dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
     int r;
@@ -860,8 +865,9 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     else r = launch_bn<1, false>(cx, st, P, grid, bn, dev);
     if (r) return r;
     if (splits > 1) {
-        if (mode == 0) {
-            splitk_store_kernel<<<grid_for(out_total, 256), 256, 0, st>>>((const float *)(ws + o_part), out, out_total, splits, bias, g.oh * g.ow, g.k);
+        if (mode == 0 || out_zero) {
+            // `out` holds nothing to add to: store the sum of the partials (0 + p0 + p1 + ...)
+            splitk_store_kernel<<<grid_for(out_total, 256), 256, 0, st>>>((const float *)(ws + o_part), out, out_total, splits, mode == 0 ? bias : nullptr, g.oh * g.ow, g.k);
             EB_LAUNCH_CHECK("conv_tc(split-K store)");
             return 0;
         }
@@ -871,7 +877,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
 }
 
 int run(DevCtx *cx, cudaStream_t st, int dev, int mode, const ConvGeom &g, const float *srcA, const float *srcB, float *out,
-        const float *bias, int precision) {
+        const float *bias, int precision, bool out_zero = false) {
     const int pq = g.oh * g.ow, hw = g.ih * g.iw, rs = g.kr * g.kc;
     TableArgs T{};
     T.g = g; T.mode = mode;
@@ -882,7 +888,7 @@ int run(DevCtx *cx, cudaStream_t st, int dev, int mode, const ConvGeom &g, const
     }
     if (mode == 2) {
         T.M_total = g.c * rs; T.N_total = g.k; T.K_total = g.n * pq; P.limY = g.ih; P.limX = g.iw; P.out_n_stride = g.c * rs;
-        return run_one(cx, st, dev, T, P, srcA, srcB, out, nullptr, precision, (size_t)g.k * g.c * rs, true);
+        return run_one(cx, st, dev, T, P, srcA, srcB, out, nullptr, precision, (size_t)g.k * g.c * rs, true, out_zero);
     }
     // backward-data: one dense problem per residue class of the strides
     P.limY = g.oh; P.limX = g.ow; P.out_n_stride = hw; T.N_total = g.c;
@@ -897,7 +903,7 @@ int run(DevCtx *cx, cudaStream_t st, int dev, int mode, const ConvGeom &g, const
             T.M_total = g.n * T.hc * T.wc; T.K_total = g.k * T.rt * T.st_;
             if (T.M_total == 0 || T.K_total == 0) continue;       // this class receives nothing
             const bool dense = (g.sr == 1 && g.sc == 1);
-            if (int r = run_one(cx, st, dev, T, P, srcA, srcB, out, nullptr, precision, (size_t)g.n * g.c * hw, dense)) return r;
+            if (int r = run_one(cx, st, dev, T, P, srcA, srcB, out, nullptr, precision, (size_t)g.n * g.c * hw, dense, dense && out_zero)) return r;
         }
     return 0;
 }
@@ -966,20 +972,26 @@ int conv_tc_fwd(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, 
     return run(cx, st, dev, 0, g, x, w, y, bias, precision);
 }
 
-int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision) {
+int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision, bool dx_zero) {
     if (!fits(g)) return 1;
     int dev = 0; cudaGetDevice(&dev);
+    const bool small_c = g.c <= 8 && (size_t)g.n * g.c * g.kr * g.kc * g.oh * g.ow < (size_t(1) << 29);
+    if (dx_zero && (small_c || g.sr != 1 || g.sc != 1)) {
+        // these routes add into dx piecewise: write the zeros the caller still owes it
+        if (int r = launch_zero_fill(cx, st, dx, (size_t)g.n * g.c * g.ih * g.iw)) return r;
+        dx_zero = false;
+    }
     if (g.c <= 8 && (size_t)g.n * g.c * g.kr * g.kc * g.oh * g.ow < (size_t(1) << 29)) {
         const int r = run_small_c_bwd_data(cx, st, dev, g, dy, w, dx, precision);
         if (r != 1) return r;
     }
-    return run(cx, st, dev, 1, g, dy, w, dx, nullptr, precision);
+    return run(cx, st, dev, 1, g, dy, w, dx, nullptr, precision, dx_zero);
 }
 
-int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *dy, float *gw, int precision) {
+int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *dy, float *gw, int precision, bool gw_zero) {
     if (!fits(g)) return 1;
     int dev = 0; cudaGetDevice(&dev);
-    return run(cx, st, dev, 2, g, x, dy, gw, nullptr, precision);
+    return run(cx, st, dev, 2, g, x, dy, gw, nullptr, precision, gw_zero);
 }
 
 // 0 = no kernel of this file has timed out on the device since the last call

@@ -59,6 +59,8 @@ template <typename F>
 int launch1(DevCtx *cx, cudaStream_t st, const float *a, float *b, size_t n, F f, const char *what) {
     if (n == 0) return 0;
     if (!a || !b) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
+    if (!F::ignores_input) EB_READS(a, n * sizeof(float));
+    EB_WRITES(b, n * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, 8.0 * n);
     if (aligned16(a) && aligned16(b)) {
         size_t n4 = n / 4;
@@ -74,6 +76,9 @@ template <typename F>
 int launch3(DevCtx *cx, cudaStream_t st, const float *a, const float *b, float *c, size_t n, F f, const char *what) {
     if (n == 0) return 0;
     if (!a || !b || !c) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
+    EB_READS(a, n * sizeof(float));
+    EB_READS(b, n * sizeof(float));
+    if (F::reads_c) EB_READS(c, n * sizeof(float)); else EB_WRITES(c, n * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, (F::reads_c ? 16.0 : 12.0) * n);
     if (aligned16(a) && aligned16(b) && aligned16(c)) {
         size_t n4 = n / 4;
@@ -85,13 +90,18 @@ int launch3(DevCtx *cx, cudaStream_t st, const float *a, const float *b, float *
     return 0;
 }
 
-struct FillF { float v; __device__ float operator()(float) const { return v; } };
-struct ScaleF { float v; __device__ float operator()(float x) const { return __fmul_rn(x, v); } };
-struct AddcF { float v; __device__ float operator()(float x) const { return __fadd_rn(x, v); } };
-struct SqrF { __device__ float operator()(float x) const { return __fmul_rn(x, x); } };
-struct SqrtF { __device__ float operator()(float x) const { return __fsqrt_rn(x); } };
-struct ClampF { float lo, hi; __device__ float operator()(float x) const { return x < lo ? lo : (x > hi ? hi : x); } };
-struct ReluF { __device__ float operator()(float x) const { return x > 0.f ? x : 0.f; } };
+struct FillF { static constexpr bool ignores_input = true; float v; __device__ float operator()(float) const { return v; } };
+struct ScaleF { static constexpr bool ignores_input = false; float v; __device__ float operator()(float x) const { return __fmul_rn(x, v); } };
+struct AddcF { static constexpr bool ignores_input = false; float v; __device__ float operator()(float x) const { return __fadd_rn(x, v); } };
+struct SqrF { static constexpr bool ignores_input = false; __device__ float operator()(float x) const { return __fmul_rn(x, x); } };
+struct SqrtF { static constexpr bool ignores_input = false; __device__ float operator()(float x) const { return __fsqrt_rn(x); } };
+struct ClampF { static constexpr bool ignores_input = false; float lo, hi; __device__ float operator()(float x) const { return x < lo ? lo : (x > hi ? hi : x); } };
+struct ReluF { static constexpr bool ignores_input = false; __device__ float operator()(float x) const { return x > 0.f ? x : 0.f; } };
+// sa*x + sb*0: gpu_add(sa, A, sb, B, C = B, 0) -- the form Tensor::inc takes on the GPU -- with B known to hold zeros
+struct AxpbZeroF { static constexpr bool ignores_input = false; float sa, sb; __device__ float operator()(float x) const { return __fadd_rn(__fmul_rn(sa, x), __fmul_rn(sb, 0.f)); } };
+struct ZeroAxpbF { static constexpr bool ignores_input = false; float sa, sb; __device__ float operator()(float y) const { return __fadd_rn(__fmul_rn(sa, 0.f), __fmul_rn(sb, y)); } };
+// b = 0 + a: what "b += a" leaves in a b known to hold zeros (the add keeps the sign of a zero result identical)
+struct AddToZeroF { static constexpr bool ignores_input = false; __device__ float operator()(float x) const { return __fadd_rn(0.f, x); } };
 
 // gpu_add: C = scA*A + scB*B (+ C).  Reference (cpu_math.cpp cpu_add): two products, one sum,
 // then "+=" when incC -- four roundings, reproduced here.
@@ -115,6 +125,17 @@ template <bool INC> struct MulF {
 struct ReluBwdF {
     static constexpr bool reads_c = true;
     __device__ float operator()(float d, float i, float pd) const { return i > 0.f ? __fadd_rn(pd, d) : pd; }
+};
+// the same with pd known to hold zeros: no read of pd
+struct ReluBwdZeroF {
+    static constexpr bool reads_c = false;
+    __device__ float operator()(float d, float i, float) const { return i > 0.f ? __fadd_rn(0.f, d) : 0.f; }
+};
+// c = 0 + (sa*a + sb*b): gpu_add with incC into a c known to hold zeros
+struct AxpbyZeroF {
+    static constexpr bool reads_c = false;
+    float sa, sb;
+    __device__ float operator()(float a, float b, float) const { return __fadd_rn(0.f, __fadd_rn(__fmul_rn(sa, a), __fmul_rn(sb, b))); }
 };
 // delta = -y * (1.0f / (p + 1e-7))   a = y_true, b = y_pred  (cpu_losses.cpp:50-57)
 struct CceDeltaF {
@@ -159,6 +180,18 @@ __global__ void __launch_bounds__(kBlock) fill_multi_kernel(const FillSeg *__res
 
 }  // namespace
 
+namespace eb {
+// writes n zeros at p; used when a deferred zero fill has to be materialised
+int launch_zero_fill(DevCtx *cx, cudaStream_t st, float *p, size_t n) {
+    if (n == 0) return 0;
+    ProfScope prof(cx, PROF_ELEMENTWISE, 4.0 * n);
+    if (aligned16(p)) { const size_t n4 = n / 4; map1_kernel<<<grid_for(n4 ? n4 : 1, kBlock), kBlock, 0, st>>>(p, p, n4, n, FillF{0.f}); }
+    else map1_scalar_kernel<<<grid_for(n, kBlock), kBlock, 0, st>>>(p, p, n, FillF{0.f});
+    EB_LAUNCH_CHECK("gpu_fill_(deferred)");
+    return 0;
+}
+}  // namespace eb
+
 using namespace eb;
 
 extern "C" {
@@ -171,6 +204,8 @@ int eddlb200_fill_multi(int dev, float *const *ptrs, const size_t *sizes, const 
     for (int i = 0; i < ntensors; i++) {
         if (!sizes[i]) continue;
         EB_REQUIRE(ptrs[i], "fill_multi");
+        if (values[i] == 0.f && lz_defer(cx, st, ptrs[i], sizes[i] * sizeof(float))) continue;
+        EB_WRITES(ptrs[i], sizes[i] * sizeof(float));
         segs.push_back(FillSeg{ptrs[i], (unsigned long long)sizes[i], values[i], 0u});
         const size_t nch = ceil_div(sizes[i], (size_t)kFillChunk);
         for (size_t c = 0; c < nch; c++) chunks.push_back(FillChunk{(unsigned)(segs.size() - 1), (unsigned)c});
@@ -195,6 +230,7 @@ int eddlb200_fill_multi(int dev, float *const *ptrs, const size_t *sizes, const 
 
 int eddlb200_fill(int dev, float *a, size_t n, float v) {
     EB_CTX(dev);
+    if (a && n && v == 0.f && lz_defer(cx, st, a, n * sizeof(float))) return 0;
     return launch1(cx, st, a, a, n, FillF{v}, "gpu_fill_");
 }
 int eddlb200_scale(int dev, const float *a, float *b, float v, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, ScaleF{v}, "gpu_mult"); }
@@ -206,12 +242,33 @@ int eddlb200_relu_fwd(int dev, const float *a, float *b, size_t n) { EB_CTX(dev)
 
 int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b, float *c, int inc_c, size_t n) {
     EB_CTX(dev);
+    if (inc_c && c && c != a && c != b && lz_any(cx)) {
+        int status = 0;
+        if (lz_take(cx, st, c, n * sizeof(float), &status)) return launch3(cx, st, a, b, c, n, AxpbyZeroF{sca, scb}, "gpu_add");
+        if (status) return status;
+    }
+    if (!inc_c && c && (c == b) != (c == a) && lz_any(cx)) {
+        // in place on one operand (Tensor::inc on the GPU is gpu_add(1, A, 1, B, B, 0)): if that operand is known to hold
+        // zeros it need not be read
+        int status = 0;
+        if (lz_take(cx, st, c, n * sizeof(float), &status)) {
+            if (c == b) return launch1(cx, st, a, c, n, AxpbZeroF{sca, scb}, "gpu_add");
+            return launch1(cx, st, b, c, n, ZeroAxpbF{sca, scb}, "gpu_add");
+        }
+        if (status) return status;
+    }
     if (inc_c) return launch3(cx, st, a, b, c, n, AxpbyF<true>{sca, scb}, "gpu_add");
     return launch3(cx, st, a, b, c, n, AxpbyF<false>{sca, scb}, "gpu_add");
 }
 int eddlb200_inc(int dev, const float *a, float *b, size_t n) {
     // gpu_inc: B += A  ==  gpu_add(1, A, 1, B, B, 0) in the reference (tensor_math.cpp Tensor::inc)
     EB_CTX(dev);
+    if (b && b != a && lz_any(cx)) {
+        // b is known to hold zeros: 1*a + 1*0 = a + 0, one read instead of two
+        int status = 0;
+        if (lz_take(cx, st, b, n * sizeof(float), &status)) return launch1(cx, st, a, b, n, AddToZeroF{}, "gpu_inc");
+        if (status) return status;
+    }
     return launch3(cx, st, a, b, b, n, AxpbyF<false>{1.f, 1.f}, "gpu_inc");
 }
 int eddlb200_el_div(int dev, const float *a, const float *b, float *c, int inc_c, size_t n) {
@@ -226,6 +283,11 @@ int eddlb200_el_mult(int dev, const float *a, const float *b, float *c, int inc_
 }
 int eddlb200_relu_bwd(int dev, const float *d, const float *i, float *pd, size_t n) {
     EB_CTX(dev);
+    if (pd && pd != d && pd != i && lz_any(cx)) {
+        int status = 0;
+        if (lz_take(cx, st, pd, n * sizeof(float), &status)) return launch3(cx, st, d, i, pd, n, ReluBwdZeroF{}, "gpu_d_relu");
+        if (status) return status;
+    }
     return launch3(cx, st, d, i, pd, n, ReluBwdF{}, "gpu_d_relu");
 }
 int eddlb200_cce_delta(int dev, const float *y_true, const float *y_pred, float *delta, size_t n) {
@@ -238,6 +300,9 @@ int eddlb200_pad(int dev, const float *a, float *b, int n, int c, int h, int w, 
     EB_REQUIRE(a && b && n >= 0 && c >= 0 && h >= 0 && w >= 0 && top >= 0 && bottom >= 0 && left >= 0 && right >= 0, "gpu_pad");
     size_t total = (size_t)n * c * h * w;
     if (!total) return 0;
+    // the kernel writes the interior of b only: zeros owed to b have to be there first
+    EB_READS(a, total * sizeof(float));
+    EB_READS(b, (size_t)n * c * (h + top + bottom) * (w + left + right) * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, 8.0 * total);
     pad_kernel<false><<<grid_for(total, kBlock), kBlock, 0, st>>>(const_cast<float *>(a), b, total, h, w, top, left, h + top + bottom, w + left + right);
     EB_LAUNCH_CHECK("gpu_pad");
@@ -248,6 +313,8 @@ int eddlb200_pad_bwd(int dev, float *a_delta, const float *b_delta, int n, int c
     EB_REQUIRE(a_delta && b_delta && n >= 0 && c >= 0 && h >= 0 && w >= 0 && top >= 0 && bottom >= 0 && left >= 0 && right >= 0, "gpu_pad_back");
     size_t total = (size_t)n * c * h * w;
     if (!total) return 0;
+    EB_READS(a_delta, total * sizeof(float));
+    EB_READS(b_delta, (size_t)n * c * (h + top + bottom) * (w + left + right) * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, 12.0 * total);
     pad_kernel<true><<<grid_for(total, kBlock), kBlock, 0, st>>>(a_delta, const_cast<float *>(b_delta), total, h, w, top, left, h + top + bottom, w + left + right);
     EB_LAUNCH_CHECK("gpu_pad_back");

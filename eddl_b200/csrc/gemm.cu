@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(TB) sgemm_kernel(const float *__restrict__ A, 
             const int gn = n0 + tx * 4 + j;
             if (gn >= n) continue;
             float *c = C + (size_t)gm * n + gn;
-            *c = inc_c ? __fadd_rn(*c, acc[i][j]) : acc[i][j];
+            *c = inc_c == 1 ? __fadd_rn(*c, acc[i][j]) : (inc_c == 2 ? __fadd_rn(0.f, acc[i][j]) : acc[i][j]);     // 2: c is known to hold zeros
         }
     }
 }
@@ -118,6 +118,13 @@ int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, flo
     EB_CTX(dev);
     EB_REQUIRE(a && b && c && m >= 0 && n >= 0 && k >= 0, "gpu_mult2D");
     if (m == 0 || n == 0) return 0;
+    EB_READS(a, (size_t)m * k * sizeof(float)); EB_READS(b, (size_t)k * n * sizeof(float));
+    if (inc_c && lz_any(cx) && c != a && c != b) {
+        int status = 0;
+        if (lz_take(cx, st, c, (size_t)m * n * sizeof(float), &status)) inc_c = 2;
+        if (status) return status;
+    }
+    if (inc_c == 1) EB_READS(c, (size_t)m * n * sizeof(float)); else EB_WRITES(c, (size_t)m * n * sizeof(float));
     ProfScope prof(cx, PROF_GEMM, 2.0 * m * (double)n * k);
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
     const int tiles = (int)(grid.x * grid.y);
@@ -141,7 +148,7 @@ int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, flo
     grid.z = splits;
     sgemm_kernel<<<grid, TB, 0, st>>>(a, ta, b, tb, c, inc_c, m, n, k, kps, part);
     EB_LAUNCH_CHECK("gpu_mult2D");
-    sgemm_combine_kernel<<<grid_for(count, 256), 256, 0, st>>>(part, c, count, splits, inc_c);
+    sgemm_combine_kernel<<<grid_for(count, 256), 256, 0, st>>>(part, c, count, splits, inc_c == 1);
     EB_LAUNCH_CHECK("gpu_mult2D(combine)");
     return 0;
 }
@@ -151,6 +158,8 @@ int eddlb200_sum2d_rowwise(int dev, const float *a, const float *b, float *c, in
     EB_REQUIRE(a && b && c && rows >= 0 && cols >= 0, "gpu_sum2D_rowwise");
     const size_t total = (size_t)rows * cols;
     if (!total) return 0;
+    EB_READS(a, total * sizeof(float)); EB_READS(b, (size_t)cols * sizeof(float));
+    if (c != a) EB_WRITES(c, total * sizeof(float));
     rowbias_kernel<<<grid_for(total, 256), 256, 0, st>>>(a, b, c, total, cols);
     EB_LAUNCH_CHECK("gpu_sum2D_rowwise");
     return 0;
@@ -159,6 +168,8 @@ int eddlb200_sum2d_rowwise(int dev, const float *a, const float *b, float *c, in
 int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols, int axis, int inc_b) {
     EB_CTX(dev);
     EB_REQUIRE(a && b && rows >= 0 && cols >= 0 && (axis == 0 || axis == 1), "gpu_reduce_sum2D");
+    EB_READS(a, (size_t)rows * cols * sizeof(float));
+    if (inc_b) EB_READS(b, (size_t)(axis == 0 ? cols : rows) * sizeof(float)); else EB_WRITES(b, (size_t)(axis == 0 ? cols : rows) * sizeof(float));
     if (axis == 0) {
         if (!cols) return 0;
         colsum_kernel<<<(cols + 255) / 256, 256, 0, st>>>(a, b, rows, cols, inc_b);

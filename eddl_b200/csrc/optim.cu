@@ -100,6 +100,7 @@ int eddlb200_sgd_momentum(int dev, float *p, const float *g, float *m, float lr,
     EB_CTX(dev);
     if (n == 0) return 0;
     EB_REQUIRE(p && g && m, "sgd");
+    EB_READS(p, n * sizeof(float)); EB_READS(g, n * sizeof(float)); EB_READS(m, n * sizeof(float));
     const bool vec = aligned16(p) && aligned16(g) && aligned16(m);
     const size_t n4 = vec ? n / 4 : 0;
     sgd_kernel<<<grid_for(vec ? (n4 ? n4 : 1) : n, kBlock), kBlock, 0, st>>>(p, g, m, lr, mu, n4, n);
@@ -116,6 +117,7 @@ int eddlb200_sgd_momentum_multi(int dev, float *const *p, const float *const *g,
     for (int i = 0; i < ntensors; i++) {
         if (sizes[i] == 0) continue;
         EB_REQUIRE(p[i] && g[i] && m[i], "sgd_multi");
+        EB_READS(p[i], sizes[i] * sizeof(float)); EB_READS(g[i], sizes[i] * sizeof(float)); EB_READS(m[i], sizes[i] * sizeof(float));
         refs.push_back(TensorRef{p[i], g[i], m[i], (unsigned long long)sizes[i]});
         const size_t nch = ceil_div(sizes[i], (size_t)kChunk);
         for (size_t c = 0; c < nch; c++) chunks.push_back(Chunk{(unsigned)(refs.size() - 1), (unsigned)c});
@@ -146,6 +148,7 @@ int eddlb200_adam(int dev, float *p, float *g, float *m, float *v, float lr, flo
     EB_CTX(dev);
     if (n == 0) return 0;
     EB_REQUIRE(p && g && m && v && t >= 1, "adam");
+    EB_READS(p, n * sizeof(float)); EB_READS(g, n * sizeof(float)); EB_READS(m, n * sizeof(float)); EB_READS(v, n * sizeof(float));
     // 1 - pow(beta, t) is a double in the reference (std::pow(float, int), optim_adam.cpp:103-107),
     // narrowed to float by div_(float), which then multiplies by the float reciprocal
     // (tensor_math.cpp:1186-1188).

@@ -85,7 +85,7 @@ __device__ __forceinline__ void covering(int v, int k, int s, int pad, int on, i
 template <bool MAX, typename IDX>
 __global__ void __launch_bounds__(kBlock) pool_bwd_kernel(const float *__restrict__ d, const float *__restrict__ ind_x,
                                                           const float *__restrict__ ind_y, float *__restrict__ id,
-                                                          size_t total_in, PoolGeom g) {
+                                                          size_t total_in, PoolGeom g, int id_zero) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const float ksize = (float)(g.kr * g.kc);
     for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < total_in; q += stride) {
@@ -97,8 +97,9 @@ __global__ void __launch_bounds__(kBlock) pool_bwd_kernel(const float *__restric
         int oi0, oi1, oj0, oj1;
         covering(y, g.kr, g.sr, g.pt, g.oh, oi0, oi1);
         covering(x, g.kc, g.sc, g.pl, g.ow, oj0, oj1);
-        float acc = id[q];
-        bool touched = false;
+        // id_zero: the input delta is known to hold zeros; it is written in full and never read
+        float acc = id_zero ? 0.f : id[q];
+        bool touched = id_zero != 0;
         const size_t obase = plane * (size_t)g.oh * g.ow;
         if (oi1 - oi0 <= 1 && oj1 - oj0 <= 1) {
             // at most 2 x 2 covering windows (kernel <= 2 * stride, the usual case): all loads go out together, with no
@@ -162,6 +163,8 @@ int eddlb200_maxpool2d_fwd(int dev, const float *in, float *out, float *ind_x, f
     const size_t total = (size_t)n * c * oh * ow;
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    EB_READS(in, (size_t)n * c * ih * iw * sizeof(float));
+    EB_WRITES(out, total * sizeof(float)); EB_WRITES(ind_x, total * sizeof(float)); EB_WRITES(ind_y, total * sizeof(float));
     ProfScope prof(cx, PROF_POOL, 4.0 * n * c * ih * iw + 12.0 * total);
     maxpool_fwd_kernel<<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, ind_x, ind_y, total, g);
     EB_LAUNCH_CHECK("gpu_mpool2D");
@@ -176,9 +179,13 @@ int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const fl
     const size_t total = (size_t)n * c * ih * iw;
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
-    ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + 8.0 * total);
-    if (total < (size_t(1) << 32)) pool_bwd_kernel<true, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g);
-    else pool_bwd_kernel<true, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g);
+    const size_t ob = (size_t)n * c * oh * ow * sizeof(float);
+    EB_READS(d, ob); EB_READS(ind_x, ob); EB_READS(ind_y, ob);
+    int id_zero = 0;
+    if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
+    ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + (id_zero ? 4.0 : 8.0) * total);
+    if (total < (size_t(1) << 32)) pool_bwd_kernel<true, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g, id_zero);
+    else pool_bwd_kernel<true, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g, id_zero);
     EB_LAUNCH_CHECK("gpu_mpool2D_back");
     return 0;
 }
@@ -191,6 +198,8 @@ int eddlb200_avgpool2d_fwd(int dev, const float *in, float *out, int n, int c, i
     const size_t total = (size_t)n * c * oh * ow;
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
+    EB_READS(in, (size_t)n * c * ih * iw * sizeof(float));
+    EB_WRITES(out, total * sizeof(float));
     ProfScope prof(cx, PROF_POOL, 4.0 * n * c * ih * iw + 4.0 * total);
     avgpool_fwd_kernel<<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, total, g);
     EB_LAUNCH_CHECK("gpu_avgpool2D");
@@ -205,9 +214,12 @@ int eddlb200_avgpool2d_bwd(int dev, const float *d, float *id, int n, int c, int
     const size_t total = (size_t)n * c * ih * iw;
     if (!total) return 0;
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
-    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + 8.0 * total);
-    if (total < (size_t(1) << 32)) pool_bwd_kernel<false, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g);
-    else pool_bwd_kernel<false, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g);
+    EB_READS(d, (size_t)n * c * oh * ow * sizeof(float));
+    int id_zero = 0;
+    if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
+    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + (id_zero ? 4.0 : 8.0) * total);
+    if (total < (size_t(1) << 32)) pool_bwd_kernel<false, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g, id_zero);
+    else pool_bwd_kernel<false, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g, id_zero);
     EB_LAUNCH_CHECK("gpu_avgpool2D_back");
     return 0;
 }

@@ -35,9 +35,13 @@ struct DevCtx {
     struct ProfRec { int kind; double work; cudaEvent_t a, b; };
     std::vector<ProfRec> prof_recs;
     std::vector<cudaEvent_t> prof_pool;
+    // deferred zero fills: start address -> bytes (disjoint ranges)
+    bool lz_on = false;
+    std::map<uintptr_t, size_t> lz;
 };
 
 static DevCtx g_ctx[EDDLB200_MAX_DEVICES];
+static bool g_lz_default = false;      // deferred zero fills: contexts created later start with this setting
 static std::mutex g_init_mu;
 static thread_local char g_err[512] = "";
 
@@ -67,6 +71,7 @@ static int init_locked(int dev) {
     if ((e = cudaMalloc((void **)&c.d_scalars, 64 * sizeof(float))) != cudaSuccess) return cuda_status(e, "cudaMalloc");
     for (int i = 0; i < 16; i++) { cudaEventCreate(&c.ev_start[i]); cudaEventCreate(&c.ev_stop[i]); }
     c.dev = dev;
+    c.lz_on = g_lz_default;
     c.ready = true;
     return 0;
 }
@@ -82,6 +87,7 @@ DevCtx *ctx(int dev) {
     return &c;
 }
 
+DevCtx *ctx_peek(int dev) { return (dev >= 0 && dev < EDDLB200_MAX_DEVICES && g_ctx[dev].ready) ? &g_ctx[dev] : nullptr; }
 cudaStream_t stream_of(DevCtx *c) { return c->stream; }
 float *host_scalars(DevCtx *c) { return c->h_scalars; }
 float *dev_scalars(DevCtx *c) { return c->d_scalars; }
@@ -114,6 +120,74 @@ void *scratch(DevCtx *c, size_t bytes) {
     if (cudaMalloc(&c->scratch_ptr, want) != cudaSuccess) { set_error(cudaErrorMemoryAllocation, "scratch arena of %zu bytes", want); return nullptr; }
     c->scratch_bytes = want;
     return c->scratch_ptr;
+}
+
+// ---- deferred zero fills ------------------------------------------------------------------------------
+constexpr size_t kLazyZeroMinBytes = size_t(256) << 10;      // smaller fills are cheaper to run (batched) than to track
+
+// totals over the process, printed at exit when EDDL_B200_LZ_STATS is set
+static struct LzStats { unsigned long long deferred = 0, taken = 0, dropped = 0, written = 0; double written_bytes = 0, deferred_bytes = 0;
+    ~LzStats() { if (getenv("EDDL_B200_LZ_STATS")) fprintf(stderr, "[lazy_zero] deferred %llu (%.1f MB) taken %llu dropped %llu written %llu (%.1f MB)\n", deferred, deferred_bytes / 1e6, taken, dropped, written, written_bytes / 1e6); } } g_lzs;
+bool lz_any(DevCtx *c) { return !c->lz.empty(); }
+
+// Visit every deferred range that overlaps [p, p + bytes): `covered` tells whether the range lies inside it.
+// The visitor may not touch the map; visited ranges are erased afterwards.
+template <typename V>
+static int lz_visit(DevCtx *c, const void *p, size_t bytes, V visit) {
+    const uintptr_t lo = (uintptr_t)p, hi = lo + bytes;
+    auto it = c->lz.upper_bound(lo);
+    if (it != c->lz.begin()) { auto prev = std::prev(it); if (prev->first + prev->second > lo) it = prev; }
+    int status = 0;
+    while (it != c->lz.end() && it->first < hi) {
+        const bool covered = it->first >= lo && it->first + it->second <= hi;
+        if (!status) status = visit(it->first, it->second, covered);
+        it = c->lz.erase(it);
+    }
+    return status;
+}
+
+int lz_read(DevCtx *c, cudaStream_t st, const void *p, size_t bytes) {
+    if (c->lz.empty() || !bytes) return 0;
+    return lz_visit(c, p, bytes, [&](uintptr_t a, size_t n, bool) { g_lzs.written++; g_lzs.written_bytes += n; return launch_zero_fill(c, st, (float *)a, n / sizeof(float)); });
+}
+int lz_write(DevCtx *c, cudaStream_t st, const void *p, size_t bytes) {
+    if (c->lz.empty() || !bytes) return 0;
+    return lz_visit(c, p, bytes, [&](uintptr_t a, size_t n, bool covered) { if (covered) g_lzs.dropped++; else { g_lzs.written++; g_lzs.written_bytes += n; } return covered ? 0 : launch_zero_fill(c, st, (float *)a, n / sizeof(float)); });
+}
+bool lz_take(DevCtx *c, cudaStream_t st, const void *p, size_t bytes, int *status) {
+    *status = 0;
+    if (c->lz.empty() || !bytes) return false;
+    auto it = c->lz.find((uintptr_t)p);
+    if (it != c->lz.end() && it->second == bytes) { c->lz.erase(it); g_lzs.taken++; return true; }
+    *status = lz_read(c, st, p, bytes);
+    return false;
+}
+bool lz_defer(DevCtx *c, cudaStream_t st, void *p, size_t bytes) {
+    if (!c->lz_on || bytes < kLazyZeroMinBytes || (bytes % sizeof(float))) return false;
+    // older deferred fills inside the new range are superseded; ones that stick out are written now
+    if (lz_write(c, st, p, bytes) != 0) return false;
+    c->lz[(uintptr_t)p] = bytes;
+    g_lzs.deferred++; g_lzs.deferred_bytes += bytes;
+    return true;
+}
+void lz_forget(DevCtx *c, const void *p, size_t bytes) {
+    if (c->lz.empty()) return;
+    lz_visit(c, p, bytes, [](uintptr_t, size_t, bool) { return 0; });
+}
+int lz_set_all(int on) {
+    g_lz_default = on != 0;
+    int status = 0;
+    for (int d = 0; d < EDDLB200_MAX_DEVICES; d++) {
+        DevCtx *c = &g_ctx[d];
+        if (!c->ready) continue;
+        c->lz_on = g_lz_default;
+        if (!on && !c->lz.empty()) {
+            if (cudaSetDevice(d) != cudaSuccess) { status = set_error(EDDLB200_ENOINIT, "cudaSetDevice(%d) failed", d); continue; }
+            for (auto &kv : c->lz) if (!status) status = launch_zero_fill(c, c->stream, (float *)kv.first, kv.second / sizeof(float));
+            c->lz.clear();
+        }
+    }
+    return status;
 }
 
 static size_t round_size(size_t b) {
@@ -178,6 +252,7 @@ int eddlb200_free(int dev, void *p) {
     size_t sz = it->second;
     cx->live.erase(it);
     cx->bytes_in_use -= sz;
+    lz_forget(cx, p, sz);
     // All work of this library runs on one stream per device, so a block handed out
     // again is only touched by work ordered after everything that used it before.
     cx->free_blocks.emplace(sz, p); cx->bytes_cached += sz;
@@ -195,6 +270,7 @@ int eddlb200_mem_info(int dev, size_t *in_use, size_t *cached) {
 int eddlb200_memcpy_h2d(int dev, void *dst, const void *src, size_t bytes) {
     EB_CTX(dev);
     if (bytes == 0) return 0;
+    EB_WRITES(dst, bytes);
     cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     return cuda_status(e, "gpu_copy_to_gpu");
@@ -203,12 +279,14 @@ int eddlb200_memcpy_h2d(int dev, void *dst, const void *src, size_t bytes) {
 int eddlb200_memcpy_h2d_async(int dev, void *dst, const void *src, size_t bytes) {
     EB_CTX(dev);
     if (bytes == 0) return 0;
+    EB_WRITES(dst, bytes);
     return cuda_status(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st), "memcpy_h2d_async");
 }
 
 int eddlb200_memcpy_d2h(int dev, void *dst, const void *src, size_t bytes) {
     EB_CTX(dev);
     if (bytes == 0) return 0;
+    EB_READS(src, bytes);
     cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     return cuda_status(e, "gpu_copy_from_gpu");
@@ -217,6 +295,8 @@ int eddlb200_memcpy_d2h(int dev, void *dst, const void *src, size_t bytes) {
 int eddlb200_memcpy_d2d(int dev, void *dst, const void *src, size_t bytes) {
     EB_CTX(dev);
     if (bytes == 0) return 0;
+    EB_READS(src, bytes);
+    EB_WRITES(dst, bytes);
     return cuda_status(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st), "gpu_copy_gpu");
 }
 

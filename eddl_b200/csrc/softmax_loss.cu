@@ -120,6 +120,8 @@ int eddlb200_softmax_fwd_nd(int dev, const float *a, float *b, int outer, int co
     const long long ns = (long long)outer * inner;
     EB_REQUIRE(ns < 0x7fffffffLL, "gpu_full_softmax");
     if (!ns) return 0;
+    EB_READS(a, (size_t)ns * cols * sizeof(float));
+    if (b != a) EB_WRITES(b, (size_t)ns * cols * sizeof(float));
     softmax_fwd_kernel<<<grid_for((size_t)ns * 32, kBlock), kBlock, 0, st>>>(a, b, (int)ns, cols, inner);
     EB_LAUNCH_CHECK("gpu_full_softmax");
     return 0;
@@ -131,6 +133,7 @@ int eddlb200_softmax_bwd_nd(int dev, const float *d, const float *s, float *pd, 
     const long long ns = (long long)outer * inner;
     EB_REQUIRE(ns < 0x7fffffffLL, "gpu_d_full_softmax");
     if (!ns) return 0;
+    EB_READS(d, (size_t)ns * cols * sizeof(float)); EB_READS(s, (size_t)ns * cols * sizeof(float)); EB_READS(pd, (size_t)ns * cols * sizeof(float));
     softmax_bwd_kernel<<<grid_for((size_t)ns * 32, kBlock), kBlock, 0, st>>>(d, s, pd, (int)ns, cols, inner);
     EB_LAUNCH_CHECK("gpu_d_full_softmax");
     return 0;
@@ -140,6 +143,7 @@ int eddlb200_cce_value(int dev, const float *y_true, const float *y_pred, int ro
     EB_CTX(dev);
     EB_REQUIRE(y_true && y_pred && host_out && rows >= 0 && cols > 0, "gpu_categorical_cross_entropy");
     float *dsc = dev_scalars(cx), *hsc = host_scalars(cx);
+    EB_READS(y_true, (size_t)rows * cols * sizeof(float)); EB_READS(y_pred, (size_t)rows * cols * sizeof(float));
     cudaError_t e = cudaMemsetAsync(dsc, 0, sizeof(float), st);
     if (e != cudaSuccess) return cuda_status(e, "gpu_categorical_cross_entropy");
     if (rows) {
@@ -157,6 +161,7 @@ int eddlb200_accuracy(int dev, const float *y_true, const float *y_pred, int row
     EB_CTX(dev);
     EB_REQUIRE(y_true && y_pred && host_out && rows >= 0 && cols > 0, "gpu_accuracy");
     int *dsc = (int *)(dev_scalars(cx) + 1), *hsc = (int *)(host_scalars(cx) + 1);
+    EB_READS(y_true, (size_t)rows * cols * sizeof(float)); EB_READS(y_pred, (size_t)rows * cols * sizeof(float));
     cudaError_t e = cudaMemsetAsync(dsc, 0, sizeof(int), st);
     if (e != cudaSuccess) return cuda_status(e, "gpu_accuracy");
     if (rows) {

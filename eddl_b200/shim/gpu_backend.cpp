@@ -89,11 +89,24 @@ void check_cublas(cublasStatus_t status, const char *f) {
 void check_curand(curandStatus_t status, const char *f) {
     if (status != CURAND_STATUS_SUCCESS) throw std::runtime_error(std::string("[CURAND ERROR]: ") + f);
 }
-void gpu_set_device(int device) { ok(eddlb200_init(device), "gpu_set_device"); }
-void gpu_init(int device) { ok(eddlb200_init(device), "gpu_init"); }
+namespace {
+// Net::do_reset zeroes every delta tensor at the start of a step, and every backward kernel then ADDS into its parent's
+// delta.  With "lazy_zero" on, the library records those fills instead of running them and lets the first accumulating
+// kernel store its result (EDDL_B200_LAZY_ZERO=0 runs every fill as issued).
+void configure_once() {
+    static bool done = false;
+    if (done) return;
+    done = true;
+    const char *e = getenv("EDDL_B200_LAZY_ZERO");
+    ok(eddlb200_set_option("lazy_zero", (e && e[0] == '0') ? 0 : 1), "gpu_init");
+}
+}
+void gpu_set_device(int device) { configure_once(); ok(eddlb200_init(device), "gpu_set_device"); }
+void gpu_init(int device) { configure_once(); ok(eddlb200_init(device), "gpu_init"); }
 int gpu_devices() { int n = 0; eddlb200_device_count(&n); return n; }
 
 float *gpu_create_tensor(int dev, int size) {
+    configure_once();
     void *p = nullptr;
     ok(eddlb200_alloc(dev, (size_t)size * sizeof(float), &p), "gpu_create_tensor");
     return (float *)p;

@@ -184,7 +184,13 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *      (3xTF32 split on the tensor cores or fp32 FMA), 1 = plain TF32, 2 = TF32 main product plus
  *      bf16 cross terms of the split (forward and backward-data; about four times the rounding error
  *      of 0, still below 1e-5 relative; backward-weight runs as 0).  Any other value is EINVAL. */
-/* Options: "conv_path" 0 = tensor-core kernel where it applies (default), 1 = fp32 FMA kernel only. */
+/* Options: "conv_path" 0 = tensor-core kernel where it applies (default), 1 = fp32 FMA kernel only.
+ *          "lazy_zero" 1 = eddlb200_fill / eddlb200_fill_multi of 256 KB or more with 0.0f only record the range; the
+ *          zeros are written when an entry point of this library reads the range, dropped when one overwrites all of
+ *          it, and an accumulating kernel (conv2d_bwd_data, bn_bwd, relu_bwd, inc, axpby with inc_c, pool backward)
+ *          that owns the whole range stores its result instead of adding to it (same bits).  Off by default: device
+ *          code outside this library does not see a deferred fill.  0 writes everything still deferred and returns
+ *          to immediate fills. */
 int eddlb200_set_option(const char *name, int value);
 int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias /* may be null */, float *y,
                         int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,

@@ -227,7 +227,11 @@ def run_b200_arm(args):
                 "achieved": achieved, "peak": tc_peak, "unit": "TFLOP/s", "frac": achieved / tc_peak if tc_peak else None,
                 "peak_source": "%s bf16_tflops_sustained / 2 (TF32 rate) / 3 (3xTF32 split)" % peak_src,
                 "launches": conv_calls, "avg_launch_ms": conv_ms / conv_calls if conv_calls else None,
-                "flops_per_step": conv_fl / args.steps, "traffic": None,
+                "flops_per_step": conv_fl / args.steps,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch (profiles/conv_fwd_n64_c256_56x56_k3_igemm_tc.md)
+                "traffic": 599.1e6,
+                "traffic_of": "one forward launch of the N=64 C=K=256 56x56 3x3 layer under ncu; its algorithmic bytes "
+                              "(input + weights + output once) are 413.4e6",
                 "share_of_step": conv_ms / (ms.value if ms.value else 1.0)}
     hbm = {}
     for nm in ("bn_fwd", "bn_bwd", "elementwise", "pool", "optimizer"):

@@ -3,6 +3,7 @@
     python -m eddl_b200.microbench conv [--precision 0|1|2] [--batch-scale 1.0] [--iters 5]
     python -m eddl_b200.microbench hbm
     python -m eddl_b200.microbench allreduce          (under torchrun for N > 1)
+    python -m eddl_b200.microbench step [--net resnet50] [--batch 64] [--steps 1]
 
 conv      forward / backward-data / backward-weight at the four Conv2D microbenchmark shapes (--set resnet: ResNet-50's layers)
           (N=64 C=K=256 56x56 3x3; N=64 C=1024 K=256 14x14 1x1; N=64 C=3 K=64 224x224 7x7 s2 p3; N=32 C=K=512 7x7 3x3),
@@ -10,6 +11,8 @@ conv      forward / backward-data / backward-weight at the four Conv2D microbenc
 hbm       BatchNorm forward/backward, ReLU forward/backward, max-pool, axpby, fused SGD at ResNet-50 sizes,
           GB/s = algorithmic bytes / time.
 allreduce parameter averaging over NCCL for 1 KB ... 1 GB buffers: algbw = S/t, busbw = algbw * 2(N-1)/N.
+step      builds the net through the drop-in library, runs one train_batch on host buffers and then --steps steps
+          with the batch resident in HBM, and exits: the short program to put under a profiler's launch list.
 Each line of output is one JSON object.
 """
 import argparse
@@ -187,17 +190,42 @@ def run_allreduce(args):
         L.call("comm_destroy", local)
 
 
+def run_step(args):
+    import time
+    from . import capi, harness
+    L = capi.lib(); L.call("init", 0)
+    G = harness.load()
+    hw, classes = (224, 1000) if args.net != "cnn" else (28, 10)
+    net = harness.NetHarness(G, args.net, device=0, hw=hw, classes=classes, optimizer="sgd_fused", lr=0.1, mu=0.9)
+    net.set_params(harness.init_weights(net.param_info(), seed=1234, mode="he_normal"))
+    rng = np.random.default_rng(0)
+    shape = (args.batch, 3, hw, hw) if args.net != "cnn" else (args.batch, 1, hw, hw)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    y = np.eye(classes, dtype=np.float32)[rng.integers(0, classes, args.batch)]
+    net.train_batch(x, y); net.sync()
+    before = L.launches()
+    t0 = time.perf_counter()
+    loss = net.train_resident(args.steps); net.sync()
+    dt = time.perf_counter() - t0
+    print(json.dumps({"bench": "step", "net": args.net, "batch": args.batch, "steps": args.steps, "loss_sum": loss,
+                      "ms_per_step_wall": 1e3 * dt / max(args.steps, 1), "launches_per_step": (L.launches() - before) / max(args.steps, 1)}), flush=True)
+    net.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["conv", "hbm", "allreduce"])
+    ap.add_argument("what", choices=["conv", "hbm", "allreduce", "step"])
     ap.add_argument("--precision", type=int, default=0)
     ap.add_argument("--set", choices=["micro", "resnet"], default="micro", help="conv shape list: the four microbenchmark shapes or ResNet-50's layers")
     ap.add_argument("--batch-scale", type=float, default=1.0)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--net", default="resnet50", help="step: cnn | vgg16bn | resnet50")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--only", default=None)
     ap.add_argument("--shape", type=int, default=-1, help="index into the conv shape list (default: all)")
     args = ap.parse_args()
-    {"conv": run_conv, "hbm": run_hbm, "allreduce": run_allreduce}[args.what](args)
+    {"conv": run_conv, "hbm": run_hbm, "allreduce": run_allreduce, "step": run_step}[args.what](args)
 
 
 if __name__ == "__main__":

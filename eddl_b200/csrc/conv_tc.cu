@@ -196,14 +196,16 @@ struct Layout {
 //               the next tile whenever tensor memory holds two sets (BN <= 64, or short chains at BN = 128).
 // WGRAD = false (forward, backward-data): A rows are pixels (one thread per row, vector stores); B is the weight operand,
 // prepared once per call by pack_b_kernel.  WGRAD = true (backward-weight): A and B are gathered with one lane per k.
-template <int BN_, int PREC, bool WGRAD>
+// BGATHER (backward-weight of 1x1 stride-1 unpadded convolutions): both operands are contiguous along k = (n, p, q) inside an
+// image, so the producers gather BOTH with 16-byte loads -- eight lanes per 128-byte row, four rows per instruction -- and no TMA.
+template <int BN_, int PREC, bool WGRAD, bool BGATHER = false>
 __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P) {
     constexpr bool SPLIT3 = PREC != 1;                   // operands staged as hi / lo planes
-    constexpr bool CROSS_BF16 = PREC == 2 && !WGRAD;     // cross terms as one bf16 MMA chain
+    constexpr bool CROSS_BF16 = PREC == 2 && !WGRAD && !BGATHER;     // cross terms as one bf16 MMA chain
     using L = Layout<BN_, SPLIT3>;
     constexpr int STAGES = L::STAGES;
     constexpr bool A_ROWMAJOR = !WGRAD;
-    constexpr bool B_TMA = !WGRAD;
+    constexpr bool B_TMA = !WGRAD && !BGATHER;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *stage_base = smem;
@@ -249,7 +251,73 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
     if (warp < 8) {
         // ============================ producers ============================
         constexpr uint32_t B_IMAGE = (uint32_t)L::B_BYTES * (SPLIT3 ? 2u : 1u);
-        if constexpr (A_ROWMAJOR) {
+        if constexpr (BGATHER && !WGRAD) {
+            // Two groups of four warps on alternate K-blocks, as below.  Warp wq of a group gathers rows [32 wq, 32 wq + 32) of
+            // A and its share of B: a quarter warp covers one 128-byte row (lane & 7 = the 16-byte chunk), so every load
+            // instruction reads four whole rows, coalesced, and every store instruction fills four whole swizzle rows.
+            const int group = warp >> 2, wq = warp & 3, sub = lane >> 3, chunk = lane & 7;
+            constexpr int BROWS = BN_ / 4, BI = BROWS / 4;        // B rows per warp and load instructions for them
+            int offA[8], offB[BI], rows_of = -1;
+            float4 a4[8], b4[BI];
+            auto load = [&](int mn, int kblock) {
+                if (mn != rows_of) {
+                    rows_of = mn;
+                    const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) { const int m = m0 + wq * 32 + 4 * i + sub; offA[i] = m < P.M_total ? __ldg(P.rowA + m).x : 0; }
+#pragma unroll
+                    for (int i = 0; i < BI; i++) { const int n = n0 + wq * BROWS + 4 * i + sub; offB[i] = n < P.N_total ? __ldg(P.rowB + n) : 0; }
+                }
+                // groups of four k are contiguous and 16-byte aligned in both tensors (checked by the dispatcher)
+                const float *pa = P.srcA + __ldg(P.kC + kblock * BK + chunk * 4);
+                const float *pb = P.srcB + __ldg(P.kB + kblock * BK + chunk * 4);
+#pragma unroll
+                for (int i = 0; i < 8; i++) a4[i] = ldg4(pa + offA[i]);
+#pragma unroll
+                for (int i = 0; i < BI; i++) b4[i] = ldg4(pb + offB[i]);
+            };
+            auto put = [&](uint8_t *hi_plane, uint8_t *lo_plane, int row, float4 v) {
+                const uint32_t off = swz(row, chunk * 4);
+                if (SPLIT3) {
+                    float4 hi, lo;
+                    split_tf32(v.x, hi.x, lo.x); split_tf32(v.y, hi.y, lo.y); split_tf32(v.z, hi.z, lo.z); split_tf32(v.w, hi.w, lo.w);
+                    *(float4 *)(hi_plane + off) = hi; *(float4 *)(lo_plane + off) = lo;
+                } else {
+                    *(float4 *)(hi_plane + off) = v;
+                }
+            };
+            auto store = [&](int s) {
+                uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
+                uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
+                uint8_t *sB_hi = sA_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
+                uint8_t *sB_lo = sB_hi + L::B_BYTES;
+#pragma unroll
+                for (int i = 0; i < 8; i++) put(sA_hi, sA_lo, wq * 32 + 4 * i + sub, a4[i]);
+#pragma unroll
+                for (int i = 0; i < BI; i++) put(sB_hi, sB_lo, wq * BROWS + 4 * i + sub, b4[i]);
+            };
+            int t = blockIdx.x, kb0 = 0, nkb = 0, it = group;
+            auto settle = [&]() {
+                while (t < total_tiles) {
+                    kb_range(t, kb0, nkb);
+                    if (it < nkb) return;
+                    it -= nkb; t += gridDim.x;
+                }
+            };
+            settle();
+            if (t < total_tiles) load(t % tiles_mn, kb0 + it);
+            for (int g = group; t < total_tiles; g += 2) {
+                const int s = g % STAGES;
+                const uint32_t par = ((g / STAGES) & 1) ^ 1;
+                if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+                store(s);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                it += 2; settle();
+                if (t < total_tiles) load(t % tiles_mn, kb0 + it);
+            }
+        } else if constexpr (A_ROWMAJOR) {
             // Two groups of four warps work on alternate K-blocks (group 0 the even ones of the CTA's K-block
             // sequence, group 1 the odd ones), one thread per tile row and all 32 k of the block per thread.
             // The groups drift out of phase, so one group's loads are in flight while the other splits and stores.
@@ -371,7 +439,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             const int group = warp >> 2, wq = warp & 3, gtid = tid & 127;
             int2 *rowsA = sRowA + group * BM;
             int *rowsB = sRowB + group * BN_;
-            float av[RA], bv[RB];
+            float av[RA], bv[BGATHER ? 1 : RB];
+            // WGRAD with BGATHER: the dy operand (contiguous along k inside an image) is gathered with 16-byte loads, a
+            // quarter warp per 128-byte row; the x operand (shifted by the filter taps) keeps one lane per k
+            constexpr int BI = RB / 4;
+            const int sub = lane >> 3, chunk = lane & 7;
+            int offB[BGATHER ? BI : 1];
+            float4 b4[BGATHER ? BI : 1];
             int row_tile = -1;
             auto load_tiles = [&](int mn, int kblock) {
                 if (mn != row_tile) {
@@ -380,8 +454,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");      // nobody still reads the previous tile's tables
                     rowsA[gtid] = (m0 + gtid < P.M_total) ? __ldg(P.rowA + m0 + gtid) : make_int2(0, INVALID_Y << 16);
-                    if (gtid < BN_) rowsB[gtid] = (n0 + gtid < P.N_total) ? __ldg(P.rowB + n0 + gtid) : -1;
+                    if (!BGATHER && gtid < BN_) rowsB[gtid] = (n0 + gtid < P.N_total) ? __ldg(P.rowB + n0 + gtid) : -1;
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
+                    if constexpr (BGATHER) {
+#pragma unroll
+                        for (int i = 0; i < BI; i++) { const int n = n0 + wq * RB + 4 * i + sub; offB[i] = n < P.N_total ? __ldg(P.rowB + n) : 0; }
+                    }
                 }
                 const int kbase = kblock * BK;
                 const int2 ke = __ldg(P.kA + kbase + lane);
@@ -394,12 +472,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
                     av[r] = ok ? __ldg(base + re.x) : 0.f;
                 }
-                const int kb = __ldg(P.kB + kbase + lane);
-                const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
+                if constexpr (BGATHER) {
+                    const float *pb = P.srcB + __ldg(P.kB + kbase + chunk * 4);
 #pragma unroll
-                for (int r = 0; r < RB; r++) {
-                    const int ro = rowsB[wq * RB + r];
-                    bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
+                    for (int i = 0; i < BI; i++) b4[i] = ldg4(pb + offB[i]);
+                } else {
+                    const int kb = __ldg(P.kB + kbase + lane);
+                    const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
+#pragma unroll
+                    for (int r = 0; r < RB; r++) {
+                        const int ro = rowsB[wq * RB + r];
+                        bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
+                    }
                 }
             };
             auto store_tiles = [&](int s) {
@@ -413,11 +497,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     if (SPLIT3) { float hi, lo; split_tf32(av[r], hi, lo); *(float *)(sA_hi + off) = hi; *(float *)(sA_lo + off) = lo; }
                     else *(float *)(sA_hi + off) = av[r];
                 }
+                if constexpr (BGATHER) {
 #pragma unroll
-                for (int r = 0; r < RB; r++) {
-                    const uint32_t off = swz(wq * RB + r, lane);
-                    if (SPLIT3) { float hi, lo; split_tf32(bv[r], hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
-                    else *(float *)(sB_hi + off) = bv[r];
+                    for (int i = 0; i < BI; i++) {
+                        const uint32_t off = swz(wq * RB + 4 * i + sub, chunk * 4);
+                        const float4 v = b4[i];
+                        if (SPLIT3) {
+                            float4 hi, lo;
+                            split_tf32(v.x, hi.x, lo.x); split_tf32(v.y, hi.y, lo.y); split_tf32(v.z, hi.z, lo.z); split_tf32(v.w, hi.w, lo.w);
+                            *(float4 *)(sB_hi + off) = hi; *(float4 *)(sB_lo + off) = lo;
+                        } else {
+                            *(float4 *)(sB_hi + off) = v;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < RB; r++) {
+                        const uint32_t off = swz(wq * RB + r, lane);
+                        if (SPLIT3) { float hi, lo; split_tf32(bv[r], hi, lo); *(float *)(sB_hi + off) = hi; *(float *)(sB_lo + off) = lo; }
+                        else *(float *)(sB_hi + off) = bv[r];
+                    }
                 }
             };
 
@@ -704,26 +803,26 @@ __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ s
     }
 }
 
-template <int BN_, int PREC, bool WGRAD>
+template <int BN_, int PREC, bool WGRAD, bool BGATHER = false>
 int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
     using L = Layout<BN_, PREC != 1>;
     static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
     bool &configured = configured_dev[dev];
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, PREC, WGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e, "conv_tc(smem attribute)");
         configured = true;
     }
-    igemm_tc_kernel<BN_, PREC, WGRAD><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
+    igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
     EB_LAUNCH_CHECK("conv_tc");
     return 0;
 }
 
-template <int PREC, bool WGRAD>
+template <int PREC, bool WGRAD, bool BGATHER = false>
 int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn, int dev) {
-    if (bn == 32) return launch_variant<32, PREC, WGRAD>(cx, st, P, grid, dev);
-    if (bn == 64) return launch_variant<64, PREC, WGRAD>(cx, st, P, grid, dev);
-    return launch_variant<128, PREC, WGRAD>(cx, st, P, grid, dev);
+    if (bn == 32) return launch_variant<32, PREC, WGRAD, BGATHER>(cx, st, P, grid, dev);
+    if (bn == 64) return launch_variant<64, PREC, WGRAD, BGATHER>(cx, st, P, grid, dev);
+    return launch_variant<128, PREC, WGRAD, BGATHER>(cx, st, P, grid, dev);
 }
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
@@ -775,6 +874,14 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         const bool inside = g.kr == 1 && g.kc == 1 && g.pt == 0 && g.pl == 0 && (g.ih - 1) / g.sr < g.oh && (g.iw - 1) / g.sc < g.ow;
         T.check = (inside && T.K_total % BK == 0) ? 0 : (T.rt * T.st_ <= 31 ? 1 : 2);
     }
+    // backward-weight of a 1x1, stride-1, unpadded convolution: k = (n, p, q) is contiguous inside an image for x and for dy, so
+    // both operands can be gathered with 16-byte loads when groups of four k never straddle an image
+    const bool both_rowmajor = mode == 2 && g.kr == 1 && g.kc == 1 && g.sr == 1 && g.sc == 1 && g.pt == 0 && g.pl == 0 &&
+                               g.ih == g.oh && g.iw == g.ow && (g.oh * g.ow) % 4 == 0 && T.K_total % BK == 0 &&
+                               aligned16(srcA) && aligned16(srcB);
+    if (both_rowmajor) T.check = 0;
+    // any backward-weight: dy alone has that property whatever the filter and stride
+    const bool b_vector = mode == 2 && (g.oh * g.ow) % 4 == 0 && T.K_total % BK == 0 && aligned16(srcB);
     // the compact k table keeps 27 bits of offset beside the 5-bit tap number
     if (T.check == 1 && (long long)(g.c > g.k ? g.c : g.k) * (g.ih * g.iw > g.oh * g.ow ? g.ih * g.iw : g.oh * g.ow) + (long long)(g.kr + 1) * (g.iw + g.ow) >= (1ll << 26)) T.check = 2;
     P.check = T.check;
@@ -859,7 +966,9 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
     int r;
     // backward-weight has no bf16 variant: precision 2 runs it as precision 0
-    if (mode == 2) r = precision != 1 ? launch_bn<0, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true>(cx, st, P, grid, bn, dev);
+    if (mode == 2 && both_rowmajor) r = precision != 1 ? launch_bn<0, false, true>(cx, st, P, grid, bn, dev) : launch_bn<1, false, true>(cx, st, P, grid, bn, dev);
+    else if (mode == 2 && b_vector) r = precision != 1 ? launch_bn<0, true, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true, true>(cx, st, P, grid, bn, dev);
+    else if (mode == 2) r = precision != 1 ? launch_bn<0, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true>(cx, st, P, grid, bn, dev);
     else if (precision == 0) r = launch_bn<0, false>(cx, st, P, grid, bn, dev);
     else if (precision == 2) r = launch_bn<2, false>(cx, st, P, grid, bn, dev);
     else r = launch_bn<1, false>(cx, st, P, grid, bn, dev);

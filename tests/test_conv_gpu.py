@@ -112,7 +112,9 @@ def test_conv_linearity_at_benchmark_size(lib):
     assert abs(lhs - float(np.sum(a["gw"].astype(np.float64) * w.astype(np.float64)))) <= 1e-5 * abs(lhs)
 
 
-@pytest.mark.parametrize("shape", [(4, 64, 14, 14, 96, 3, 3, 1, (1, 1, 1, 1)), (2, 48, 9, 9, 40, 1, 1, 1, (0, 0, 0, 0)), (2, 16, 20, 20, 24, 3, 3, 2, (1, 1, 1, 1))])
+@pytest.mark.parametrize("shape", [(4, 64, 14, 14, 96, 3, 3, 1, (1, 1, 1, 1)), (2, 48, 9, 9, 40, 1, 1, 1, (0, 0, 0, 0)), (2, 16, 20, 20, 24, 3, 3, 2, (1, 1, 1, 1)),
+                                   # 1x1 stride 1 with p*q a multiple of 4: backward-weight gathers both operands with 16-byte loads
+                                   (4, 48, 8, 8, 40, 1, 1, 1, (0, 0, 0, 0)), (8, 200, 28, 28, 136, 1, 1, 1, (0, 0, 0, 0))])
 def test_tensor_core_path_against_fma_path_and_tf32_mode(lib, shape):
     """The tcgen05 kernel (3xTF32) and the fp32 FMA kernel agree to 1e-5, and so does precision 2 (bf16 cross terms of the
     split, coarser but inside the same bound); plain TF32 (precision 1) stays within 1e-3."""

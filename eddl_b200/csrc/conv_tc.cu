@@ -775,31 +775,51 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
 
 // B operand of forward / backward-data (the weights), prepared once per call: for every (K-block, filter tile) the
 // [BN x 32] tile is written in the exact shared-memory image the MMA reads (K-major SWIZZLE_128B), hi plane then lo
-// plane, so the main kernel fetches it with a single 16-byte-aligned TMA bulk copy.
+// plane, so the main kernel fetches it with a single 16-byte-aligned TMA bulk copy.  The tile is read with consecutive
+// threads along the dimension that is contiguous in the weight tensor -- k for forward (w[f][c*r*s]), the in-channel row
+// for backward-data (w[f][c][r][s] with k = (f, r, s)) -- staged in shared memory, and written out 16 bytes per thread.
 template <int PREC>
 __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ src, const int *__restrict__ rowB, const int *__restrict__ kB,
                                                      float *__restrict__ packed, int bn, int n_total, int tiles_n, int row_fastest) {
-    const int kb = blockIdx.x, nt = blockIdx.y;
     constexpr bool SPLIT3 = PREC != 1;
+    __shared__ float tile[128][BK + 1];
+    const int kb = blockIdx.x, nt = blockIdx.y;
     const size_t image_floats = (size_t)bn * BK * (SPLIT3 ? 2 : 1);
     char *img = (char *)(packed + ((size_t)kb * tiles_n + nt) * image_floats);
     for (int e = threadIdx.x; e < bn * BK; e += blockDim.x) {
-        // consecutive threads follow the dimension that is contiguous in the weight tensor: k for forward
-        // (w[f][c*r*s]), the in-channel row for backward-data (w[f][c][r][s] with k = (f, r, s))
         const int row = row_fastest ? e % bn : e / BK, k = row_fastest ? e / bn : e % BK;
         const int n = nt * bn + row;
         const int ko = kB[kb * BK + k];
-        const float v = (n < n_total && ko >= 0) ? __ldg(src + rowB[n] + ko) : 0.f;
-        const uint32_t off = swz(row, k);
-        if (PREC == 0) { float hi, lo; split_tf32(v, hi, lo); *(float *)(img + off) = hi; *(float *)(img + (size_t)bn * BK * 4 + off) = lo; }
-        else if (PREC == 2) {
-            // plane 0: hi as TF32; plane 1: bf16 row of 64 = [hi(0..31) | lo(0..31)], the partner of the A rows' [lo | hi]
-            float hi, lo; split_tf32(v, hi, lo);
-            *(float *)(img + off) = hi;
-            char *x = img + (size_t)bn * BK * 4;
-            *(__nv_bfloat16 *)(x + swz_chunk(row, k >> 3) + (k & 7) * 2) = __float2bfloat16_rn(hi);
-            *(__nv_bfloat16 *)(x + swz_chunk(row, 4 + (k >> 3)) + (k & 7) * 2) = __float2bfloat16_rn(lo);
-        } else *(float *)(img + off) = v;
+        tile[row][k] = (n < n_total && ko >= 0) ? __ldg(src + rowB[n] + ko) : 0.f;
+    }
+    __syncthreads();
+    char *plane1 = img + (size_t)bn * BK * 4;
+    for (int q = threadIdx.x; q < bn * (BK / 4); q += blockDim.x) {
+        const int row = q / (BK / 4), c = q % (BK / 4);
+        const float4 v = make_float4(tile[row][4 * c], tile[row][4 * c + 1], tile[row][4 * c + 2], tile[row][4 * c + 3]);
+        const uint32_t off = swz(row, 4 * c);
+        if (SPLIT3) {
+            float4 hi, lo;
+            split_tf32(v.x, hi.x, lo.x); split_tf32(v.y, hi.y, lo.y); split_tf32(v.z, hi.z, lo.z); split_tf32(v.w, hi.w, lo.w);
+            *(float4 *)(img + off) = hi;
+            if (PREC == 0) *(float4 *)(plane1 + off) = lo;
+        } else {
+            *(float4 *)(img + off) = v;
+        }
+    }
+    if (PREC == 2) {
+        // plane 1: bf16 row of 64 = [hi(0..31) | lo(0..31)], the partner of the A rows' [lo | hi]; one 16-byte chunk = 8 values
+        for (int q = threadIdx.x; q < bn * 8; q += blockDim.x) {
+            const int row = q / 8, c = q % 8, k0 = (c & 3) * 8;
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float h0, l0, h1, l1;
+                split_tf32(tile[row][k0 + 2 * j], h0, l0); split_tf32(tile[row][k0 + 2 * j + 1], h1, l1);
+                w[j] = c < 4 ? pack_bf16(h0, h1) : pack_bf16(l0, l1);
+            }
+            *(uint4 *)(plane1 + swz_chunk(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
     }
 }
 

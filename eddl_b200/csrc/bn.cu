@@ -285,7 +285,7 @@ int eddlb200_bn_bwd(int dev, int b, int z, int rc, float *delta, const float *op
             if (status) return status;
         }
     }
-    ProfScope prof(cx, PROF_BN_BWD, (pd_zero ? 20.0 : 24.0) * b * (double)z * rc);
+    ProfScope prof(cx, PROF_BN_BWD, 24.0 * b * (double)z * rc);     // canonical count; the pd_zero variant moves 20 B/element
     const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
     const bool vec = (rc % 4 == 0) && aligned16(delta) && aligned16(opa) && aligned16(pdelta);
     dim3 grid(z, S);

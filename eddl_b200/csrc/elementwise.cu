@@ -56,12 +56,14 @@ __global__ void __launch_bounds__(kBlock) map3_scalar_kernel(const float *a, con
 }
 
 template <typename F>
-int launch1(DevCtx *cx, cudaStream_t st, const float *a, float *b, size_t n, F f, const char *what) {
+int launch1(DevCtx *cx, cudaStream_t st, const float *a, float *b, size_t n, F f, const char *what, double bytes_per_element = 8.0) {
     if (n == 0) return 0;
     if (!a || !b) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
     if (!F::ignores_input) EB_READS(a, n * sizeof(float));
     EB_WRITES(b, n * sizeof(float));
-    ProfScope prof(cx, PROF_ELEMENTWISE, 8.0 * n);
+    // profile work = the canonical byte count of the operation (a "destination is zero" variant moves fewer bytes but
+    // is charged like the read-modify-write it replaces)
+    ProfScope prof(cx, PROF_ELEMENTWISE, bytes_per_element * n);
     if (aligned16(a) && aligned16(b)) {
         size_t n4 = n / 4;
         map1_kernel<<<grid_for(n4 ? n4 : 1, kBlock), kBlock, 0, st>>>(a, b, n4, n, f);
@@ -73,13 +75,13 @@ int launch1(DevCtx *cx, cudaStream_t st, const float *a, float *b, size_t n, F f
 }
 
 template <typename F>
-int launch3(DevCtx *cx, cudaStream_t st, const float *a, const float *b, float *c, size_t n, F f, const char *what) {
+int launch3(DevCtx *cx, cudaStream_t st, const float *a, const float *b, float *c, size_t n, F f, const char *what, double bytes_per_element = 0.0) {
     if (n == 0) return 0;
     if (!a || !b || !c) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
     EB_READS(a, n * sizeof(float));
     EB_READS(b, n * sizeof(float));
     if (F::reads_c) EB_READS(c, n * sizeof(float)); else EB_WRITES(c, n * sizeof(float));
-    ProfScope prof(cx, PROF_ELEMENTWISE, (F::reads_c ? 16.0 : 12.0) * n);
+    ProfScope prof(cx, PROF_ELEMENTWISE, (bytes_per_element > 0 ? bytes_per_element : (F::reads_c ? 16.0 : 12.0)) * n);
     if (aligned16(a) && aligned16(b) && aligned16(c)) {
         size_t n4 = n / 4;
         map3_kernel<<<grid_for(n4 ? n4 : 1, kBlock), kBlock, 0, st>>>(a, b, c, n4, n, f);
@@ -244,7 +246,7 @@ int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b
     EB_CTX(dev);
     if (inc_c && c && c != a && c != b && lz_any(cx)) {
         int status = 0;
-        if (lz_take(cx, st, c, n * sizeof(float), &status)) return launch3(cx, st, a, b, c, n, AxpbyZeroF{sca, scb}, "gpu_add");
+        if (lz_take(cx, st, c, n * sizeof(float), &status)) return launch3(cx, st, a, b, c, n, AxpbyZeroF{sca, scb}, "gpu_add", 16.0);
         if (status) return status;
     }
     if (!inc_c && c && (c == b) != (c == a) && lz_any(cx)) {
@@ -252,8 +254,8 @@ int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b
         // zeros it need not be read
         int status = 0;
         if (lz_take(cx, st, c, n * sizeof(float), &status)) {
-            if (c == b) return launch1(cx, st, a, c, n, AxpbZeroF{sca, scb}, "gpu_add");
-            return launch1(cx, st, b, c, n, ZeroAxpbF{sca, scb}, "gpu_add");
+            if (c == b) return launch1(cx, st, a, c, n, AxpbZeroF{sca, scb}, "gpu_add", 12.0);
+            return launch1(cx, st, b, c, n, ZeroAxpbF{sca, scb}, "gpu_add", 12.0);
         }
         if (status) return status;
     }
@@ -266,7 +268,7 @@ int eddlb200_inc(int dev, const float *a, float *b, size_t n) {
     if (b && b != a && lz_any(cx)) {
         // b is known to hold zeros: 1*a + 1*0 = a + 0, one read instead of two
         int status = 0;
-        if (lz_take(cx, st, b, n * sizeof(float), &status)) return launch1(cx, st, a, b, n, AddToZeroF{}, "gpu_inc");
+        if (lz_take(cx, st, b, n * sizeof(float), &status)) return launch1(cx, st, a, b, n, AddToZeroF{}, "gpu_inc", 12.0);
         if (status) return status;
     }
     return launch3(cx, st, a, b, b, n, AxpbyF<false>{1.f, 1.f}, "gpu_inc");
@@ -285,7 +287,7 @@ int eddlb200_relu_bwd(int dev, const float *d, const float *i, float *pd, size_t
     EB_CTX(dev);
     if (pd && pd != d && pd != i && lz_any(cx)) {
         int status = 0;
-        if (lz_take(cx, st, pd, n * sizeof(float), &status)) return launch3(cx, st, d, i, pd, n, ReluBwdZeroF{}, "gpu_d_relu");
+        if (lz_take(cx, st, pd, n * sizeof(float), &status)) return launch3(cx, st, d, i, pd, n, ReluBwdZeroF{}, "gpu_d_relu", 16.0);
         if (status) return status;
     }
     return launch3(cx, st, d, i, pd, n, ReluBwdF{}, "gpu_d_relu");

@@ -183,7 +183,7 @@ int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const fl
     EB_READS(d, ob); EB_READS(ind_x, ob); EB_READS(ind_y, ob);
     int id_zero = 0;
     if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
-    ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + (id_zero ? 4.0 : 8.0) * total);
+    ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + 8.0 * total);     // canonical count, also for the id_zero variant
     if (total < (size_t(1) << 32)) pool_bwd_kernel<true, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g, id_zero);
     else pool_bwd_kernel<true, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g, id_zero);
     EB_LAUNCH_CHECK("gpu_mpool2D_back");
@@ -217,7 +217,7 @@ int eddlb200_avgpool2d_bwd(int dev, const float *d, float *id, int n, int c, int
     EB_READS(d, (size_t)n * c * oh * ow * sizeof(float));
     int id_zero = 0;
     if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
-    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + (id_zero ? 4.0 : 8.0) * total);
+    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + 8.0 * total);
     if (total < (size_t(1) << 32)) pool_bwd_kernel<false, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g, id_zero);
     else pool_bwd_kernel<false, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g, id_zero);
     EB_LAUNCH_CHECK("gpu_avgpool2D_back");

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(kBlock) bn_stats_kernel(const float *__restric
 #pragma unroll 4
         for (unsigned t = sl.begin + threadIdx.x * 4; t < sl.end; t += kBlock * 4) {
             const size_t off = item_offset(t, rc, z, j);
-            const float4 v = ld_stream4(x + off);
+            const float4 v = ldg4(x + off);           // left in L2 on purpose: the apply pass walks its slice backwards
             if (MODE == 0) {
                 a0 += (v.x + v.y) + (v.z + v.w);
                 a1 += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
@@ -134,7 +134,11 @@ __global__ void __launch_bounds__(kBlock) bn_fwd_apply_kernel(const float *__res
     const Slice sl = slice_of(b * rc, nsplit, s);
     if (VEC) {
 #pragma unroll 4
-        for (unsigned t = sl.begin + threadIdx.x * 4; t < sl.end; t += kBlock * 4) {
+        // Backwards through the slice: the statistics pass read it forwards just before, so its tail is what the L2 still
+        // holds; the second read of tensors up to about the L2 size then costs no HBM traffic.
+        for (unsigned it = (sl.end - sl.begin + kBlock * 4 - 1) / (kBlock * 4); it-- > 0;) {
+            const unsigned t = sl.begin + it * (kBlock * 4) + threadIdx.x * 4;
+            if (t >= sl.end) continue;
             const size_t off = item_offset(t, rc, z, j);
             const float4 v = ld_stream4(x + off);
             float4 o, r;
@@ -154,7 +158,9 @@ __global__ void __launch_bounds__(kBlock) bn_fwd_apply_kernel(const float *__res
             }
         }
     } else {
-        for (unsigned t = sl.begin + threadIdx.x; t < sl.end; t += kBlock) {
+        for (unsigned it = (sl.end - sl.begin + kBlock - 1) / kBlock; it-- > 0;) {
+            const unsigned t = sl.begin + it * kBlock + threadIdx.x;
+            if (t >= sl.end) continue;
             const size_t off = item_offset(t, rc, z, j);
             const float o = __fdiv_rn(__fsub_rn(x[off], mean), sigma);
             float r = o;
@@ -192,7 +198,11 @@ __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(float *__restrict_
     const Slice sl = slice_of(b * rc, nsplit, s);
     if (VEC) {
 #pragma unroll 4
-        for (unsigned t = sl.begin + threadIdx.x * 4; t < sl.end; t += kBlock * 4) {
+        // Backwards through the slice: the statistics pass read it forwards just before, so its tail is what the L2 still
+        // holds; the second read of tensors up to about the L2 size then costs no HBM traffic.
+        for (unsigned it = (sl.end - sl.begin + kBlock * 4 - 1) / (kBlock * 4); it-- > 0;) {
+            const unsigned t = sl.begin + it * (kBlock * 4) + threadIdx.x * 4;
+            if (t >= sl.end) continue;
             const size_t off = item_offset(t, rc, z, j);
             float4 d = *reinterpret_cast<const float4 *>(delta + off);
             const float4 o = ld_stream4(opa + off);
@@ -208,7 +218,9 @@ __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(float *__restrict_
             *reinterpret_cast<float4 *>(pdelta + off) = p;
         }
     } else {
-        for (unsigned t = sl.begin + threadIdx.x; t < sl.end; t += kBlock) {
+        for (unsigned it = (sl.end - sl.begin + kBlock - 1) / kBlock; it-- > 0;) {
+            const unsigned t = sl.begin + it * kBlock + threadIdx.x;
+            if (t >= sl.end) continue;
             const size_t off = item_offset(t, rc, z, j);
             float d = delta[off];
             if (affine) { d = __fmul_rn(d, gj); delta[off] = d; }

@@ -102,7 +102,7 @@ inline int grid_for(size_t work_items, int block, int max_blocks_per_sm = 8) {
     return (int)blocks;
 }
 
-inline bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
+__host__ __device__ inline bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
 
 #ifdef __CUDACC__
 __device__ __forceinline__ float warp_sum(float v) {

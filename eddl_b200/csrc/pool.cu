@@ -143,6 +143,51 @@ __global__ void __launch_bounds__(kBlock) pool_bwd_kernel(const float *__restric
     }
 }
 
+// Max-pool backward, one block per (n, c) plane: the plane's output-side tensors (delta and the two argmax coordinates,
+// 12 bytes per output element) are staged in shared memory once, then every input element tests its covering windows
+// there.  Same window order and arithmetic as pool_bwd_kernel; used when the plane fits (12 * oh * ow bytes).
+__global__ void __launch_bounds__(256) maxpool_bwd_plane_kernel(const float *__restrict__ d, const float *__restrict__ ind_x,
+                                                                const float *__restrict__ ind_y, float *__restrict__ id,
+                                                                unsigned planes, PoolGeom g, int id_zero) {
+    extern __shared__ float sm_pool[];
+    const int opl = g.oh * g.ow, ipl = g.ih * g.iw;
+    float *sd = sm_pool, *sx = sm_pool + opl, *sy = sm_pool + 2 * opl;
+    for (unsigned plane = blockIdx.x; plane < planes; plane += gridDim.x) {
+        const size_t obase = (size_t)plane * opl;
+        __syncthreads();                       // the previous plane's readers are done
+        if ((opl & 3) == 0 && aligned16(d) && aligned16(ind_x) && aligned16(ind_y)) {
+            // 16-byte loads, several per thread in flight: the staging is one memory latency, not one per element
+#pragma unroll 4
+            for (int p = threadIdx.x * 4; p < opl; p += blockDim.x * 4) {
+                const float4 a = ldg4(d + obase + p), b = ldg4(ind_x + obase + p), c = ldg4(ind_y + obase + p);
+                *reinterpret_cast<float4 *>(sd + p) = a; *reinterpret_cast<float4 *>(sx + p) = b; *reinterpret_cast<float4 *>(sy + p) = c;
+            }
+        } else {
+            for (int p = threadIdx.x; p < opl; p += blockDim.x) { sd[p] = __ldg(d + obase + p); sx[p] = __ldg(ind_x + obase + p); sy[p] = __ldg(ind_y + obase + p); }
+        }
+        __syncthreads();
+        float *idp = id + (size_t)plane * ipl;
+        int y = threadIdx.x / g.iw, x = threadIdx.x - y * g.iw;
+        const int dy = blockDim.x / g.iw, dx = blockDim.x - dy * g.iw;      // advance of (y, x) per blockDim.x elements
+        for (int q = threadIdx.x; q < ipl; q += blockDim.x) {
+            int oi0, oi1, oj0, oj1;
+            covering(y, g.kr, g.sr, g.pt, g.oh, oi0, oi1);
+            covering(x, g.kc, g.sc, g.pl, g.ow, oj0, oj1);
+            float acc = id_zero ? 0.f : idp[q];
+            bool touched = id_zero != 0;
+            for (int oi = oi0; oi <= oi1; oi++)
+                for (int oj = oj0; oj <= oj1; oj++) {
+                    const int p = oi * g.ow + oj;
+                    // int x = D->indX->ptr[p]  (float -> int conversion in the reference)
+                    if ((int)sx[p] == x && (int)sy[p] == y) { acc = __fadd_rn(acc, sd[p]); touched = true; }
+                }
+            if (touched) idp[q] = acc;
+            x += dx; y += dy;
+            if (x >= g.iw) { x -= g.iw; y++; }
+        }
+    }
+}
+
 int check_geom(const char *what, int n, int c, int ih, int iw, int oh, int ow, int kr, int kc, int sr, int sc, int pt, int pl) {
     if (n < 0 || c < 0 || ih <= 0 || iw <= 0 || oh <= 0 || ow <= 0 || kr <= 0 || kc <= 0 || sr <= 0 || sc <= 0 || pt < 0 || pl < 0)
         return set_error(EDDLB200_EINVAL, "%s: bad geometry", what);
@@ -184,6 +229,23 @@ int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const fl
     int id_zero = 0;
     if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + 8.0 * total);     // canonical count, also for the id_zero variant
+    const size_t plane_smem = (size_t)12 * oh * ow;
+    if (plane_smem <= (size_t)160 * 1024 && ih * iw >= 1024 && (size_t)n * c < 0x7fffffffu) {
+        static bool configured[EDDLB200_MAX_DEVICES] = {};
+        if (!configured[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(maxpool_bwd_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            if (e != cudaSuccess) return cuda_status(e, "gpu_mpool2D_back(smem attribute)");
+            configured[dev] = true;
+        }
+        const unsigned planes = (unsigned)(n * c);
+        int per_sm = (int)((size_t)200 * 1024 / plane_smem);
+        if (per_sm > 8) per_sm = 8;
+        if (per_sm < 1) per_sm = 1;
+        unsigned blocks = planes < (unsigned)(EDDLB200_NUM_SMS * per_sm) ? planes : (unsigned)(EDDLB200_NUM_SMS * per_sm);
+        maxpool_bwd_plane_kernel<<<blocks, 256, plane_smem, st>>>(d, ind_x, ind_y, id, planes, g, id_zero);
+        EB_LAUNCH_CHECK("gpu_mpool2D_back");
+        return 0;
+    }
     if (total < (size_t(1) << 32)) pool_bwd_kernel<true, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g, id_zero);
     else pool_bwd_kernel<true, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, ind_x, ind_y, id, total, g, id_zero);
     EB_LAUNCH_CHECK("gpu_mpool2D_back");

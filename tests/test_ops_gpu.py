@@ -131,7 +131,10 @@ def test_softmax_and_cce_golden(lib, kats):
 POOL_CASES = [((2, 2), (2, 2), (0, 0, 0, 0), (2, 3, 28, 28)), ((2, 2), (2, 2), (0, 0, 0, 0), (2, 3, 7, 7)),
               ((3, 3), (2, 2), (0, 0, 0, 0), (2, 4, 18, 18)), ((3, 3), (2, 2), (1, 1, 1, 1), (1, 2, 9, 11)),
               ((3, 3), (1, 1), (1, 1, 1, 1), (2, 2, 6, 5)), ((7, 7), (1, 1), (0, 0, 0, 0), (3, 16, 7, 7)),
-              ((2, 2), (2, 2), (0, 1, 0, 1), (1, 1, 5, 5))]
+              ((2, 2), (2, 2), (0, 1, 0, 1), (1, 1, 5, 5)),
+              # planes of >= 1024 elements: max-pool backward stages each plane's output side in shared memory
+              ((3, 3), (2, 2), (1, 1, 1, 1), (3, 5, 40, 36)), ((2, 2), (2, 2), (0, 0, 0, 0), (2, 300, 32, 32)),
+              ((3, 3), (1, 1), (1, 1, 1, 1), (1, 3, 33, 34))]
 
 
 @pytest.mark.parametrize("kernel,stride,pads,shape", POOL_CASES)

@@ -134,13 +134,17 @@ def run_reference_arm(args):
 
 
 def run_b200_arm(args):
+    # EDDL's host side of train_batch (Tensor::select gathering the batch, the host->device copy of it) runs under OpenMP:
+    # give every rank an equal share of the host cores and keep its workers spinning between the short parallel regions.
+    # Set before anything loads an OpenMP runtime; an explicit setting in the environment wins.
+    os.environ.setdefault("OMP_NUM_THREADS", str(max(1, (os.cpu_count() or 1) // max(1, int(os.environ.get("WORLD_SIZE", "1"))))))
+    os.environ.setdefault("OMP_WAIT_POLICY", "active")
     if args.gpus > 1:
         import torch  # noqa: F401  (first, so that the process-wide libnccl.so.2 is the one torch was built against)
     from eddl_b200 import capi, harness, dist as ebd
     rank, world, local = ebd.rendezvous("gloo")
     if world != args.gpus:
         raise SystemExit("--gpus %d but WORLD_SIZE=%d (launch N>1 with torchrun)" % (args.gpus, world))
-    os.environ.setdefault("OMP_NUM_THREADS", "4")
     L = capi.lib()
     if L.device_count() <= local:
         raise SystemExit("no CUDA device %d: the B200 backend has no CPU fallback" % local)
@@ -248,7 +252,7 @@ def run_b200_arm(args):
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "global_batch": batch * world, "optimizer": args.optimizer,
                        "l2": "per-step working set (about 11 GB of activations) far exceeds the 126 MB L2; no explicit flush",
-                       "conv_precision": "fp32-equivalent (mode 0)"},
+                       "conv_precision": "fp32-equivalent (mode 0)", "host_threads_per_rank": int(os.environ.get("OMP_NUM_THREADS", "0"))},
             "clocks": clocks,
             "e2e": {"value": imgs / e2e_s, "unit": "img/s", "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 16,
                     "ms_per_step": 1e3 * e2e_s / args.steps},

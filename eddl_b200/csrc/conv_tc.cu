@@ -34,6 +34,9 @@
 // the stage's mbarrier).  The activation operand is gathered by the producer warps with ordinary coalesced
 // loads rather than TMA tensor copies: the tap offset (s - pad) of an NCHW row is not a multiple of 16
 // bytes, which a tiled TMA copy requires, and the hi/lo split needs a pass through registers anyway.
+// Backward-weight gathers both operands: whatever is contiguous along k = (n, p, q) inside an image (dy always, x for 1x1
+// stride-1 layers) is read with 16-byte loads, a quarter warp per 128-byte row, so every load and store instruction touches
+// four whole rows; the tap-shifted x operand of larger filters keeps one lane per k.
 // Every wait on an mbarrier is bounded; on time-out the kernel records a status code, leaves
 // its loops, frees its tensor memory and returns.
 #include <cuda_bf16.h>

@@ -789,11 +789,24 @@ __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ s
     const int kb = blockIdx.x, nt = blockIdx.y;
     const size_t image_floats = (size_t)bn * BK * (SPLIT3 ? 2 : 1);
     char *img = (char *)(packed + ((size_t)kb * tiles_n + nt) * image_floats);
-    for (int e = threadIdx.x; e < bn * BK; e += blockDim.x) {
-        const int row = row_fastest ? e % bn : e / BK, k = row_fastest ? e / bn : e % BK;
-        const int n = nt * bn + row;
-        const int ko = kB[kb * BK + k];
-        tile[row][k] = (n < n_total && ko >= 0) ? __ldg(src + rowB[n] + ko) : 0.f;
+    // blockDim.x = 256 is a multiple of BK and of bn, so one of the two coordinates is fixed per thread: its table entry is
+    // looked up once, and the loop's loads are independent of each other (several in flight per thread)
+    if (row_fastest) {
+        const int row = threadIdx.x % bn, n = nt * bn + row;
+        const int ro = n < n_total ? __ldg(rowB + n) : -1;
+#pragma unroll 4
+        for (int k = threadIdx.x / bn; k < BK; k += 256 / bn) {
+            const int ko = __ldg(kB + kb * BK + k);
+            tile[row][k] = (ro >= 0 && ko >= 0) ? __ldg(src + ro + ko) : 0.f;
+        }
+    } else {
+        const int k = threadIdx.x % BK;
+        const int ko = __ldg(kB + kb * BK + k);
+#pragma unroll 4
+        for (int row = threadIdx.x / BK; row < bn; row += 256 / BK) {
+            const int n = nt * bn + row;
+            tile[row][k] = (n < n_total && ko >= 0) ? __ldg(src + __ldg(rowB + n) + ko) : 0.f;
+        }
     }
     __syncthreads();
     char *plane1 = img + (size_t)bn * BK * 4;

@@ -382,7 +382,8 @@ extern "C" int eddlb200_bn_fwd_noalloc(int dev, int b, int z, int rc, const floa
     if (!partial) return EDDLB200_ENOINIT;
     cudaStream_t st = (cudaStream_t)cuda_stream;
     if (DevCtx *cx = ctx_peek(dev)) {
-        // a device context exists and may owe zeros to one of these buffers (deferred fills): settle them on this stream
+        // a device context exists and may owe zeros or a recorded copy to one of these buffers: settle them on this stream
+        if (pend_copy_active(cx)) { if (int r = pend_copy_flush(cx, st)) return r; }
         const size_t tb = (size_t)b * z * rc * sizeof(float), zb = (size_t)z * sizeof(float);
         EB_READS(input, tb); EB_WRITES(output, tb); EB_WRITES(opa, tb); EB_WRITES(relu_out, tb);
         EB_READS(global_mean, zb); EB_READS(global_variance, zb); EB_READS(affine_g, zb); EB_READS(affine_b, zb);

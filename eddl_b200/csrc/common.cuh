@@ -59,6 +59,15 @@ void lz_forget(DevCtx *c, const void *p, size_t bytes);                  // the 
 int lz_set_all(int on);                                                  // every device; turning it off writes every deferred fill
 int launch_zero_fill(DevCtx *c, cudaStream_t st, float *p, size_t n);    // defined with the elementwise kernels
 
+// Deferred first term of an in-place sum.  LAdd::forward is "out = 0; out += a; out += b": with the fill deferred, the first
+// add is the copy out = 1*a + 1*0.  It is recorded instead of run; if the very next call is the second in-place add into the
+// same buffer, one kernel computes out = s2*b + t2*(s1*a + t1*0) (12 bytes per element instead of 8 + 12).  ANY other entry
+// point writes the recorded copy out first, so the record never outlives the call that follows it.
+struct PendCopy { bool active = false; float *dst = nullptr; const float *src = nullptr; float sa = 0.f, sb = 0.f; size_t n = 0; };
+bool pend_copy_active(DevCtx *c);
+PendCopy &pend_copy(DevCtx *c);
+int pend_copy_flush(DevCtx *c, cudaStream_t st);                         // defined with the elementwise kernels
+
 }  // namespace eb
 
 #define EB_READS(p, bytes)                                                              \
@@ -70,11 +79,15 @@ int launch_zero_fill(DevCtx *c, cudaStream_t st, float *p, size_t n);    // defi
         if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_write(cx, st, (p), (bytes))) return r__; } \
     } while (0)
 
-#define EB_CTX(dev)                                   \
+// Every entry point but eddlb200_axpby starts by writing out a deferred "first term" of an in-place sum (see pend_copy_*).
+#define EB_CTX_KEEP_PENDING(dev)                      \
     eb::DevCtx *cx = eb::ctx(dev);                    \
     if (!cx) return EDDLB200_ENOINIT;                 \
     cudaStream_t st = eb::stream_of(cx);              \
     (void)st
+#define EB_CTX(dev)                                   \
+    EB_CTX_KEEP_PENDING(dev);                         \
+    if (eb::pend_copy_active(cx)) { if (int r__ = eb::pend_copy_flush(cx, st)) return r__; }
 
 #define EB_LAUNCH_CHECK(what)                                         \
     do {                                                              \

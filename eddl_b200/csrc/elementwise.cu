@@ -133,6 +133,15 @@ struct ReluBwdZeroF {
     static constexpr bool reads_c = false;
     __device__ float operator()(float d, float i, float) const { return i > 0.f ? __fadd_rn(0.f, d) : 0.f; }
 };
+// c = s2*y + t2*(s1*x + t1*0): the two in-place adds "c = s1*x + t1*c; c = s2*y + t2*c" into a c known to hold zeros
+struct Sum2IntoZeroF {
+    static constexpr bool reads_c = false;
+    float s1, t1, s2, t2;
+    __device__ float operator()(float x, float y, float) const {
+        const float first = __fadd_rn(__fmul_rn(s1, x), __fmul_rn(t1, 0.f));
+        return __fadd_rn(__fmul_rn(s2, y), __fmul_rn(t2, first));
+    }
+};
 // c = 0 + (sa*a + sb*b): gpu_add with incC into a c known to hold zeros
 struct AxpbyZeroF {
     static constexpr bool reads_c = false;
@@ -183,6 +192,13 @@ __global__ void __launch_bounds__(kBlock) fill_multi_kernel(const FillSeg *__res
 }  // namespace
 
 namespace eb {
+// runs a recorded "dst = sa*src + sb*0" (see PendCopy)
+int pend_copy_flush(DevCtx *cx, cudaStream_t st) {
+    PendCopy &p = pend_copy(cx);
+    if (!p.active) return 0;
+    p.active = false;
+    return launch1(cx, st, p.src, p.dst, p.n, AxpbZeroF{p.sa, p.sb}, "gpu_add", 12.0);
+}
 // writes n zeros at p; used when a deferred zero fill has to be materialised
 int launch_zero_fill(DevCtx *cx, cudaStream_t st, float *p, size_t n) {
     if (n == 0) return 0;
@@ -243,7 +259,17 @@ int eddlb200_clamp(int dev, const float *a, float *b, float lo, float hi, size_t
 int eddlb200_relu_fwd(int dev, const float *a, float *b, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, ReluF{}, "gpu_relu"); }
 
 int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b, float *c, int inc_c, size_t n) {
-    EB_CTX(dev);
+    EB_CTX_KEEP_PENDING(dev);
+    if (pend_copy_active(cx)) {
+        PendCopy &p = pend_copy(cx);
+        if (!inc_c && c == b && c == p.dst && n == p.n && a != c && a && n) {
+            // second in-place add into the buffer whose first term is still on record: both in one pass
+            p.active = false;
+            EB_READS(a, n * sizeof(float));
+            return launch3(cx, st, p.src, a, c, n, Sum2IntoZeroF{p.sa, p.sb, sca, scb}, "gpu_add", 20.0);
+        }
+        if (int r = pend_copy_flush(cx, st)) return r;
+    }
     if (inc_c && c && c != a && c != b && lz_any(cx)) {
         int status = 0;
         if (lz_take(cx, st, c, n * sizeof(float), &status)) return launch3(cx, st, a, b, c, n, AxpbyZeroF{sca, scb}, "gpu_add", 16.0);
@@ -254,7 +280,12 @@ int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b
         // zeros it need not be read
         int status = 0;
         if (lz_take(cx, st, c, n * sizeof(float), &status)) {
-            if (c == b) return launch1(cx, st, a, c, n, AxpbZeroF{sca, scb}, "gpu_add", 12.0);
+            if (c == b) {
+                // record instead of run: the next call is usually the second term of the same sum
+                PendCopy &p = pend_copy(cx);
+                p.active = true; p.dst = c; p.src = a; p.sa = sca; p.sb = scb; p.n = n;
+                return 0;
+            }
             return launch1(cx, st, b, c, n, ZeroAxpbF{sca, scb}, "gpu_add", 12.0);
         }
         if (status) return status;

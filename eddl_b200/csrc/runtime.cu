@@ -38,6 +38,7 @@ struct DevCtx {
     // deferred zero fills: start address -> bytes (disjoint ranges)
     bool lz_on = false;
     std::map<uintptr_t, size_t> lz;
+    PendCopy pend;
 };
 
 static DevCtx g_ctx[EDDLB200_MAX_DEVICES];
@@ -129,6 +130,8 @@ constexpr size_t kLazyZeroMinBytes = size_t(256) << 10;      // smaller fills ar
 static struct LzStats { unsigned long long deferred = 0, taken = 0, dropped = 0, written = 0; double written_bytes = 0, deferred_bytes = 0;
     ~LzStats() { if (getenv("EDDL_B200_LZ_STATS")) fprintf(stderr, "[lazy_zero] deferred %llu (%.1f MB) taken %llu dropped %llu written %llu (%.1f MB)\n", deferred, deferred_bytes / 1e6, taken, dropped, written, written_bytes / 1e6); } } g_lzs;
 bool lz_any(DevCtx *c) { return !c->lz.empty(); }
+bool pend_copy_active(DevCtx *c) { return c->pend.active; }
+PendCopy &pend_copy(DevCtx *c) { return c->pend; }
 
 // Visit every deferred range that overlaps [p, p + bytes): `covered` tells whether the range lies inside it.
 // The visitor may not touch the map; visited ranges are erased afterwards.
@@ -387,7 +390,7 @@ int eddlb200_profile_reset(int dev) {
 }
 
 int eddlb200_launch_count(int dev, unsigned long long *n) {
-    EB_CTX(dev);
+    EB_CTX_KEEP_PENDING(dev);       // a pure counter read: it does not touch device memory
     if (!n) return set_error(EDDLB200_EINVAL, "launch_count: null");
     *n = cx->launches;
     return 0;

@@ -115,6 +115,27 @@ def test_accumulating_kernels_take_over_the_fill(lazy):
     lib.call("inc", 0, da, d, N)
     np.testing.assert_array_equal(d.numpy(), (orc.axpby(0.3, a, -1.7, b, zero, 1) + a).astype(F))
 
+    # LAdd::forward on the GPU: out = 0; out = 1*a + 1*out; out = 1*b + 1*out.  The first add is only recorded, the second
+    # runs both in one launch
+    d = fresh(); before = lib.launches()
+    lib.call("axpby", 0, 1.0, da, 1.0, d, d, 0, N)
+    assert lib.launches() == before
+    lib.call("axpby", 0, 0.5, db, 2.0, d, d, 0, N)
+    assert lib.launches() == before + 1
+    first = orc.axpby(1.0, a, 1.0, zero)
+    got = d.numpy(); want = orc.axpby(0.5, b, 2.0, first)
+    np.testing.assert_array_equal(got, want); np.testing.assert_array_equal(np.signbit(got), np.signbit(want))
+    # a recorded first term is written out by whatever else comes next: a read of the destination ...
+    d = fresh()
+    lib.call("axpby", 0, 1.0, da, 1.0, d, d, 0, N)
+    np.testing.assert_array_equal(d.numpy(), first)
+    # ... or an operation that is about to change the source
+    d = fresh(); src = dev(lib, a)
+    lib.call("axpby", 0, 1.0, src, 1.0, d, d, 0, N)
+    lib.call("scale", 0, src, src, 3.0, N)
+    np.testing.assert_array_equal(d.numpy(), first)
+    np.testing.assert_array_equal(src.numpy(), (a * F(3.0)).astype(F))
+
 
 @pytest.mark.parametrize("stride,c", [(1, 32), (2, 32), (1, 3)])
 def test_conv_bn_pool_backward_into_deferred_zero(lazy, stride, c):

@@ -188,7 +188,9 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *          "lazy_zero" 1 = eddlb200_fill / eddlb200_fill_multi of 256 KB or more with 0.0f only record the range; the
  *          zeros are written when an entry point of this library reads the range, dropped when one overwrites all of
  *          it, and an accumulating kernel (conv2d_bwd_data, bn_bwd, relu_bwd, inc, axpby with inc_c, pool backward)
- *          that owns the whole range stores its result instead of adding to it (same bits).  Off by default: device
+ *          that owns the whole range stores its result instead of adding to it (same bits); the in-place form
+ *          eddlb200_axpby(s, a, t, c, c, 0) into such a c is recorded and runs with the next call (fused with it when
+ *          that is the second in-place add into c).  Off by default: device
  *          code outside this library does not see a deferred fill.  0 writes everything still deferred and returns
  *          to immediate fills. */
 int eddlb200_set_option(const char *name, int value);

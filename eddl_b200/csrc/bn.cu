@@ -21,7 +21,7 @@ namespace {
 using namespace eb;
 
 constexpr int kBlock = 256;
-constexpr int kMaxSplit = 64;
+constexpr int kMaxSplit = 256;
 
 struct Slice { unsigned begin, end; };   // element range inside one channel's b*rc items
 
@@ -105,7 +105,8 @@ __global__ void __launch_bounds__(kBlock) bn_fwd_apply_kernel(const float *__res
                                                               float *mean_out, float *var_out,
                                                               unsigned b, unsigned z, unsigned rc, float eps, float momentum) {
     __shared__ float sh[2];
-    const unsigned j = blockIdx.x, s = blockIdx.y, nsplit = gridDim.y;
+    // slices in reverse launch order: the statistics pass finished with the highest slices, so those are what the L2 holds
+    const unsigned j = blockIdx.x, nsplit = gridDim.y, s = nsplit - 1 - blockIdx.y;
     float mean, sigma;
     if (TRAIN) {
         float sum, sumsq;
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(float *__restrict_
                                                               const float *__restrict__ variance, float *mean1, float *mean2,
                                                               unsigned b, unsigned z, unsigned rc) {
     __shared__ float sh[2];
-    const unsigned j = blockIdx.x, s = blockIdx.y, nsplit = gridDim.y;
+    const unsigned j = blockIdx.x, nsplit = gridDim.y, s = nsplit - 1 - blockIdx.y;     // reverse launch order, see forward
     float s1, s2;
     reduce_partials(partial, j, nsplit, sh, s1, s2);
     const float N = (float)(b * rc);
@@ -229,10 +230,13 @@ __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(float *__restrict_
     }
 }
 
+// Slices per channel.  A launch is cut into several waves of short-lived blocks (g_bn_waves times the 8 blocks of 256 threads
+// an SM holds): with barely more blocks than the GPU holds at once, the few left over for a second wave run almost alone
+// at a fraction of the bandwidth while the rest of the GPU idles.
+int g_bn_waves = 16, g_bn_min_items = 8192;
 inline unsigned pick_split(unsigned z, unsigned per_channel) {
-    // enough blocks for ~8 per SM, at least 2048 items per block, at most kMaxSplit
-    unsigned want = (EDDLB200_NUM_SMS * 8 + z - 1) / z;
-    unsigned cap = (per_channel + 2047) / 2048;
+    unsigned want = (EDDLB200_NUM_SMS * 8 * (unsigned)g_bn_waves + z - 1) / z;
+    unsigned cap = (per_channel + (unsigned)g_bn_min_items - 1) / (unsigned)g_bn_min_items;
     unsigned s = want < cap ? want : cap;
     if (s < 1) s = 1;
     if (s > kMaxSplit) s = kMaxSplit;
@@ -240,6 +244,15 @@ inline unsigned pick_split(unsigned z, unsigned per_channel) {
 }
 
 }  // namespace
+
+namespace eb {
+// tuning knobs behind eddlb200_set_option("bn_waves" / "bn_min_items")
+int bn_set_tuning(int waves, int min_items) {
+    if (waves > 0) g_bn_waves = waves > 64 ? 64 : waves;
+    if (min_items > 0) g_bn_min_items = min_items < 1024 ? 1024 : min_items;
+    return 0;
+}
+}  // namespace eb
 
 using namespace eb;
 
@@ -342,7 +355,7 @@ int eddlb200_bn_bwd(int dev, int b, int z, int rc, float *delta, const float *op
 //   on the array and give wrong statistics; order them.
 namespace {
 
-constexpr unsigned kNoAllocPairs = 4096u * kMaxSplit;     // 262144 float2 = 2 MiB
+constexpr unsigned kNoAllocPairs = 262144u;               // float2 pairs = 2 MiB
 static __device__ __align__(256) float2 g_noalloc_partials[kNoAllocPairs];
 
 float2 *g_noalloc_addr[EDDLB200_MAX_DEVICES] = {};

@@ -57,6 +57,7 @@ int lz_write(DevCtx *c, cudaStream_t st, const void *p, size_t bytes);
 bool lz_take(DevCtx *c, cudaStream_t st, const void *p, size_t bytes, int *status);
 void lz_forget(DevCtx *c, const void *p, size_t bytes);                  // the memory is being released
 int lz_set_all(int on);                                                  // every device; turning it off writes every deferred fill
+int bn_set_tuning(int waves, int min_items);                             // BatchNorm grid sizing knobs (0 = leave unchanged)
 int launch_zero_fill(DevCtx *c, cudaStream_t st, float *p, size_t n);    // defined with the elementwise kernels
 
 // Deferred first term of an in-place sum.  LAdd::forward is "out = 0; out += a; out += b": with the fill deferred, the first

@@ -21,42 +21,66 @@ constexpr int kBlock = 256;
 
 struct PoolGeom { int ih, iw, oh, ow, kr, kc, sr, sc, pt, pl; };
 
+// IDX = unsigned when the tensors have fewer than 2^32 elements (32-bit divisions), size_t otherwise.
+// KR, KC > 0: window size known at compile time (2x2, 3x3) -- the loops unroll and all of a window's loads are issued
+// before the first compare, so an output costs one memory latency instead of kr*kc of them.  0, 0: any window.
+template <int KR, int KC, typename IDX>
 __global__ void __launch_bounds__(kBlock) maxpool_fwd_kernel(const float *__restrict__ in, float *__restrict__ out,
                                                              float *__restrict__ ind_x, float *__restrict__ ind_y,
                                                              size_t total, PoolGeom g) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int kr = KR > 0 ? KR : g.kr, kc = KC > 0 ? KC : g.kc;
     for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += stride) {
-        const int oj = (int)(p % g.ow);
-        const size_t t = p / g.ow;
-        const int oi = (int)(t % g.oh);
-        const size_t plane = t / g.oh;
+        const IDX pi = (IDX)p;
+        const IDX t = pi / (IDX)g.ow;
+        const int oj = (int)(pi - t * (IDX)g.ow);
+        const IDX plane = t / (IDX)g.oh;
+        const int oi = (int)(t - plane * (IDX)g.oh);
         const float *src = in + plane * (size_t)g.ih * g.iw;
         const int i0 = oi * g.sr - g.pt, j0 = oj * g.sc - g.pl;
         float m = -3.40282e+38f;
         // A window in which nothing exceeds the lowest value (all NaN / -inf) reports
         // position (0, 0); the reference leaves the previous content there.
         float bx = 0.f, by = 0.f;
-        for (int ki = 0; ki < g.kr; ki++) {
-            const int y = i0 + ki;
-            for (int kj = 0; kj < g.kc; kj++) {
-                const int x = j0 + kj;
-                float v = -3.40282e+38f;
-                if (y >= 0 && y < g.ih && x >= 0 && x < g.iw) v = __ldg(src + (size_t)y * g.iw + x);
-                if (v > m) { m = v; bx = (float)x; by = (float)y; }
+        if (KR > 0) {
+            float v[KR > 0 ? KR * KC : 1];
+#pragma unroll
+            for (int ki = 0; ki < KR; ki++)
+#pragma unroll
+                for (int kj = 0; kj < KC; kj++) {
+                    const int y = i0 + ki, x = j0 + kj;
+                    v[ki * KC + kj] = (y >= 0 && y < g.ih && x >= 0 && x < g.iw) ? __ldg(src + (y * g.iw + x)) : -3.40282e+38f;
+                }
+#pragma unroll
+            for (int ki = 0; ki < KR; ki++)
+#pragma unroll
+                for (int kj = 0; kj < KC; kj++)
+                    if (v[ki * KC + kj] > m) { m = v[ki * KC + kj]; bx = (float)(j0 + kj); by = (float)(i0 + ki); }
+        } else {
+            for (int ki = 0; ki < kr; ki++) {
+                const int y = i0 + ki;
+                for (int kj = 0; kj < kc; kj++) {
+                    const int x = j0 + kj;
+                    float v = -3.40282e+38f;
+                    if (y >= 0 && y < g.ih && x >= 0 && x < g.iw) v = __ldg(src + (y * g.iw + x));
+                    if (v > m) { m = v; bx = (float)x; by = (float)y; }
+                }
             }
         }
         out[p] = m; ind_x[p] = bx; ind_y[p] = by;
     }
 }
 
+template <typename IDX>
 __global__ void __launch_bounds__(kBlock) avgpool_fwd_kernel(const float *__restrict__ in, float *__restrict__ out, size_t total, PoolGeom g) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const float ksize = (float)(g.kr * g.kc);
     for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total; p += stride) {
-        const int oj = (int)(p % g.ow);
-        const size_t t = p / g.ow;
-        const int oi = (int)(t % g.oh);
-        const size_t plane = t / g.oh;
+        const IDX pi = (IDX)p;
+        const IDX t = pi / (IDX)g.ow;
+        const int oj = (int)(pi - t * (IDX)g.ow);
+        const IDX plane = t / (IDX)g.oh;
+        const int oi = (int)(t - plane * (IDX)g.oh);
         const float *src = in + plane * (size_t)g.ih * g.iw;
         const int i0 = oi * g.sr - g.pt, j0 = oj * g.sc - g.pl;
         float s = 0.f;
@@ -65,11 +89,16 @@ __global__ void __launch_bounds__(kBlock) avgpool_fwd_kernel(const float *__rest
             if (y < 0 || y >= g.ih) continue;
             for (int kj = 0; kj < g.kc; kj++) {
                 const int x = j0 + kj;
-                if (x >= 0 && x < g.iw) s = __fadd_rn(s, __ldg(src + (size_t)y * g.iw + x));
+                if (x >= 0 && x < g.iw) s = __fadd_rn(s, __ldg(src + (y * g.iw + x)));
             }
         }
         out[p] = __fdiv_rn(s, ksize);
     }
+}
+
+// Argmax coordinates as one key: the element's index inside its plane, -1 for coordinates outside the plane.
+__device__ __forceinline__ int pool_key(int x, int y, int iw, int ih) {
+    return ((unsigned)x < (unsigned)iw && (unsigned)y < (unsigned)ih) ? y * iw + x : -1;
 }
 
 // First / last output index whose window [o*s - pad, o*s - pad + k) contains position v.
@@ -143,47 +172,91 @@ __global__ void __launch_bounds__(kBlock) pool_bwd_kernel(const float *__restric
     }
 }
 
-// Max-pool backward, one block per (n, c) plane: the plane's output-side tensors (delta and the two argmax coordinates,
-// 12 bytes per output element) are staged in shared memory once, then every input element tests its covering windows
-// there.  Same window order and arithmetic as pool_bwd_kernel; used when the plane fits (12 * oh * ow bytes).
+// Max-pool backward, one block per (n, c) plane.  The plane's output-side tensors are staged in shared memory once, as 8
+// bytes per output element: the delta and the argmax position folded into ONE integer key (row * iw + column, or -1 when
+// the stored coordinates lie outside the plane and can match no element).  The covering-window ranges of every input row
+// and column are tabulated once per block (they need integer divisions by the stride), so an input element costs two table
+// reads plus, per covering window, one key compare and a predicated add.  Same window order and arithmetic as
+// pool_bwd_kernel; used when the plane fits.
 __global__ void __launch_bounds__(256) maxpool_bwd_plane_kernel(const float *__restrict__ d, const float *__restrict__ ind_x,
                                                                 const float *__restrict__ ind_y, float *__restrict__ id,
                                                                 unsigned planes, PoolGeom g, int id_zero) {
     extern __shared__ float sm_pool[];
     const int opl = g.oh * g.ow, ipl = g.ih * g.iw;
-    float *sd = sm_pool, *sx = sm_pool + opl, *sy = sm_pool + 2 * opl;
+    float *sd = sm_pool;
+    int *skey = reinterpret_cast<int *>(sm_pool + opl);
+    int *rowtab = skey + opl, *coltab = rowtab + g.ih;        // (first | last << 16) covering output row / column
+    for (int v = threadIdx.x; v < g.ih + g.iw; v += blockDim.x) {
+        int lo, hi;
+        if (v < g.ih) covering(v, g.kr, g.sr, g.pt, g.oh, lo, hi);
+        else covering(v - g.ih, g.kc, g.sc, g.pl, g.ow, lo, hi);
+        rowtab[v] = lo | (hi << 16);         // lo > hi: no window covers it; both grow with v
+    }
+    const bool vec = (opl & 3) == 0 && aligned16(d) && aligned16(ind_x) && aligned16(ind_y);
     for (unsigned plane = blockIdx.x; plane < planes; plane += gridDim.x) {
         const size_t obase = (size_t)plane * opl;
         __syncthreads();                       // the previous plane's readers are done
-        if ((opl & 3) == 0 && aligned16(d) && aligned16(ind_x) && aligned16(ind_y)) {
+        if (vec) {
             // 16-byte loads, several per thread in flight: the staging is one memory latency, not one per element
 #pragma unroll 4
             for (int p = threadIdx.x * 4; p < opl; p += blockDim.x * 4) {
-                const float4 a = ldg4(d + obase + p), b = ldg4(ind_x + obase + p), c = ldg4(ind_y + obase + p);
-                *reinterpret_cast<float4 *>(sd + p) = a; *reinterpret_cast<float4 *>(sx + p) = b; *reinterpret_cast<float4 *>(sy + p) = c;
+                const float4 a = ld_stream4(d + obase + p), b = ld_stream4(ind_x + obase + p), c = ld_stream4(ind_y + obase + p);
+                *reinterpret_cast<float4 *>(sd + p) = a;
+                int4 k;
+                // int x = D->indX->ptr[p]  (float -> int conversion in the reference)
+                k.x = pool_key((int)b.x, (int)c.x, g.iw, g.ih); k.y = pool_key((int)b.y, (int)c.y, g.iw, g.ih);
+                k.z = pool_key((int)b.z, (int)c.z, g.iw, g.ih); k.w = pool_key((int)b.w, (int)c.w, g.iw, g.ih);
+                *reinterpret_cast<int4 *>(skey + p) = k;
             }
         } else {
-            for (int p = threadIdx.x; p < opl; p += blockDim.x) { sd[p] = __ldg(d + obase + p); sx[p] = __ldg(ind_x + obase + p); sy[p] = __ldg(ind_y + obase + p); }
+            for (int p = threadIdx.x; p < opl; p += blockDim.x) {
+                sd[p] = __ldg(d + obase + p);
+                skey[p] = pool_key((int)__ldg(ind_x + obase + p), (int)__ldg(ind_y + obase + p), g.iw, g.ih);
+            }
         }
         __syncthreads();
         float *idp = id + (size_t)plane * ipl;
-        int y = threadIdx.x / g.iw, x = threadIdx.x - y * g.iw;
-        const int dy = blockDim.x / g.iw, dx = blockDim.x - dy * g.iw;      // advance of (y, x) per blockDim.x elements
-        for (int q = threadIdx.x; q < ipl; q += blockDim.x) {
-            int oi0, oi1, oj0, oj1;
-            covering(y, g.kr, g.sr, g.pt, g.oh, oi0, oi1);
-            covering(x, g.kc, g.sc, g.pl, g.ow, oj0, oj1);
-            float acc = id_zero ? 0.f : idp[q];
-            bool touched = id_zero != 0;
-            for (int oi = oi0; oi <= oi1; oi++)
-                for (int oj = oj0; oj <= oj1; oj++) {
-                    const int p = oi * g.ow + oj;
-                    // int x = D->indX->ptr[p]  (float -> int conversion in the reference)
-                    if ((int)sx[p] == x && (int)sy[p] == y) { acc = __fadd_rn(acc, sd[p]); touched = true; }
-                }
-            if (touched) idp[q] = acc;
-            x += dx; y += dy;
-            if (x >= g.iw) { x -= g.iw; y++; }
+        if ((g.iw & 3) == 0 && aligned16(id)) {
+            // Four consecutive elements of one row per thread (16-byte accesses to the input delta).  They share the row's
+            // window range, and the windows of columns first(x0) .. last(x0 + 3) are each read once: a window's key names
+            // at most one of the four elements, which takes its delta.  Per element the order stays rows-outer, columns-inner.
+            const int iw4 = g.iw >> 2;
+            int y = threadIdx.x / iw4, xq = threadIdx.x - y * iw4;
+            const int dy = blockDim.x / iw4, dxq = blockDim.x - dy * iw4;
+#pragma unroll 2
+            for (int q4 = threadIdx.x; q4 < (ipl >> 2); q4 += blockDim.x) {
+                const int rt = rowtab[y], x0 = xq << 2, base = q4 << 2;
+                const int oi0 = rt & 0xffff, oi1 = rt >> 16, oj0 = coltab[x0] & 0xffff, oj1 = coltab[x0 + 3] >> 16;
+                float4 acc = id_zero ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4 *>(idp + base);
+                for (int oi = oi0; oi <= oi1; oi++)
+                    for (int oj = oj0; oj <= oj1; oj++) {
+                        const int p = oi * g.ow + oj, e = skey[p] - base;
+                        const float v = sd[p];
+                        acc.x = e == 0 ? __fadd_rn(acc.x, v) : acc.x;
+                        acc.y = e == 1 ? __fadd_rn(acc.y, v) : acc.y;
+                        acc.z = e == 2 ? __fadd_rn(acc.z, v) : acc.z;
+                        acc.w = e == 3 ? __fadd_rn(acc.w, v) : acc.w;
+                    }
+                *reinterpret_cast<float4 *>(idp + base) = acc;        // untouched elements get their own value back
+                xq += dxq; y += dy;
+                if (xq >= iw4) { xq -= iw4; y++; }
+            }
+        } else {
+            int y = threadIdx.x / g.iw, x = threadIdx.x - y * g.iw;
+            const int dy = blockDim.x / g.iw, dx = blockDim.x - dy * g.iw;      // advance of (y, x) per blockDim.x elements
+            for (int q = threadIdx.x; q < ipl; q += blockDim.x) {
+                const int rt = rowtab[y], ct = coltab[x];
+                const int oi0 = rt & 0xffff, oi1 = rt >> 16, oj0 = ct & 0xffff, oj1 = ct >> 16;
+                float acc = id_zero ? 0.f : idp[q];
+                for (int oi = oi0; oi <= oi1; oi++)
+                    for (int oj = oj0; oj <= oj1; oj++) {
+                        const int p = oi * g.ow + oj;
+                        if (skey[p] == q) acc = __fadd_rn(acc, sd[p]);
+                    }
+                idp[q] = acc;
+                x += dx; y += dy;
+                if (x >= g.iw) { x -= g.iw; y++; }
+            }
         }
     }
 }
@@ -211,7 +284,11 @@ int eddlb200_maxpool2d_fwd(int dev, const float *in, float *out, float *ind_x, f
     EB_READS(in, (size_t)n * c * ih * iw * sizeof(float));
     EB_WRITES(out, total * sizeof(float)); EB_WRITES(ind_x, total * sizeof(float)); EB_WRITES(ind_y, total * sizeof(float));
     ProfScope prof(cx, PROF_POOL, 4.0 * n * c * ih * iw + 12.0 * total);
-    maxpool_fwd_kernel<<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, ind_x, ind_y, total, g);
+    const int blocks = grid_for(total, kBlock);
+    if ((size_t)n * c * ih * iw >= (size_t(1) << 32)) maxpool_fwd_kernel<0, 0, size_t><<<blocks, kBlock, 0, st>>>(in, out, ind_x, ind_y, total, g);
+    else if (kr == 2 && kc == 2) maxpool_fwd_kernel<2, 2, unsigned><<<blocks, kBlock, 0, st>>>(in, out, ind_x, ind_y, total, g);
+    else if (kr == 3 && kc == 3) maxpool_fwd_kernel<3, 3, unsigned><<<blocks, kBlock, 0, st>>>(in, out, ind_x, ind_y, total, g);
+    else maxpool_fwd_kernel<0, 0, unsigned><<<blocks, kBlock, 0, st>>>(in, out, ind_x, ind_y, total, g);
     EB_LAUNCH_CHECK("gpu_mpool2D");
     return 0;
 }
@@ -229,8 +306,8 @@ int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const fl
     int id_zero = 0;
     if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + 8.0 * total);     // canonical count, also for the id_zero variant
-    const size_t plane_smem = (size_t)12 * oh * ow;
-    if (plane_smem <= (size_t)160 * 1024 && ih * iw >= 1024 && (size_t)n * c < 0x7fffffffu) {
+    const size_t plane_smem = (size_t)8 * oh * ow + (size_t)4 * (ih + iw);
+    if (plane_smem <= (size_t)160 * 1024 && ih * iw >= 1024 && oh < 32768 && ow < 32768 && (size_t)n * c < 0x7fffffffu) {
         static bool configured[EDDLB200_MAX_DEVICES] = {};
         if (!configured[dev]) {
             cudaError_t e = cudaFuncSetAttribute(maxpool_bwd_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -263,7 +340,8 @@ int eddlb200_avgpool2d_fwd(int dev, const float *in, float *out, int n, int c, i
     EB_READS(in, (size_t)n * c * ih * iw * sizeof(float));
     EB_WRITES(out, total * sizeof(float));
     ProfScope prof(cx, PROF_POOL, 4.0 * n * c * ih * iw + 4.0 * total);
-    avgpool_fwd_kernel<<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, total, g);
+    if ((size_t)n * c * ih * iw < (size_t(1) << 32)) avgpool_fwd_kernel<unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, total, g);
+    else avgpool_fwd_kernel<size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(in, out, total, g);
     EB_LAUNCH_CHECK("gpu_avgpool2D");
     return 0;
 }

@@ -99,7 +99,14 @@ def run_hbm(args):
     if os.path.exists(p):
         peak = json.load(open(p))["hbm_gbs"]
 
+    for o in args.opt:
+        k, v = o.split("=")
+        L.call("set_option", k.encode(), int(v))
+    only = args.only.split(",") if args.only else None
+
     def report(name, shape, nbytes, fn):
+        if only and not any(name.startswith(o) for o in only):
+            return
         fn(); fn(); fn(); L.sync(dev)
         med, best = _timed(L, dev, fn, args.iters, flush)
         gbs = nbytes / (med * 1e-3) / 1e9
@@ -222,7 +229,8 @@ def main():
     ap.add_argument("--net", default="resnet50", help="step: cnn | vgg16bn | resnet50")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--steps", type=int, default=1)
-    ap.add_argument("--only", default=None)
+    ap.add_argument("--only", default=None, help="hbm: comma-separated kernel-name prefixes (bn, relu, maxpool, ...)")
+    ap.add_argument("--opt", action="append", default=[], help="name=value for eddlb200_set_option (repeatable)")
     ap.add_argument("--shape", type=int, default=-1, help="index into the conv shape list (default: all)")
     args = ap.parse_args()
     {"conv": run_conv, "hbm": run_hbm, "allreduce": run_allreduce, "step": run_step}[args.what](args)

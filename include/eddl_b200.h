@@ -192,7 +192,11 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *          eddlb200_axpby(s, a, t, c, c, 0) into such a c is recorded and runs with the next call (fused with it when
  *          that is the second in-place add into c).  Off by default: device
  *          code outside this library does not see a deferred fill.  0 writes everything still deferred and returns
- *          to immediate fills. */
+ *          to immediate fills.
+ *          "bn_waves" (1..64, default 16) and "bn_min_items" (>= 1024, default 8192): grid sizing of the BatchNorm
+ *          kernels -- every channel is cut into slices so that a launch has about bn_waves x (8 blocks per SM) blocks
+ *          of at least bn_min_items elements each.  Results depend on the slicing only through the fp32 order of the
+ *          partial sums (about 1e-7 relative on the statistics). */
 int eddlb200_set_option(const char *name, int value);
 int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias /* may be null */, float *y,
                         int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,

@@ -24,6 +24,9 @@ int conv_tc_fwd(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, 
 int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision, bool dx_zero);
 int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *dy, float *gw, int precision, bool gw_zero);
 
+// 1 (default): the tensor-core kernel's prefetch warp pulls the activation operand of 1x1 layers into L2 ahead of the gather.
+int conv_tc_set_prefetch(int on);
+
 // Reads and clears the device's time-out flag of the tensor-core kernels (blocking).
 int conv_tc_status(int dev, cudaStream_t st, int *out);
 

@@ -54,7 +54,8 @@ constexpr int BM = 128;             // UMMA M (TMEM lanes)
 constexpr int BK = 32;              // fp32 per 128-byte swizzle row
 constexpr int NPROD = 256;          // producer threads (warps 0-7); warp 8 issues the MMAs; warps 9-12 run the epilogue
 constexpr int NEPI = 128;           // epilogue threads (warps 9-12)
-constexpr int NTHREADS = NPROD + 32 + NEPI;
+constexpr int NTHREADS = NPROD + 32 + NEPI + 32;     // + warp 13: L2 prefetch of the activation operand
+constexpr int PF_AHEAD = 8;         // K-blocks the prefetch warp may run ahead of the producers
 constexpr int INVALID_Y = -20000;
 constexpr int NMAIN = 3;             // rotating hi*hi accumulators; a fourth holds the cross terms
 
@@ -79,6 +80,7 @@ struct TcParams {
     int check;              // padding test of the gathered operand: 0 none needed, 1 per-row tap bitmask, 2 coordinates
     const float *packedB;   // forward / backward-data: pre-split, pre-swizzled B tiles [kblock][n tile][hi|lo][BN x 32]
     int nmain;              // rotating hi*hi accumulators in use: 1 for short chains, NMAIN otherwise
+    int pf_rows;            // > 0: warp 13 prefetches the A operand into L2, one line per pf_rows tile rows and k (0 = off)
     int *status;
 };
 
@@ -217,6 +219,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
     uint64_t *bars = (uint64_t *)(sRowB + 2 * BN_);                      // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    volatile int *progress = abort_flag + 1;              // last K-block (CTA sequence number) producer group 0 has stored
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kb_total = P.K_pad / BK;
@@ -235,6 +238,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
         for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD / 64 + (B_TMA ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); }
         for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, NEPI / 32); }
         *abort_flag = 0;
+        *progress = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 8) tmem_alloc(smem_u32(tmem_slot), 512);
@@ -432,6 +436,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
                 __syncwarp();                       // orders the other lanes' stores and fences before lane 0's arrive
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);      // one arrive per warp: 32 lanes on one barrier word serialise
+                if (tid == 0) *progress = g;        // paces the prefetch warp
                 it += 2; settle();
                 if (t < total_tiles) load_row(t, kb0, it);
             }
@@ -587,6 +592,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             }
         }
         __syncwarp();
+    } else if (warp >= 13) {
+        // ============================ L2 prefetch of the A operand (warp 13) ============================
+        // Layers with a short reduction and no padding (1x1) are bound by the latency of the producers' gather: a group
+        // has one K-block (16 KB) in flight per round trip to HBM.  This warp walks the CTA's K-block sequence up to
+        // PF_AHEAD blocks ahead of producer group 0 and touches one address per (pf_rows consecutive tile rows, k): the
+        // rows are consecutive pixels, so that is every line the producers will read, and their loads then hit in L2.
+        // Nothing waits on this warp; its own wait on the producers' progress is bounded and it simply stops on a time-out.
+        if constexpr (A_ROWMAJOR && B_TMA) {
+            if (P.pf_rows > 0) {
+                const int nr = (BM + P.pf_rows - 1) / P.pf_rows;          // <= 32
+                int g = 0;
+                bool stop = false;
+                for (int t = blockIdx.x; t < total_tiles && !stop; t += gridDim.x) {
+                    int kb0, nkb; kb_range(t, kb0, nkb);
+                    const int mn = t % tiles_mn;
+                    const int m0 = (mn % P.tiles_m) * BM;
+                    // lane j < nr: first row of group j; lane nr: the tile's last row (the line the last group spills into)
+                    int mrow = lane < nr ? m0 + lane * P.pf_rows : m0 + BM - 1;
+                    if (mrow >= P.M_total) mrow = P.M_total - 1;
+                    const int roff = (lane <= nr && mrow >= m0) ? __ldg(P.rowA + mrow).x : -1;
+                    for (int it = 0; it < nkb; it++, g++) {
+                        int spins = 0;
+                        while (g > *progress + PF_AHEAD) {
+                            if (*abort_flag || ++spins > (1 << 18)) { stop = true; break; }
+                            __nanosleep(128);
+                        }
+                        if (stop) break;
+                        const float *pk = P.srcA + __ldg(P.kC + (kb0 + it) * BK + lane);
+                        for (int j = 0; j <= nr && j < 32; j++) {
+                            const int ro = __shfl_sync(0xffffffffu, roff, j);
+                            if (ro >= 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(pk + ro));
+                        }
+                    }
+                }
+            }
+        }
     } else {
         // ============================ epilogue (warps 9-12) ============================
         const int quarter = warp & 3;                     // the TMEM lane quarter this warp may access
@@ -862,6 +903,7 @@ int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn,
 }
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
+int g_conv_prefetch = 1;       // eddlb200_set_option("conv_prefetch", 0 / 1)
 
 // The index tables are a pure function of the problem geometry, so they are built once per distinct geometry and kept
 // in device memory (a few MB per ResNet-50 layer shape); past the budget, tables go to the scratch arena and are
@@ -921,6 +963,12 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     // the compact k table keeps 27 bits of offset beside the 5-bit tap number
     if (T.check == 1 && (long long)(g.c > g.k ? g.c : g.k) * (g.ih * g.iw > g.oh * g.ow ? g.ih * g.iw : g.oh * g.ow) + (long long)(g.kr + 1) * (g.iw + g.ow) >= (1ll << 26)) T.check = 2;
     P.check = T.check;
+    // 1x1 unpadded layers: the prefetch warp covers pf_rows consecutive rows per touched line (a row step of sc pixels)
+    P.pf_rows = 0;
+    if (g_conv_prefetch && T.check == 0 && g.kr == 1 && g.kc == 1) {
+        if (mode == 1) P.pf_rows = 32;
+        else if (mode == 0) P.pf_rows = g.sc == 1 ? 32 : (g.sc == 2 ? 16 : 0);
+    }
     const int bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);
     const int tiles_m = (T.M_total + BM - 1) / BM, tiles_n = (T.N_total + bn - 1) / bn;
     const int kblocks = T.K_pad / BK;
@@ -1138,6 +1186,8 @@ int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const flo
     int dev = 0; cudaGetDevice(&dev);
     return run(cx, st, dev, 2, g, x, dy, gw, nullptr, precision, gw_zero);
 }
+
+int conv_tc_set_prefetch(int on) { g_conv_prefetch = on ? 1 : 0; return 0; }
 
 // 0 = no kernel of this file has timed out on the device since the last call
 int conv_tc_status(int dev, cudaStream_t st, int *out) {

@@ -62,6 +62,9 @@ def run_conv(args):
     L.call("init", dev)
     flush = L.empty((64 << 20,), dev)
     rng = np.random.default_rng(0)
+    for o in args.opt:
+        k_, v_ = o.split("=")
+        L.call("set_option", k_.encode(), int(v_))
     table = RESNET_SHAPES if args.set == "resnet" else CONV_SHAPES
     shapes = table if args.shape < 0 else [table[args.shape]]
     for (n, c, h, w, k, kr, kc, st, pad) in shapes:

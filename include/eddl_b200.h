@@ -193,6 +193,8 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *          that is the second in-place add into c).  Off by default: device
  *          code outside this library does not see a deferred fill.  0 writes everything still deferred and returns
  *          to immediate fills.
+ *          "conv_prefetch" 1 (default) = in 1x1 unpadded layers a spare warp of the tensor-core kernel prefetches the
+ *          activation operand into L2 ahead of the gather (results unchanged); 0 = off.
  *          "bn_waves" (1..64, default 16) and "bn_min_items" (>= 1024, default 8192): grid sizing of the BatchNorm
  *          kernels -- every channel is cut into slices so that a launch has about bn_waves x (8 blocks per SM) blocks
  *          of at least bn_min_items elements each.  Results depend on the slicing only through the fp32 order of the

@@ -134,7 +134,10 @@ POOL_CASES = [((2, 2), (2, 2), (0, 0, 0, 0), (2, 3, 28, 28)), ((2, 2), (2, 2), (
               ((2, 2), (2, 2), (0, 1, 0, 1), (1, 1, 5, 5)),
               # planes of >= 1024 elements: max-pool backward stages each plane's output side in shared memory
               ((3, 3), (2, 2), (1, 1, 1, 1), (3, 5, 40, 36)), ((2, 2), (2, 2), (0, 0, 0, 0), (2, 300, 32, 32)),
-              ((3, 3), (1, 1), (1, 1, 1, 1), (1, 3, 33, 34))]
+              ((3, 3), (1, 1), (1, 1, 1, 1), (1, 3, 33, 34)),
+              # four-elements-per-thread path (width a multiple of 4): nine covering windows per element; windows with gaps
+              ((3, 3), (1, 1), (1, 1, 1, 1), (2, 2, 36, 40)), ((2, 2), (3, 3), (0, 0, 0, 0), (1, 2, 36, 36)),
+              ((5, 5), (2, 2), (2, 2, 2, 2), (1, 2, 32, 48))]
 
 
 @pytest.mark.parametrize("kernel,stride,pads,shape", POOL_CASES)

@@ -64,7 +64,16 @@ int launch_zero_fill(DevCtx *c, cudaStream_t st, float *p, size_t n);    // defi
 // add is the copy out = 1*a + 1*0.  It is recorded instead of run; if the very next call is the second in-place add into the
 // same buffer, one kernel computes out = s2*b + t2*(s1*a + t1*0) (12 bytes per element instead of 8 + 12).  ANY other entry
 // point writes the recorded copy out first, so the record never outlives the call that follows it.
-struct PendCopy { bool active = false; float *dst = nullptr; const float *src = nullptr; float sa = 0.f, sb = 0.f; size_t n = 0; };
+// When that second add arrives, the SUM is kept on record in turn (kind 2): if the next call is the ReLU of the sum -- the
+// activation that follows LAdd in a residual block -- one kernel writes both the sum and its ReLU (16 bytes per element instead
+// of 12 + 8); again any other entry point first runs what is on record.  LAdd::backward adds its delta into the (zero) deltas of
+// both parents: the second such copy FROM THE SAME SOURCE joins the record (kind 3) and one kernel reads the source once.
+struct PendCopy {
+    bool active = false; int kind = 1;                   // 1: dst = sa*src + sb*0     2: dst = s2*src2 + t2*(sa*src + sb*0)
+                                                         // 3: dst = dst2 = sa*src + sb*0   (LAdd::backward: the delta into both parents)
+    float *dst = nullptr, *dst2 = nullptr; const float *src = nullptr, *src2 = nullptr;
+    float sa = 0.f, sb = 0.f, s2 = 0.f, t2 = 0.f; size_t n = 0;
+};
 bool pend_copy_active(DevCtx *c);
 PendCopy &pend_copy(DevCtx *c);
 int pend_copy_flush(DevCtx *c, cudaStream_t st);                         // defined with the elementwise kernels
@@ -80,7 +89,7 @@ int pend_copy_flush(DevCtx *c, cudaStream_t st);                         // defi
         if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_write(cx, st, (p), (bytes))) return r__; } \
     } while (0)
 
-// Every entry point but eddlb200_axpby starts by writing out a deferred "first term" of an in-place sum (see pend_copy_*).
+// Every entry point but eddlb200_axpby and eddlb200_relu_fwd starts by writing out a deferred "first term" of an in-place sum (see pend_copy_*).
 #define EB_CTX_KEEP_PENDING(dev)                      \
     eb::DevCtx *cx = eb::ctx(dev);                    \
     if (!cx) return EDDLB200_ENOINIT;                 \

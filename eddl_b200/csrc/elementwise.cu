@@ -55,6 +55,37 @@ __global__ void __launch_bounds__(kBlock) map3_scalar_kernel(const float *a, con
     for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride) c[j] = f(a[j], b[j], F::reads_c ? c[j] : 0.f);
 }
 
+// c = f(a, b); r = max(c, 0): a recorded sum together with the ReLU that follows it.  n4 = 0 runs everything in the scalar loop.
+template <typename F>
+__global__ void __launch_bounds__(kBlock) map3_relu_kernel(const float *a, const float *b, float *c, float *r, size_t n4, size_t n, F f) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t j = i; j < n4; j += stride) {
+        const float4 x = *reinterpret_cast<const float4 *>(a + 4 * j);
+        const float4 y = *reinterpret_cast<const float4 *>(b + 4 * j);
+        float4 z;
+        z.x = f(x.x, y.x, 0.f); z.y = f(x.y, y.y, 0.f); z.z = f(x.z, y.z, 0.f); z.w = f(x.w, y.w, 0.f);
+        *reinterpret_cast<float4 *>(c + 4 * j) = z;
+        z.x = z.x > 0.f ? z.x : 0.f; z.y = z.y > 0.f ? z.y : 0.f; z.z = z.z > 0.f ? z.z : 0.f; z.w = z.w > 0.f ? z.w : 0.f;
+        *reinterpret_cast<float4 *>(r + 4 * j) = z;
+    }
+    for (size_t j = 4 * n4 + i; j < n; j += stride) { const float z = f(a[j], b[j], 0.f); c[j] = z; r[j] = z > 0.f ? z : 0.f; }
+}
+
+// b = c = f(a): one source copied into two destinations.  n4 = 0 runs everything in the scalar loop.
+template <typename F>
+__global__ void __launch_bounds__(kBlock) map1_twice_kernel(const float *a, float *b, float *c, size_t n4, size_t n, F f) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t j = i; j < n4; j += stride) {
+        float4 v = *reinterpret_cast<const float4 *>(a + 4 * j);
+        v.x = f(v.x); v.y = f(v.y); v.z = f(v.z); v.w = f(v.w);
+        *reinterpret_cast<float4 *>(b + 4 * j) = v;
+        *reinterpret_cast<float4 *>(c + 4 * j) = v;
+    }
+    for (size_t j = 4 * n4 + i; j < n; j += stride) { const float v = f(a[j]); b[j] = v; c[j] = v; }
+}
+
 template <typename F>
 int launch1(DevCtx *cx, cudaStream_t st, const float *a, float *b, size_t n, F f, const char *what, double bytes_per_element = 8.0) {
     if (n == 0) return 0;
@@ -197,6 +228,16 @@ int pend_copy_flush(DevCtx *cx, cudaStream_t st) {
     PendCopy &p = pend_copy(cx);
     if (!p.active) return 0;
     p.active = false;
+    if (p.kind == 2) return launch3(cx, st, p.src, p.src2, p.dst, p.n, Sum2IntoZeroF{p.sa, p.sb, p.s2, p.t2}, "gpu_add", 20.0);
+    if (p.kind == 3) {
+        const size_t n = p.n;
+        EB_READS(p.src, n * sizeof(float)); EB_WRITES(p.dst, n * sizeof(float)); EB_WRITES(p.dst2, n * sizeof(float));
+        ProfScope prof(cx, PROF_ELEMENTWISE, 24.0 * n);             // canonical: two in-place adds of 12 bytes per element
+        const size_t n4 = (aligned16(p.src) && aligned16(p.dst) && aligned16(p.dst2)) ? n / 4 : 0;
+        map1_twice_kernel<<<grid_for(n4 ? n4 : n, kBlock), kBlock, 0, st>>>(p.src, p.dst, p.dst2, n4, n, AxpbZeroF{p.sa, p.sb});
+        EB_LAUNCH_CHECK("gpu_add (two destinations)");
+        return 0;
+    }
     return launch1(cx, st, p.src, p.dst, p.n, AxpbZeroF{p.sa, p.sb}, "gpu_add", 12.0);
 }
 // writes n zeros at p; used when a deferred zero fill has to be materialised
@@ -256,17 +297,41 @@ int eddlb200_addc(int dev, const float *a, float *b, float v, size_t n) { EB_CTX
 int eddlb200_sqr(int dev, const float *a, float *b, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, SqrF{}, "gpu_sqr"); }
 int eddlb200_sqrt(int dev, const float *a, float *b, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, SqrtF{}, "gpu_sqrt"); }
 int eddlb200_clamp(int dev, const float *a, float *b, float lo, float hi, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, ClampF{lo, hi}, "gpu_clamp"); }
-int eddlb200_relu_fwd(int dev, const float *a, float *b, size_t n) { EB_CTX(dev); return launch1(cx, st, a, b, n, ReluF{}, "gpu_relu"); }
+int eddlb200_relu_fwd(int dev, const float *a, float *b, size_t n) {
+    EB_CTX_KEEP_PENDING(dev);
+    if (pend_copy_active(cx)) {
+        PendCopy &p = pend_copy(cx);
+        if (p.kind == 2 && a == p.dst && n == p.n && b && b != a && b != p.src && b != p.src2) {
+            // the ReLU of a sum that is still on record: one pass writes the sum and its ReLU
+            p.active = false;
+            EB_READS(p.src, n * sizeof(float)); EB_READS(p.src2, n * sizeof(float));
+            EB_WRITES(p.dst, n * sizeof(float)); EB_WRITES(b, n * sizeof(float));
+            ProfScope prof(cx, PROF_ELEMENTWISE, 28.0 * n);          // canonical: 8 + 12 for the two adds, 8 for the ReLU
+            const size_t n4 = (aligned16(p.src) && aligned16(p.src2) && aligned16(p.dst) && aligned16(b)) ? n / 4 : 0;
+            map3_relu_kernel<<<grid_for(n4 ? n4 : n, kBlock), kBlock, 0, st>>>(p.src, p.src2, p.dst, b, n4, n, Sum2IntoZeroF{p.sa, p.sb, p.s2, p.t2});
+            EB_LAUNCH_CHECK("gpu_add + gpu_relu");
+            return 0;
+        }
+        if (int r = pend_copy_flush(cx, st)) return r;
+    }
+    return launch1(cx, st, a, b, n, ReluF{}, "gpu_relu");
+}
 
 int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b, float *c, int inc_c, size_t n) {
     EB_CTX_KEEP_PENDING(dev);
     if (pend_copy_active(cx)) {
         PendCopy &p = pend_copy(cx);
-        if (!inc_c && c == b && c == p.dst && n == p.n && a != c && a && n) {
-            // second in-place add into the buffer whose first term is still on record: both in one pass
-            p.active = false;
-            EB_READS(a, n * sizeof(float));
-            return launch3(cx, st, p.src, a, c, n, Sum2IntoZeroF{p.sa, p.sb, sca, scb}, "gpu_add", 20.0);
+        if (p.kind == 1 && !inc_c && c == b && c == p.dst && n == p.n && a != c && a && n) {
+            // second in-place add into the buffer whose first term is still on record: both in one pass, which is itself
+            // kept on record for one more call (the ReLU of the sum takes it over, anything else runs it first)
+            p.kind = 2; p.src2 = a; p.s2 = sca; p.t2 = scb;
+            return 0;
+        }
+        if (p.kind == 1 && !inc_c && c && c == b && c != p.dst && a == p.src && a != c && n == p.n && sca == p.sa && scb == p.sb && lz_any(cx)) {
+            // the same source copied into a second zero destination (LAdd::backward, second parent): one pass for both
+            int status = 0;
+            if (lz_take(cx, st, c, n * sizeof(float), &status)) { p.kind = 3; p.dst2 = c; return 0; }
+            if (status) return status;
         }
         if (int r = pend_copy_flush(cx, st)) return r;
     }
@@ -283,7 +348,7 @@ int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b
             if (c == b) {
                 // record instead of run: the next call is usually the second term of the same sum
                 PendCopy &p = pend_copy(cx);
-                p.active = true; p.dst = c; p.src = a; p.sa = sca; p.sb = scb; p.n = n;
+                p.active = true; p.kind = 1; p.dst = c; p.src = a; p.src2 = nullptr; p.sa = sca; p.sb = scb; p.n = n;
                 return 0;
             }
             return launch1(cx, st, b, c, n, ZeroAxpbF{sca, scb}, "gpu_add", 12.0);

@@ -190,7 +190,8 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *          it, and an accumulating kernel (conv2d_bwd_data, bn_bwd, relu_bwd, inc, axpby with inc_c, pool backward)
  *          that owns the whole range stores its result instead of adding to it (same bits); the in-place form
  *          eddlb200_axpby(s, a, t, c, c, 0) into such a c is recorded and runs with the next call (fused with it when
- *          that is the second in-place add into c).  Off by default: device
+ *          that is the second in-place add into c; the sum then stays on record for one more call and is fused
+ *          with an eddlb200_relu_fwd of c).  Off by default: device
  *          code outside this library does not see a deferred fill.  0 writes everything still deferred and returns
  *          to immediate fills.
  *          "conv_prefetch" 1 (default) = in 1x1 unpadded layers a spare warp of the tensor-core kernel prefetches the

@@ -121,10 +121,46 @@ def test_accumulating_kernels_take_over_the_fill(lazy):
     lib.call("axpby", 0, 1.0, da, 1.0, d, d, 0, N)
     assert lib.launches() == before
     lib.call("axpby", 0, 0.5, db, 2.0, d, d, 0, N)
-    assert lib.launches() == before + 1
+    assert lib.launches() == before                          # the sum stays on record for one more call ...
     first = orc.axpby(1.0, a, 1.0, zero)
-    got = d.numpy(); want = orc.axpby(0.5, b, 2.0, first)
+    got = d.numpy(); want = orc.axpby(0.5, b, 2.0, first)    # ... and the read runs both adds in one launch
+    assert lib.launches() == before + 1
     np.testing.assert_array_equal(got, want); np.testing.assert_array_equal(np.signbit(got), np.signbit(want))
+    # the activation that follows LAdd: the ReLU of a sum still on record writes the sum and its ReLU in ONE launch
+    for n_el in (N, N - 3):                                  # 16-byte path and the scalar tail
+        d = fresh(); r = garbage(lib, (N,), rng); before = lib.launches()
+        lib.call("axpby", 0, 1.0, da, 1.0, d, d, 0, N)
+        lib.call("axpby", 0, 1.0, db, 1.0, d, d, 0, N)
+        if n_el == N:
+            lib.call("relu_fwd", 0, d, r, N)
+            assert lib.launches() == before + 1
+            want = orc.axpby(1.0, b, 1.0, first)
+            np.testing.assert_array_equal(d.numpy(), want)
+            np.testing.assert_array_equal(r.numpy(), np.where(want > 0, want, F(0.0)).astype(F))
+        else:
+            # a ReLU of another length is not the layer that follows: the sum is written first, then the ReLU runs alone
+            lib.call("relu_fwd", 0, d, r, n_el)
+            assert lib.launches() == before + 2
+            want = orc.axpby(1.0, b, 1.0, first)
+            np.testing.assert_array_equal(d.numpy(), want)
+            np.testing.assert_array_equal(r.numpy()[:n_el], np.where(want > 0, want, F(0.0)).astype(F)[:n_el])
+    # LAdd::backward: the same delta is added into the (zero) deltas of both parents -- one launch for both copies
+    d = fresh(); d2 = fresh(); before = lib.launches()
+    lib.call("axpby", 0, 1.0, da, 1.0, d, d, 0, N)
+    lib.call("axpby", 0, 1.0, da, 1.0, d2, d2, 0, N)
+    assert lib.launches() == before
+    got = d.numpy()
+    assert lib.launches() == before + 1
+    np.testing.assert_array_equal(got, first); np.testing.assert_array_equal(np.signbit(got), np.signbit(first))
+    got = d2.numpy()
+    np.testing.assert_array_equal(got, first); np.testing.assert_array_equal(np.signbit(got), np.signbit(first))
+    # ... but not when the second copy has another source: two launches
+    d = fresh(); d2 = fresh(); before = lib.launches()
+    lib.call("axpby", 0, 1.0, da, 1.0, d, d, 0, N)
+    lib.call("axpby", 0, 1.0, db, 1.0, d2, d2, 0, N)
+    np.testing.assert_array_equal(d.numpy(), first)
+    np.testing.assert_array_equal(d2.numpy(), orc.axpby(1.0, b, 1.0, zero))
+    assert lib.launches() == before + 2
     # a recorded first term is written out by whatever else comes next: a read of the destination ...
     d = fresh()
     lib.call("axpby", 0, 1.0, da, 1.0, d, d, 0, N)

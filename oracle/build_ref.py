@@ -1,7 +1,7 @@
 """TEST INFRASTRUCTURE ONLY: compile the reference's own host sources in place.
 
-Compiles the EDDL v1.1 C++ sources where they lie (``$EDDL_REFERENCE``, default
-``/root/reference``) with plain g++ -- the reference's CMake superbuild needs
+Compiles the EDDL v1.1 C++ sources where they lie (the directory
+``$EDDL_REFERENCE`` names) with plain g++ -- the reference's CMake superbuild needs
 network access and Eigen, so it is not used -- into objects under a git-ignored
 ``_ref`` directory.  Two flavours:
 

@@ -1,5 +1,5 @@
 """Regenerates the golden fixtures of this directory.  Needs the EDDL source tree
-(``$EDDL_REFERENCE``, default ``/root/reference``) and the reference CPU build
+(the directory ``$EDDL_REFERENCE`` names) and the reference CPU build
 (``python oracle/build_ref.py cpu``); the fixtures themselves are committed so that the tests run
 where neither is present.
 

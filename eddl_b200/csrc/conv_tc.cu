@@ -199,6 +199,7 @@ struct Layout {
 //   warp  8     one lane issues the MMAs of a tile into one of the accumulator SETS in tensor memory.
 //   warps 9-12  epilogue: drain a finished set (tcgen05.ld), add its accumulators, store -- overlapped with the MMAs of
 //               the next tile whenever tensor memory holds two sets (BN <= 64, or short chains at BN = 128).
+//   warp  13    1x1 unpadded forward / backward-data only: prefetches the activation operand of coming K-blocks into L2.
 // WGRAD = false (forward, backward-data): A rows are pixels (one thread per row, vector stores); B is the weight operand,
 // prepared once per call by pack_b_kernel.  WGRAD = true (backward-weight): A and B are gathered with one lane per k.
 // BGATHER (backward-weight of 1x1 stride-1 unpadded convolutions): both operands are contiguous along k = (n, p, q) inside an

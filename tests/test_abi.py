@@ -64,3 +64,15 @@ def test_dropin_library_exports_harness_and_distributed_api():
     for s in ("_ZN9eddl_b20016init_distributedEv", "_ZN9eddl_b20023avg_weights_distributedEP3Netii",
               "_ZN9eddl_b20028broadcast_params_distributedEP3Net", "_Z10gpu_conv2DP16ConvolDescriptor", "_Z8gpu_reluP6TensorS0_"):
         assert hasattr(cdll, s), s
+
+
+def test_tuning_options_are_host_side_switches():
+    """The kernel tuning switches are plain host state: they can be set without a GPU, and unknown names or values are refused."""
+    cdll = ctypes.CDLL(capi.LIBPATH)
+    cdll.eddlb200_set_option.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    cdll.eddlb200_set_option.restype = ctypes.c_int
+    for name, value in ((b"conv_prefetch", 0), (b"conv_prefetch", 1), (b"bn_waves", 4), (b"bn_waves", 16),
+                        (b"bn_min_items", 2048), (b"bn_min_items", 8192), (b"conv_path", 0)):
+        assert cdll.eddlb200_set_option(name, value) == 0, (name, value)
+    for name, value in ((b"conv_prefetch", 2), (b"bn_waves", 0), (b"no_such_option", 1), (b"conv_path", 7)):
+        assert cdll.eddlb200_set_option(name, value) == -1, (name, value)      # EDDLB200_EINVAL

@@ -6,7 +6,7 @@
 ``build_dropin()``   g++ -> ``baseline/_ref/libeddl_b200_dropin.so``: the C++ shim that defines
                      EDDL's ``gpu_*`` functions on top of the C ABI (``eddl_b200/shim``), the
                      distributed entry points and the net harness, linked with EDDL's own host
-                     sources compiled with ``-DcGPU`` (``oracle/build_ref.py``).  Needs the EDDL
+                     sources compiled with ``-DcGPU`` (``baseline/build_host.py``).  Needs the EDDL
                      source tree; skipped when it is absent (the prebuilt library is used).
 """
 import concurrent.futures as cf
@@ -63,19 +63,24 @@ def build_kernels(verbose=False):
     return lib
 
 
+def _host_recipe():
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import build_host
+    return build_host
+
+
 def build_dropin():
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import build_ref
+    recipe = _host_recipe()
     outdir = os.path.join(ROOT, "baseline", "_ref")
     lib = os.path.join(outdir, "libeddl_b200_dropin.so")
-    if not build_ref.have_reference():
+    if not recipe.have_reference():
         return lib if os.path.exists(lib) else None
     kernels = build_kernels()
-    objs = build_ref.build_gpu_host_objects()
+    objs = recipe.build_gpu_host_objects()
     mine = sorted(os.path.join(PKG, "shim", f) for f in os.listdir(os.path.join(PKG, "shim")) if f.endswith(".cpp"))
     mine.append(os.path.join(PKG, "host", "net_harness.cpp"))
     hdrs = [os.path.join(ROOT, "include", f) for f in os.listdir(os.path.join(ROOT, "include"))]
-    flags = build_ref.COMMON + ["-DcGPU", "-I" + build_ref.CUDA_INC, "-I" + os.path.join(ROOT, "include")]
+    flags = recipe.COMMON + ["-DcGPU", "-I" + recipe.CUDA_INC, "-I" + os.path.join(ROOT, "include")]
     shim_objs = []
     for s in mine:
         o = os.path.join(outdir, "obj_shim", os.path.basename(s)[:-4] + ".o")

@@ -269,8 +269,8 @@ int eddlb200_bn_fwd(int dev, int b, int z, int rc, const float *input, float *ou
     {
         const size_t tb = (size_t)b * z * rc * sizeof(float), zb = (size_t)z * sizeof(float);
         EB_READS(input, tb); EB_WRITES(output, tb); EB_WRITES(opa, tb); EB_WRITES(relu_out, tb);
-        EB_READS(global_mean, zb); EB_READS(global_variance, zb); EB_READS(affine_g, zb); EB_READS(affine_b, zb);
-        EB_READS(mean, zb); EB_READS(variance, zb);
+        EB_MODIFIES(global_mean, zb); EB_MODIFIES(global_variance, zb); EB_READS(affine_g, zb); EB_READS(affine_b, zb);
+        EB_MODIFIES(mean, zb); EB_MODIFIES(variance, zb);
     }
     ProfScope prof(cx, PROF_BN_FWD, 16.0 * b * (double)z * rc);
     const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
@@ -302,8 +302,9 @@ int eddlb200_bn_bwd(int dev, int b, int z, int rc, float *delta, const float *op
     bool pd_zero = false;
     {
         const size_t tb = (size_t)b * z * rc * sizeof(float), zb = (size_t)z * sizeof(float);
-        EB_READS(delta, tb); EB_READS(opa, tb);
-        EB_READS(gbn_g, zb); EB_READS(gbn_b, zb); EB_READS(bn_g, zb); EB_READS(variance, zb); EB_READS(mean1, zb); EB_READS(mean2, zb);
+        EB_MODIFIES(delta, tb); EB_READS(opa, tb);
+        EB_MODIFIES(gbn_g, zb); EB_MODIFIES(gbn_b, zb); EB_READS(bn_g, zb); EB_READS(variance, zb); EB_MODIFIES(mean1, zb); EB_MODIFIES(mean2, zb);
+        EB_NOTES(pdelta, tb);
         if (lz_any(cx) && pdelta != delta && pdelta != opa) {
             int status = 0;
             pd_zero = lz_take(cx, st, pdelta, tb, &status);
@@ -386,22 +387,32 @@ extern "C" int eddlb200_bn_fwd_noalloc(int dev, int b, int z, int rc, const floa
         (affine_g && !(affine_b && opa)) || (trmode && !mean) || (size_t)b * rc >= 0xfffffff0u)
         return set_error(EDDLB200_EINVAL, "bn_fwd_noalloc: bad argument");
     const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
-    if ((size_t)z * S > kNoAllocPairs)
+    if (trmode && (size_t)z * S > kNoAllocPairs)          // inference reads no partial sums
         return set_error(EDDLB200_ELIMIT, "bn_fwd_noalloc: %d channels x %u slices need %zu partial pairs, the built-in scratch holds %u",
                          z, S, (size_t)z * S, kNoAllocPairs);
     cudaError_t e = cudaSetDevice(dev);
     if (e != cudaSuccess) return cuda_status(e, "bn_fwd_noalloc(cudaSetDevice)");
     float2 *partial = noalloc_scratch(dev);
     if (!partial) return EDDLB200_ENOINIT;
-    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const cudaStream_t caller = (cudaStream_t)cuda_stream;
     if (DevCtx *cx = ctx_peek(dev)) {
-        // a device context exists and may owe zeros or a recorded copy to one of these buffers: settle them on this stream
+        // A device context exists.  It may owe deferred zeros or a recorded copy -- possibly to buffers this call never
+        // sees -- and that work belongs on the library's compute stream, where whatever produces its operands runs.  It
+        // is settled THERE; when the caller's stream is a different one, an event that exists since the context was
+        // created is recorded behind it and the caller's stream waits on it, so the kernels below run after the settled
+        // work and after everything the library had enqueued (nothing is created or allocated on this path).
+        const cudaStream_t st = stream_of(cx);
         if (pend_copy_active(cx)) { if (int r = pend_copy_flush(cx, st)) return r; }
         const size_t tb = (size_t)b * z * rc * sizeof(float), zb = (size_t)z * sizeof(float);
         EB_READS(input, tb); EB_WRITES(output, tb); EB_WRITES(opa, tb); EB_WRITES(relu_out, tb);
-        EB_READS(global_mean, zb); EB_READS(global_variance, zb); EB_READS(affine_g, zb); EB_READS(affine_b, zb);
-        EB_READS(mean, zb); EB_READS(variance, zb);
+        EB_MODIFIES(global_mean, zb); EB_MODIFIES(global_variance, zb); EB_READS(affine_g, zb); EB_READS(affine_b, zb);
+        EB_MODIFIES(mean, zb); EB_MODIFIES(variance, zb);
+        if (caller != st) {
+            if ((e = cudaEventRecord(handoff_event(cx), st)) != cudaSuccess) return cuda_status(e, "bn_fwd_noalloc(record)");
+            if ((e = cudaStreamWaitEvent(caller, handoff_event(cx), 0)) != cudaSuccess) return cuda_status(e, "bn_fwd_noalloc(wait)");
+        }
     }
+    const cudaStream_t st = caller;
     const bool vec = (rc % 4 == 0) && aligned16(input) && aligned16(output) && (!opa || aligned16(opa)) && (!relu_out || aligned16(relu_out));
     dim3 grid(z, S);
     if (trmode) {

@@ -118,7 +118,7 @@ int eddlb200_allreduce_avg(int dev, float *buf, size_t n) {
     EB_CTX(dev);
     if (n == 0) return 0;
     EB_REQUIRE(buf, "allreduce_avg");
-    EB_READS(buf, n * sizeof(float));
+    EB_MODIFIES(buf, n * sizeof(float));
     ProfScope prof(cx, PROF_COMM, 4.0 * n);
     const int N = comm_nranks(cx);
     if (comm_of(cx)) {
@@ -136,7 +136,7 @@ int eddlb200_allreduce_avg_multi(int dev, float *const *bufs, const size_t *size
     for (int i = 0; i < ntensors; i++) {
         if (!sizes[i]) continue;
         EB_REQUIRE(bufs[i], "allreduce_avg_multi");
-        EB_READS(bufs[i], sizes[i] * sizeof(float));
+        EB_MODIFIES(bufs[i], sizes[i] * sizeof(float));
         segs.push_back(Seg{bufs[i], (unsigned long long)sizes[i], (unsigned long long)total});
         total += (sizes[i] + 3) & ~size_t(3);
         if (sizes[i] > largest) largest = sizes[i];
@@ -168,7 +168,7 @@ int eddlb200_broadcast(int dev, float *buf, size_t n, int root) {
     EB_CTX(dev);
     if (n == 0 || !comm_of(cx)) return 0;
     EB_REQUIRE(buf && root >= 0 && root < comm_nranks(cx), "broadcast");
-    EB_READS(buf, n * sizeof(float));
+    EB_MODIFIES(buf, n * sizeof(float));
     if (int r = nccl_status(ncclBroadcast(buf, buf, n, ncclFloat, root, comm_of(cx), st), "ncclBroadcast")) return r;
     count_launch(cx);
     return 0;
@@ -178,7 +178,7 @@ int eddlb200_avg_grad_sgd(int dev, float *p, float *g, float *m, float lr, float
     EB_CTX(dev);
     if (n == 0) return 0;
     EB_REQUIRE(p && g && m, "avg_grad_sgd");
-    EB_READS(p, n * sizeof(float)); EB_READS(g, n * sizeof(float)); EB_READS(m, n * sizeof(float));
+    EB_MODIFIES(p, n * sizeof(float)); EB_MODIFIES(g, n * sizeof(float)); EB_MODIFIES(m, n * sizeof(float));
     const int N = comm_nranks(cx);
     if (comm_of(cx)) {
         if (int r = nccl_status(ncclAllReduce(g, g, n, ncclFloat, ncclSum, comm_of(cx), st), "ncclAllReduce")) return r;

@@ -20,6 +20,9 @@ DevCtx *ctx(int dev);
 // The context of `dev` if one has been created, else nullptr; creates and allocates nothing.
 DevCtx *ctx_peek(int dev);
 cudaStream_t stream_of(DevCtx *c);
+// An event that exists for the lifetime of the context (nothing is created when it is used): record it on the compute
+// stream and make another stream wait on it to order that stream after everything enqueued so far.
+cudaEvent_t handoff_event(DevCtx *c);
 // Stream-ordered scratch of at least `bytes` bytes, reused by every kernel that
 // runs on the device's compute stream (valid until the next scratch() call).
 void *scratch(DevCtx *c, size_t bytes);
@@ -80,13 +83,49 @@ int pend_copy_flush(DevCtx *c, cudaStream_t st);                         // defi
 
 }  // namespace eb
 
+namespace eb {
+// Write observers.  A cache whose contents are derived from device memory (packed weight tiles, the value of a loss)
+// registers the source range with watch_add and remembers the version it returns; every entry point declares what it
+// writes (EB_WRITES: overwrites, EB_MODIFIES: read-modify-write, lz_take: accumulates), and a declared write that overlaps
+// a watched range gives it a new version, so the cache sees that its copy is stale.  Ranges vanish when their memory is
+// released.
+unsigned long long watch_add(DevCtx *c, const void *p, size_t bytes);     // registers (or finds) the range; returns its version
+unsigned long long watch_version(DevCtx *c, const void *p);               // 0 = not watched (any more)
+bool watch_any(DevCtx *c);
+void note_write(DevCtx *c, const void *p, size_t bytes);
+void watch_forget(DevCtx *c, const void *p, size_t bytes);
+}  // namespace eb
+
+namespace eb {
+// Loss and metric of one (target, prediction) pair, kept per device.  Net::train_batch evaluates both twice per step
+// (src/net/net_api.cpp:46 and :1300 -> :534-569) on unchanged tensors: the first request computes both values with one
+// read-back, the others are answered from here as long as no declared write has touched either tensor.
+struct LossCache {
+    bool valid = false;
+    const float *y_true = nullptr, *y_pred = nullptr; int rows = 0, cols = 0;
+    unsigned long long v_true = 0, v_pred = 0;
+    float loss = 0.f; int hits = 0;
+};
+LossCache &loss_cache(DevCtx *c);
+}  // namespace eb
+
 #define EB_READS(p, bytes)                                                              \
     do {                                                                                \
         if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_read(cx, st, (p), (bytes))) return r__; } \
     } while (0)
 #define EB_WRITES(p, bytes)                                                             \
     do {                                                                                \
+        if ((p) && eb::watch_any(cx)) eb::note_write(cx, (p), (bytes));                 \
         if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_write(cx, st, (p), (bytes))) return r__; } \
+    } while (0)
+// an accumulated-into destination whose deferred zeros are dealt with separately (lz_take): tell the observers only
+#define EB_NOTES(p, bytes)                                                              \
+    do { if ((p) && eb::watch_any(cx)) eb::note_write(cx, (p), (bytes)); } while (0)
+// read-modify-write of a destination: zeros owed to it are written first, and observers of the range are told
+#define EB_MODIFIES(p, bytes)                                                           \
+    do {                                                                                \
+        if ((p) && eb::watch_any(cx)) eb::note_write(cx, (p), (bytes));                 \
+        if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_read(cx, st, (p), (bytes))) return r__; } \
     } while (0)
 
 // Every entry point but eddlb200_axpby and eddlb200_relu_fwd starts by writing out a deferred "first term" of an in-place sum (see pend_copy_*).

@@ -103,6 +103,7 @@ int eddlb200_conv2d_bwd_data(int dev, const float *dy, const float *w, float *dx
     EB_READS(dy, (size_t)n * k * oh * ow * sizeof(float)); EB_READS(w, (size_t)k * c * kr * kc * sizeof(float));
     const size_t dx_elems = (size_t)n * c * ih * iw;
     bool dx_zero = false;
+    EB_NOTES(dx, dx_elems * sizeof(float));
     if (lz_any(cx)) { int status = 0; dx_zero = lz_take(cx, st, dx, dx_elems * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_CONV_BWD_DATA, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
@@ -125,6 +126,7 @@ int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *
     EB_READS(gbias, (size_t)k * sizeof(float));
     const size_t gw_elems = (size_t)k * c * kr * kc;
     bool gw_zero = false;
+    EB_NOTES(gw, gw_elems * sizeof(float)); EB_NOTES(gbias, (size_t)k * sizeof(float));
     if (lz_any(cx)) { int status = 0; gw_zero = lz_take(cx, st, gw, gw_elems * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_CONV_BWD_WEIGHT, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (gbias) {

@@ -111,7 +111,7 @@ int launch3(DevCtx *cx, cudaStream_t st, const float *a, const float *b, float *
     if (!a || !b || !c) return set_error(EDDLB200_EINVAL, "%s: null pointer", what);
     EB_READS(a, n * sizeof(float));
     EB_READS(b, n * sizeof(float));
-    if (F::reads_c) EB_READS(c, n * sizeof(float)); else EB_WRITES(c, n * sizeof(float));
+    if (F::reads_c) EB_MODIFIES(c, n * sizeof(float)); else EB_WRITES(c, n * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, (bytes_per_element > 0 ? bytes_per_element : (F::reads_c ? 16.0 : 12.0)) * n);
     if (aligned16(a) && aligned16(b) && aligned16(c)) {
         size_t n4 = n / 4;
@@ -400,7 +400,7 @@ int eddlb200_pad(int dev, const float *a, float *b, int n, int c, int h, int w, 
     if (!total) return 0;
     // the kernel writes the interior of b only: zeros owed to b have to be there first
     EB_READS(a, total * sizeof(float));
-    EB_READS(b, (size_t)n * c * (h + top + bottom) * (w + left + right) * sizeof(float));
+    EB_MODIFIES(b, (size_t)n * c * (h + top + bottom) * (w + left + right) * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, 8.0 * total);
     pad_kernel<false><<<grid_for(total, kBlock), kBlock, 0, st>>>(const_cast<float *>(a), b, total, h, w, top, left, h + top + bottom, w + left + right);
     EB_LAUNCH_CHECK("gpu_pad");
@@ -411,7 +411,7 @@ int eddlb200_pad_bwd(int dev, float *a_delta, const float *b_delta, int n, int c
     EB_REQUIRE(a_delta && b_delta && n >= 0 && c >= 0 && h >= 0 && w >= 0 && top >= 0 && bottom >= 0 && left >= 0 && right >= 0, "gpu_pad_back");
     size_t total = (size_t)n * c * h * w;
     if (!total) return 0;
-    EB_READS(a_delta, total * sizeof(float));
+    EB_MODIFIES(a_delta, total * sizeof(float));
     EB_READS(b_delta, (size_t)n * c * (h + top + bottom) * (w + left + right) * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, 12.0 * total);
     pad_kernel<true><<<grid_for(total, kBlock), kBlock, 0, st>>>(a_delta, const_cast<float *>(b_delta), total, h, w, top, left, h + top + bottom, w + left + right);

@@ -124,7 +124,7 @@ int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, flo
         if (lz_take(cx, st, c, (size_t)m * n * sizeof(float), &status)) inc_c = 2;
         if (status) return status;
     }
-    if (inc_c == 1) EB_READS(c, (size_t)m * n * sizeof(float)); else EB_WRITES(c, (size_t)m * n * sizeof(float));
+    if (inc_c == 1) EB_MODIFIES(c, (size_t)m * n * sizeof(float)); else EB_WRITES(c, (size_t)m * n * sizeof(float));
     ProfScope prof(cx, PROF_GEMM, 2.0 * m * (double)n * k);
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
     const int tiles = (int)(grid.x * grid.y);
@@ -169,7 +169,7 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
     EB_CTX(dev);
     EB_REQUIRE(a && b && rows >= 0 && cols >= 0 && (axis == 0 || axis == 1), "gpu_reduce_sum2D");
     EB_READS(a, (size_t)rows * cols * sizeof(float));
-    if (inc_b) EB_READS(b, (size_t)(axis == 0 ? cols : rows) * sizeof(float)); else EB_WRITES(b, (size_t)(axis == 0 ? cols : rows) * sizeof(float));
+    if (inc_b) EB_MODIFIES(b, (size_t)(axis == 0 ? cols : rows) * sizeof(float)); else EB_WRITES(b, (size_t)(axis == 0 ? cols : rows) * sizeof(float));
     if (axis == 0) {
         if (!cols) return 0;
         colsum_kernel<<<(cols + 255) / 256, 256, 0, st>>>(a, b, rows, cols, inc_b);

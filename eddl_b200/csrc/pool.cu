@@ -304,6 +304,7 @@ int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const fl
     const size_t ob = (size_t)n * c * oh * ow * sizeof(float);
     EB_READS(d, ob); EB_READS(ind_x, ob); EB_READS(ind_y, ob);
     int id_zero = 0;
+    EB_NOTES(id, total * sizeof(float));
     if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + 8.0 * total);     // canonical count, also for the id_zero variant
     const size_t plane_smem = (size_t)8 * oh * ow + (size_t)4 * (ih + iw);
@@ -356,6 +357,7 @@ int eddlb200_avgpool2d_bwd(int dev, const float *d, float *id, int n, int c, int
     PoolGeom g{ih, iw, oh, ow, kr, kc, sr, sc, pad_top, pad_left};
     EB_READS(d, (size_t)n * c * oh * ow * sizeof(float));
     int id_zero = 0;
+    EB_NOTES(id, total * sizeof(float));
     if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + 8.0 * total);
     if (total < (size_t(1) << 32)) pool_bwd_kernel<false, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g, id_zero);

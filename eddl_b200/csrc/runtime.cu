@@ -39,6 +39,19 @@ struct DevCtx {
     bool lz_on = false;
     std::map<uintptr_t, size_t> lz;
     PendCopy pend;
+    // write observers: start address -> (bytes, version)
+    struct Watch { size_t bytes; unsigned long long version; };
+    std::map<uintptr_t, Watch> watch;
+    unsigned long long watch_clock = 0;
+    LossCache loss;
+    // staged host->device copies: a ring of (pinned host buffer, device buffer) pairs fed by a copy stream
+    struct Stage { void *host = nullptr, *dev = nullptr; size_t cap = 0; cudaEvent_t landed = nullptr, consumed = nullptr; bool used = false; };
+    static constexpr int kStages = 4;
+    Stage stages[kStages];
+    int stage_next = 0;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_peer = nullptr, ev_peer_done = nullptr;
+    cudaEvent_t ev_handoff = nullptr;        // created with the context: orders a caller's stream after the compute stream
 };
 
 static DevCtx g_ctx[EDDLB200_MAX_DEVICES];
@@ -71,6 +84,7 @@ static int init_locked(int dev) {
     if ((e = cudaMallocHost((void **)&c.h_scalars, 64 * sizeof(float))) != cudaSuccess) return cuda_status(e, "cudaMallocHost");
     if ((e = cudaMalloc((void **)&c.d_scalars, 64 * sizeof(float))) != cudaSuccess) return cuda_status(e, "cudaMalloc");
     for (int i = 0; i < 16; i++) { cudaEventCreate(&c.ev_start[i]); cudaEventCreate(&c.ev_stop[i]); }
+    if ((e = cudaEventCreateWithFlags(&c.ev_handoff, cudaEventDisableTiming)) != cudaSuccess) return cuda_status(e, "cudaEventCreate");
     c.dev = dev;
     c.lz_on = g_lz_default;
     c.ready = true;
@@ -90,6 +104,7 @@ DevCtx *ctx(int dev) {
 
 DevCtx *ctx_peek(int dev) { return (dev >= 0 && dev < EDDLB200_MAX_DEVICES && g_ctx[dev].ready) ? &g_ctx[dev] : nullptr; }
 cudaStream_t stream_of(DevCtx *c) { return c->stream; }
+cudaEvent_t handoff_event(DevCtx *c) { return c->ev_handoff; }
 float *host_scalars(DevCtx *c) { return c->h_scalars; }
 float *dev_scalars(DevCtx *c) { return c->d_scalars; }
 ncclComm *comm_of(DevCtx *c) { return c->comm; }
@@ -121,6 +136,43 @@ void *scratch(DevCtx *c, size_t bytes) {
     if (cudaMalloc(&c->scratch_ptr, want) != cudaSuccess) { set_error(cudaErrorMemoryAllocation, "scratch arena of %zu bytes", want); return nullptr; }
     c->scratch_bytes = want;
     return c->scratch_ptr;
+}
+
+// ---- write observers ----------------------------------------------------------------------------------
+LossCache &loss_cache(DevCtx *c) { return c->loss; }
+bool watch_any(DevCtx *c) { return !c->watch.empty(); }
+template <typename V>
+static void watch_visit(DevCtx *c, const void *p, size_t bytes, V visit) {
+    if (c->watch.empty() || !bytes) return;
+    const uintptr_t lo = (uintptr_t)p, hi = lo + bytes;
+    // registered ranges are kept disjoint (watch_add), so at most one range starting below lo can reach into [lo, hi)
+    auto it = c->watch.lower_bound(lo);
+    if (it != c->watch.begin()) { auto prev = std::prev(it); if (prev->first + prev->second.bytes > lo) visit(prev); }
+    for (; it != c->watch.end() && it->first < hi; ++it) visit(it);
+}
+unsigned long long watch_add(DevCtx *c, const void *p, size_t bytes) {
+    auto it = c->watch.find((uintptr_t)p);
+    if (it != c->watch.end() && it->second.bytes >= bytes) return it->second.version;
+    // a new range, or one that grew: drop whatever it overlaps (those observers then read version 0 = stale, which is safe)
+    std::vector<uintptr_t> gone;
+    watch_visit(c, p, bytes, [&](std::map<uintptr_t, DevCtx::Watch>::iterator w) { gone.push_back(w->first); });
+    for (uintptr_t k : gone) c->watch.erase(k);
+    const unsigned long long v = ++c->watch_clock;
+    c->watch[(uintptr_t)p] = DevCtx::Watch{bytes, v};
+    return v;
+}
+unsigned long long watch_version(DevCtx *c, const void *p) {
+    auto it = c->watch.find((uintptr_t)p);
+    return it == c->watch.end() ? 0ull : it->second.version;
+}
+void note_write(DevCtx *c, const void *p, size_t bytes) {
+    watch_visit(c, p, bytes, [&](std::map<uintptr_t, DevCtx::Watch>::iterator it) { it->second.version = ++c->watch_clock; });
+}
+void watch_forget(DevCtx *c, const void *p, size_t bytes) {
+    if (c->watch.empty() || !bytes) return;
+    std::vector<uintptr_t> gone;
+    watch_visit(c, p, bytes, [&](std::map<uintptr_t, DevCtx::Watch>::iterator it) { gone.push_back(it->first); });
+    for (uintptr_t k : gone) c->watch.erase(k);
 }
 
 // ---- deferred zero fills ------------------------------------------------------------------------------
@@ -159,6 +211,7 @@ int lz_write(DevCtx *c, cudaStream_t st, const void *p, size_t bytes) {
 }
 bool lz_take(DevCtx *c, cudaStream_t st, const void *p, size_t bytes, int *status) {
     *status = 0;
+    if (!c->watch.empty()) note_write(c, p, bytes);       // the caller is about to accumulate into [p, p + bytes)
     if (c->lz.empty() || !bytes) return false;
     auto it = c->lz.find((uintptr_t)p);
     if (it != c->lz.end() && it->second == bytes) { c->lz.erase(it); g_lzs.taken++; return true; }
@@ -167,6 +220,7 @@ bool lz_take(DevCtx *c, cudaStream_t st, const void *p, size_t bytes, int *statu
 }
 bool lz_defer(DevCtx *c, cudaStream_t st, void *p, size_t bytes) {
     if (!c->lz_on || bytes < kLazyZeroMinBytes || (bytes % sizeof(float))) return false;
+    if (!c->watch.empty()) note_write(c, p, bytes);       // a recorded fill is a write all the same
     // older deferred fills inside the new range are superseded; ones that stick out are written now
     if (lz_write(c, st, p, bytes) != 0) return false;
     c->lz[(uintptr_t)p] = bytes;
@@ -256,6 +310,7 @@ int eddlb200_free(int dev, void *p) {
     cx->live.erase(it);
     cx->bytes_in_use -= sz;
     lz_forget(cx, p, sz);
+    watch_forget(cx, p, sz);
     // All work of this library runs on one stream per device, so a block handed out
     // again is only touched by work ordered after everything that used it before.
     cx->free_blocks.emplace(sz, p); cx->bytes_cached += sz;
@@ -286,6 +341,42 @@ int eddlb200_memcpy_h2d_async(int dev, void *dst, const void *src, size_t bytes)
     return cuda_status(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st), "memcpy_h2d_async");
 }
 
+int eddlb200_memcpy_h2d_staged(int dev, void *dst, const void *src, size_t bytes) {
+    EB_CTX(dev);
+    if (bytes == 0) return 0;
+    if (!dst || !src) return set_error(EDDLB200_EINVAL, "memcpy_h2d_staged: null pointer");
+    cudaError_t e = cudaSuccess;
+    if (!cx->copy_stream && (e = cudaStreamCreateWithFlags(&cx->copy_stream, cudaStreamNonBlocking)) != cudaSuccess) return cuda_status(e, "memcpy_h2d_staged(stream)");
+    DevCtx::Stage &sg = cx->stages[cx->stage_next];
+    cx->stage_next = (cx->stage_next + 1) % DevCtx::kStages;
+    if (!sg.landed) {
+        if ((e = cudaEventCreateWithFlags(&sg.landed, cudaEventDisableTiming)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&sg.consumed, cudaEventDisableTiming)) != cudaSuccess) return cuda_status(e, "memcpy_h2d_staged(event)");
+    }
+    // the pair is free again once the device-side copy of its previous use has run
+    if (sg.used && (e = cudaEventSynchronize(sg.consumed)) != cudaSuccess) return cuda_status(e, "memcpy_h2d_staged(wait)");
+    if (sg.cap < bytes) {
+        if (sg.host) cudaFreeHost(sg.host);
+        if (sg.dev) cudaFree(sg.dev);
+        sg.host = sg.dev = nullptr; sg.cap = 0;
+        const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+        if ((e = cudaMallocHost(&sg.host, want)) != cudaSuccess || (e = cudaMalloc(&sg.dev, want)) != cudaSuccess) {
+            if (sg.host) cudaFreeHost(sg.host);
+            sg.host = nullptr;
+            return cuda_status(e, "memcpy_h2d_staged(buffers)");
+        }
+        sg.cap = want;
+    }
+    memcpy(sg.host, src, bytes);                 // from here on the caller's buffer is no longer needed
+    if ((e = cudaMemcpyAsync(sg.dev, sg.host, bytes, cudaMemcpyHostToDevice, cx->copy_stream)) != cudaSuccess) return cuda_status(e, "memcpy_h2d_staged(h2d)");
+    if ((e = cudaEventRecord(sg.landed, cx->copy_stream)) != cudaSuccess) return cuda_status(e, "memcpy_h2d_staged(record)");
+    if ((e = cudaStreamWaitEvent(st, sg.landed, 0)) != cudaSuccess) return cuda_status(e, "memcpy_h2d_staged(wait event)");
+    EB_WRITES(dst, bytes);
+    if ((e = cudaMemcpyAsync(dst, sg.dev, bytes, cudaMemcpyDeviceToDevice, st)) != cudaSuccess) return cuda_status(e, "memcpy_h2d_staged(d2d)");
+    sg.used = true;
+    return cuda_status(cudaEventRecord(sg.consumed, st), "memcpy_h2d_staged(record)");
+}
+
 int eddlb200_memcpy_d2h(int dev, void *dst, const void *src, size_t bytes) {
     EB_CTX(dev);
     if (bytes == 0) return 0;
@@ -301,6 +392,39 @@ int eddlb200_memcpy_d2d(int dev, void *dst, const void *src, size_t bytes) {
     EB_READS(src, bytes);
     EB_WRITES(dst, bytes);
     return cuda_status(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st), "gpu_copy_gpu");
+}
+
+static cudaEvent_t peer_event(cudaEvent_t &slot) {
+    if (!slot && cudaEventCreateWithFlags(&slot, cudaEventDisableTiming) != cudaSuccess) slot = nullptr;
+    return slot;
+}
+
+int eddlb200_memcpy_peer(int dst_dev, void *dst, int src_dev, const void *src, size_t bytes) {
+    if (dst_dev == src_dev) return eddlb200_memcpy_d2d(dst_dev, dst, src, bytes);
+    if (bytes == 0) return 0;
+    if (!dst || !src) return set_error(EDDLB200_EINVAL, "memcpy_peer: null pointer");
+    DevCtx *cd = ctx(dst_dev);
+    if (!cd) return EDDLB200_ENOINIT;
+    cudaEvent_t ready = peer_event(cd->ev_peer);
+    if (!ready) return set_error(EDDLB200_ENOINIT, "memcpy_peer: cannot create an event on device %d", dst_dev);
+    {
+        // what the destination's stream has enqueued so far may still use dst: the copy waits for it
+        DevCtx *cx = cd; cudaStream_t st = stream_of(cd);
+        if (pend_copy_active(cx)) { if (int r = pend_copy_flush(cx, st)) return r; }
+        EB_WRITES(dst, bytes);
+        cudaError_t e = cudaEventRecord(ready, st);
+        if (e != cudaSuccess) return cuda_status(e, "memcpy_peer(record)");
+    }
+    EB_CTX(src_dev);                              // makes src_dev current; the copy runs on the source device's stream
+    EB_READS(src, bytes);
+    cudaEvent_t done = peer_event(cx->ev_peer_done);
+    if (!done) return set_error(EDDLB200_ENOINIT, "memcpy_peer: cannot create an event on device %d", src_dev);
+    cudaError_t e = cudaStreamWaitEvent(st, ready, 0);
+    if (e == cudaSuccess) e = cudaMemcpyPeerAsync(dst, dst_dev, src, src_dev, bytes, st);
+    if (e == cudaSuccess) e = cudaEventRecord(done, st);
+    if (e != cudaSuccess) return cuda_status(e, "memcpy_peer");
+    // later work on the destination's stream is ordered after the copy
+    return cuda_status(cudaStreamWaitEvent(stream_of(cd), done, 0), "memcpy_peer(order)");
 }
 
 int eddlb200_host_alloc(size_t bytes, void **out) {

@@ -133,46 +133,57 @@ int eddlb200_softmax_bwd_nd(int dev, const float *d, const float *s, float *pd, 
     const long long ns = (long long)outer * inner;
     EB_REQUIRE(ns < 0x7fffffffLL, "gpu_d_full_softmax");
     if (!ns) return 0;
-    EB_READS(d, (size_t)ns * cols * sizeof(float)); EB_READS(s, (size_t)ns * cols * sizeof(float)); EB_READS(pd, (size_t)ns * cols * sizeof(float));
+    EB_READS(d, (size_t)ns * cols * sizeof(float)); EB_READS(s, (size_t)ns * cols * sizeof(float)); EB_MODIFIES(pd, (size_t)ns * cols * sizeof(float));
     softmax_bwd_kernel<<<grid_for((size_t)ns * 32, kBlock), kBlock, 0, st>>>(d, s, pd, (int)ns, cols, inner);
     EB_LAUNCH_CHECK("gpu_d_full_softmax");
+    return 0;
+}
+
+// Both scalars of a (target, prediction) pair with ONE read-back, remembered until either tensor is written again.
+static int loss_and_hits(DevCtx *cx, cudaStream_t st, const float *y_true, const float *y_pred, int rows, int cols, float *loss, int *hits) {
+    LossCache &lc = loss_cache(cx);
+    const size_t bytes = (size_t)rows * cols * sizeof(float);
+    if (lc.valid && lc.y_true == y_true && lc.y_pred == y_pred && lc.rows == rows && lc.cols == cols &&
+        lc.v_true == watch_version(cx, y_true) && lc.v_pred == watch_version(cx, y_pred)) {
+        *loss = lc.loss; *hits = lc.hits;
+        return 0;
+    }
+    lc.valid = false;
+    float *dsc = dev_scalars(cx), *hsc = host_scalars(cx);
+    EB_READS(y_true, bytes); EB_READS(y_pred, bytes);
+    cudaError_t e = cudaMemsetAsync(dsc, 0, 2 * sizeof(float), st);
+    if (e != cudaSuccess) return cuda_status(e, "gpu_categorical_cross_entropy");
+    if (rows) {
+        cce_value_kernel<<<((size_t)rows * cols <= (size_t(1) << 20)) ? 1 : grid_for((size_t)rows * 32, kBlock, 1), kBlock, 0, st>>>(y_true, y_pred, rows, cols, dsc);
+        EB_LAUNCH_CHECK("gpu_categorical_cross_entropy");
+        accuracy_kernel<<<grid_for((size_t)rows * 32, kBlock, 1), kBlock, 0, st>>>(y_true, y_pred, rows, cols, (int *)(dsc + 1));
+        EB_LAUNCH_CHECK("gpu_accuracy");
+    }
+    e = cudaMemcpyAsync(hsc, dsc, 2 * sizeof(float), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_status(e, "gpu_categorical_cross_entropy");
+    *loss = -hsc[0]; *hits = ((const int *)hsc)[1];
+    if (bytes) {
+        lc.y_true = y_true; lc.y_pred = y_pred; lc.rows = rows; lc.cols = cols;
+        lc.v_true = watch_add(cx, y_true, bytes); lc.v_pred = watch_add(cx, y_pred, bytes);
+        lc.loss = *loss; lc.hits = *hits;
+        lc.valid = lc.v_true != 0 && lc.v_pred != 0 && watch_version(cx, y_true) == lc.v_true;     // overlapping tensors evict each other
+    }
     return 0;
 }
 
 int eddlb200_cce_value(int dev, const float *y_true, const float *y_pred, int rows, int cols, float *host_out) {
     EB_CTX(dev);
     EB_REQUIRE(y_true && y_pred && host_out && rows >= 0 && cols > 0, "gpu_categorical_cross_entropy");
-    float *dsc = dev_scalars(cx), *hsc = host_scalars(cx);
-    EB_READS(y_true, (size_t)rows * cols * sizeof(float)); EB_READS(y_pred, (size_t)rows * cols * sizeof(float));
-    cudaError_t e = cudaMemsetAsync(dsc, 0, sizeof(float), st);
-    if (e != cudaSuccess) return cuda_status(e, "gpu_categorical_cross_entropy");
-    if (rows) {
-        cce_value_kernel<<<((size_t)rows * cols <= (size_t(1) << 20)) ? 1 : grid_for((size_t)rows * 32, kBlock, 1), kBlock, 0, st>>>(y_true, y_pred, rows, cols, dsc);
-        EB_LAUNCH_CHECK("gpu_categorical_cross_entropy");
-    }
-    e = cudaMemcpyAsync(hsc, dsc, sizeof(float), cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) return cuda_status(e, "gpu_categorical_cross_entropy");
-    *host_out = -hsc[0];
-    return 0;
+    int hits = 0;
+    return loss_and_hits(cx, st, y_true, y_pred, rows, cols, host_out, &hits);
 }
 
 int eddlb200_accuracy(int dev, const float *y_true, const float *y_pred, int rows, int cols, int *host_out) {
     EB_CTX(dev);
     EB_REQUIRE(y_true && y_pred && host_out && rows >= 0 && cols > 0, "gpu_accuracy");
-    int *dsc = (int *)(dev_scalars(cx) + 1), *hsc = (int *)(host_scalars(cx) + 1);
-    EB_READS(y_true, (size_t)rows * cols * sizeof(float)); EB_READS(y_pred, (size_t)rows * cols * sizeof(float));
-    cudaError_t e = cudaMemsetAsync(dsc, 0, sizeof(int), st);
-    if (e != cudaSuccess) return cuda_status(e, "gpu_accuracy");
-    if (rows) {
-        accuracy_kernel<<<grid_for((size_t)rows * 32, kBlock, 1), kBlock, 0, st>>>(y_true, y_pred, rows, cols, dsc);
-        EB_LAUNCH_CHECK("gpu_accuracy");
-    }
-    e = cudaMemcpyAsync(hsc, dsc, sizeof(int), cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) return cuda_status(e, "gpu_accuracy");
-    *host_out = hsc[0];
-    return 0;
+    float loss = 0.f;
+    return loss_and_hits(cx, st, y_true, y_pred, rows, cols, &loss, host_out);
 }
 
 }  // extern "C"

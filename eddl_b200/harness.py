@@ -73,10 +73,27 @@ class NetHarness:
         self._ck(f(self.h, _ptr(x), _ptr(y), x.shape[0], ctypes.byref(loss), ctypes.byref(acc)))
         return loss.value, acc.value
 
+    def train_fine(self, x, y):
+        """One step as zeroGrads / forward / backward / update instead of train_batch."""
+        x = np.ascontiguousarray(x, dtype=np.float32); y = np.ascontiguousarray(y, dtype=np.float32)
+        loss, acc = ctypes.c_float(), ctypes.c_float()
+        self._ck(self.L.ebh_train_fine(self.h, _ptr(x), _ptr(y), x.shape[0], ctypes.byref(loss), ctypes.byref(acc)))
+        return loss.value, acc.value
+
+    def save(self, path):
+        self._ck(self.L.ebh_save(self.h, os.fsencode(path)))
+
+    def load(self, path):
+        self._ck(self.L.ebh_load(self.h, os.fsencode(path)))
+
     def train_resident(self, steps):
         loss = ctypes.c_float()
         self._ck(self.L.ebh_train_resident(self.h, steps, ctypes.byref(loss)))
         return loss.value
+
+    def local_step(self):
+        """One step on the resident batch without cross-rank averaging."""
+        self._ck(self.L.ebh_local_step(self.h))
 
     def forward(self, x, classes):
         x = np.ascontiguousarray(x, dtype=np.float32)

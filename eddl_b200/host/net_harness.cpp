@@ -123,7 +123,7 @@ extern "C" {
 const char *ebh_last_error() { return g_err.c_str(); }
 
 // device < 0: CS_CPU(threads) ; device >= 0: CS_GPU with that single device (needs the -DcGPU build).
-// optimizer: "sgd" (the reference's SGD) or "sgd_fused" (eddl_b200::SGDFused, GPU build only).
+// optimizer: "sgd" / "adam" (the reference's classes) or "sgd_fused" / "adam_fused" (eddl_b200::SGDFused / AdamFused, GPU build only).
 // loss: "categorical_cross_entropy" | "softmax_cross_entropy".
 int ebh_create(const char *config, int hw, int classes, int device, int threads, const char *optimizer,
                float lr, float mu, const char *loss, int *out_handle) {
@@ -136,6 +136,7 @@ int ebh_create(const char *config, int hw, int classes, int device, int threads,
         else if (o == "adam") opt = adam(lr);
 #ifdef cGPU
         else if (o == "sgd_fused") opt = new eddl_b200::SGDFused(lr, mu);
+        else if (o == "adam_fused") opt = new eddl_b200::AdamFused(lr, 0.9f, 0.999f, 0.000001f);      // eddl::adam's defaults
 #endif
         else throw std::runtime_error("unknown optimizer '" + o + "'");
         CompServ *cs = nullptr;
@@ -239,6 +240,29 @@ int ebh_train_batch_nocopy(int id, float *x, float *y, int batch, float *loss, f
     });
 }
 
+// One training step through the fine-grained API instead of train_batch (src/net/net_api.cpp:266-298, 384-433, 762-783):
+// zeroGrads, forward, backward(target), update.  Reports the same loss / metric figures as ebh_train_batch.
+int ebh_train_fine(int id, const float *x, const float *y, int batch, float *loss, float *acc) {
+    return guarded([&] {
+        Handle *h = get(id);
+        ensure_xy(h, batch);
+        memcpy(h->x->ptr, x, h->x->size * sizeof(float));
+        memcpy(h->y->ptr, y, h->y->size * sizeof(float));
+        reset_loss(h->net);
+        set_mode(h->net, TRMODE);
+        zeroGrads(h->net);
+        forward(h->net, std::vector<Tensor *>{h->x});
+        backward(h->net, std::vector<Tensor *>{h->y});
+        update(h->net);
+        if (loss) *loss = get_losses(h->net)[0];
+        if (acc) *acc = get_metrics(h->net)[0];
+    });
+}
+
+// Net::save / Net::load (src/net/net.cpp:411-449), "bin" format.
+int ebh_save(int id, const char *path) { return guarded([&] { save(get(id)->net, path, "bin"); }); }
+int ebh_load(int id, const char *path) { return guarded([&] { load(get(id)->net, path, "bin"); }); }
+
 // `steps` training steps on the batch already resident in the replica (set by the last
 // ebh_train_batch): the body of train_batch_t (src/net/net_api.cpp:39-53) without the
 // host->device copy of inputs.  Returns the last step's summed loss.
@@ -254,6 +278,16 @@ int ebh_train_resident(int id, int steps, float *loss_sum) {
 #endif
         }
         if (loss_sum) *loss_sum = rep->fiterr[0];
+    });
+}
+
+// One step of the body of train_batch_t on the resident batch WITHOUT the cross-rank averaging that
+// ebh_train_resident applies: afterwards the replicas of different ranks differ (used to check the averaging).
+int ebh_local_step(int id) {
+    return guarded([&] {
+        Net *rep = get(id)->net->snets[0];
+        rep->do_reset(); rep->do_reset_grads(); rep->do_forward(); rep->do_compute_loss();
+        rep->do_delta(); rep->do_backward(); rep->do_applygrads();
     });
 }
 

@@ -56,39 +56,45 @@ def _timed(L, dev, fn, iters, flush):
     return float(np.median(ms_all)), float(min(ms_all))
 
 
-def run_conv(args):
-    from . import capi
-    L = capi.lib(); dev = 0
-    L.call("init", dev)
+def conv_bench(L, dev, shapes, precision=0, iters=5, only=None, batch_scale=1.0):
+    """Yields one record per (shape, pass): CUDA-event time with a flushed L2, TFLOP/s from the real FLOP count."""
     flush = L.empty((64 << 20,), dev)
     rng = np.random.default_rng(0)
-    for o in args.opt:
-        k_, v_ = o.split("=")
-        L.call("set_option", k_.encode(), int(v_))
-    table = RESNET_SHAPES if args.set == "resnet" else CONV_SHAPES
-    shapes = table if args.shape < 0 else [table[args.shape]]
     for (n, c, h, w, k, kr, kc, st, pad) in shapes:
-        n = max(1, int(round(n * args.batch_scale)))
+        n = max(1, int(round(n * batch_scale)))
         oh = (h + 2 * pad - kr) // st + 1; ow = (w + 2 * pad - kc) // st + 1
         x = L.to_device(rng.standard_normal((n, c, h, w), dtype=np.float32), dev)
         wt = L.to_device(rng.standard_normal((k, c, kr, kc), dtype=np.float32), dev)
         dy = L.to_device(rng.standard_normal((n, k, oh, ow), dtype=np.float32), dev)
         y, gw, dx = L.empty((n, k, oh, ow), dev), L.zeros((k, c, kr, kc), dev), L.zeros((n, c, h, w), dev)
-        geo = (n, c, h, w, k, kr, kc, oh, ow, st, st, pad, pad, args.precision)
+        geo = (n, c, h, w, k, kr, kc, oh, ow, st, st, pad, pad, precision)
         flops = 2.0 * n * k * c * kr * kc * oh * ow
         nbytes = 4.0 * (n * c * h * w + k * c * kr * kc + n * k * oh * ow)     # each tensor once
         passes = {"fwd": lambda: L.call("conv2d_fwd", dev, x, wt, None, y, *geo),
                   "bwd_data": lambda: L.call("conv2d_bwd_data", dev, dy, wt, dx, *geo),
                   "bwd_weight": lambda: L.call("conv2d_bwd_weight", dev, x, dy, gw, None, *geo)}
         for name, fn in passes.items():
-            if args.only and name != args.only:
+            if only and name != only:
                 continue
             fn(); fn(); fn(); L.sync(dev)
-            med, best = _timed(L, dev, fn, args.iters, flush)
-            print(json.dumps({"bench": "conv", "pass": name, "shape": {"n": n, "c": c, "h": h, "w": w, "k": k, "kr": kr, "kc": kc, "stride": st, "pad": pad},
-                              "precision": {0: "3xTF32", 1: "TF32", 2: "TF32+bf16 cross terms"}[args.precision], "gflop": flops / 1e9, "ms": med, "ms_best": best,
-                              "tflops": flops / (med * 1e-3) / 1e12, "GB/s_each_tensor_once": nbytes / (med * 1e-3) / 1e9}), flush=True)
+            med, best = _timed(L, dev, fn, iters, flush)
+            yield {"bench": "conv", "pass": name, "shape": {"n": n, "c": c, "h": h, "w": w, "k": k, "kr": kr, "kc": kc, "stride": st, "pad": pad},
+                   "precision": {0: "3xTF32", 1: "TF32", 2: "TF32+bf16 cross terms"}[precision], "gflop": flops / 1e9, "ms": med, "ms_best": best,
+                   "tflops": flops / (med * 1e-3) / 1e12, "GB/s_each_tensor_once": nbytes / (med * 1e-3) / 1e9}
         L.sync(dev)
+
+
+def run_conv(args):
+    from . import capi
+    L = capi.lib(); dev = 0
+    L.call("init", dev)
+    for o in args.opt:
+        k_, v_ = o.split("=")
+        L.call("set_option", k_.encode(), int(v_))
+    table = RESNET_SHAPES if args.set == "resnet" else CONV_SHAPES
+    shapes = table if args.shape < 0 else [table[args.shape]]
+    for rec in conv_bench(L, dev, shapes, args.precision, args.iters, args.only, args.batch_scale):
+        print(json.dumps(rec), flush=True)
 
 
 def run_hbm(args):
@@ -145,26 +151,18 @@ def run_hbm(args):
     report("sgd_momentum", [nparam], 20 * nparam, lambda: L.call("sgd_momentum", dev, p_, g_, m_, 0.1, 0.9, nparam))
 
 
-def run_allreduce(args):
-    import torch  # noqa: F401  first: the process-wide libnccl.so.2 must be the one torch was built against
-    from . import capi, dist as ebd
-    rank, world, local = ebd.rendezvous("gloo")
-    L = capi.lib()
-    L.call("init", local)
-    if world > 1:
-        def make_id():
-            buf = ctypes.create_string_buffer(128); L.call("comm_unique_id", buf); return buf.raw
-        uid = ebd.share_unique_id(make_id)
-        L.call("comm_init_rank", local, world, rank, uid)
+def allreduce_bench(L, ebd, local, rank, world, max_floats=1 << 28):
+    """Parameter averaging over the communicator already set up on `local`: for 1 KB ... 4*max_floats bytes (powers of 4) a
+    correctness record (against the fp32 rank-order sum times 1.0f/N, the arithmetic of Net::sync_weights) and a timing
+    record per mode.  Every rank must run it; records are meaningful on rank 0."""
     size = 256
-    while size <= (1 << 28):
+    while size <= max_floats:
         rng = np.random.default_rng(1234 + rank)
         host = rng.standard_normal(size, dtype=np.float32)
         buf = L.to_device(host, local)
         p_, m_ = L.zeros((size,), local), L.zeros((size,), local)
         if size <= (1 << 24):
-            # correctness: every rank can regenerate every rank's buffer; the result must equal the fp32
-            # rank-order sum times 1.0f/N (the arithmetic of Net::sync_weights) within rel 1e-6
+            # every rank can regenerate every rank's buffer
             reps = [np.random.default_rng(1234 + r).standard_normal(size, dtype=np.float32) for r in range(world)]
             want = ebd.average_replicas_host(reps)
             chk = L.to_device(host, local)
@@ -174,11 +172,10 @@ def run_allreduce(args):
             pc, gc, mc = L.to_device(reps[0] * 0 + 1.0, local), L.to_device(host, local), L.zeros((size,), local)
             L.call("avg_grad_sgd", local, pc, gc, mc, 0.1, 0.9, size)
             m_want = (np.float32(0.1) * want).astype(np.float32)
-            err2 = float(np.max(np.abs(pc.numpy() - (np.float32(1.0) - m_want))) )
+            err2 = float(np.max(np.abs(pc.numpy() - (np.float32(1.0) - m_want))))
             worst = ebd.max_over_ranks(max(err, err2))
-            if rank == 0:
-                print(json.dumps({"bench": "allreduce_check", "ranks": world, "floats": size, "max_rel_err_weight_avg": err,
-                                  "max_abs_err_fused_sgd": err2, "worst_over_ranks": worst, "ok": bool(worst <= 1e-6)}), flush=True)
+            yield {"bench": "allreduce_check", "ranks": world, "floats": size, "max_rel_err_weight_avg": err,
+                   "max_abs_err_fused_sgd": err2, "worst_over_ranks": worst, "ok": bool(worst <= 1e-6)}
         for mode, fn in (("weight_avg", lambda: L.call("allreduce_avg", local, buf, size)),
                          ("grad_avg_sgd", lambda: L.call("avg_grad_sgd", local, p_, buf, m_, 0.1, 0.9, size))):
             for _ in range(3):
@@ -191,11 +188,27 @@ def run_allreduce(args):
             L.call("timer_stop", local, 3)
             ms = ctypes.c_float(); L.call("timer_elapsed_ms", local, 3, ctypes.byref(ms))
             t = ebd.max_over_ranks(ms.value / iters) * 1e-3
-            if rank == 0:
-                alg = size * 4 / t / 1e9
-                print(json.dumps({"bench": "allreduce", "mode": mode, "ranks": world, "bytes": size * 4, "us": t * 1e6, "algbw_GB/s": alg,
-                                  "busbw_GB/s": alg * 2 * (world - 1) / world if world > 1 else 0.0}), flush=True)
+            alg = size * 4 / t / 1e9
+            yield {"bench": "allreduce", "mode": mode, "ranks": world, "bytes": size * 4, "us": t * 1e6, "algbw_GB/s": alg,
+                   "busbw_GB/s": alg * 2 * (world - 1) / world if world > 1 else 0.0,
+                   "frac_of_900_GB/s": (alg * 2 * (world - 1) / world / 900.0) if world > 1 else 0.0}
         size *= 4
+
+
+def run_allreduce(args):
+    import torch  # noqa: F401  first: the process-wide libnccl.so.2 must be the one torch was built against
+    from . import capi, dist as ebd
+    rank, world, local = ebd.rendezvous("gloo")
+    L = capi.lib()
+    L.call("init", local)
+    if world > 1:
+        def make_id():
+            buf = ctypes.create_string_buffer(128); L.call("comm_unique_id", buf); return buf.raw
+        uid = ebd.share_unique_id(make_id)
+        L.call("comm_init_rank", local, world, rank, uid)
+    for rec in allreduce_bench(L, ebd, local, rank, world):
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
     if world > 1:
         L.call("comm_destroy", local)
 

@@ -101,4 +101,42 @@ void SGDFused::applygrads(int batch) {
     ok(eddlb200_sgd_momentum_multi(dev, p.data(), g.data(), m.data(), sizes.data(), (int)p.size(), lr, mu), "SGDFused::applygrads");
 }
 
+AdamFused::AdamFused(float lr, float beta_1, float beta_2, float epsilon, float weight_decay, bool amsgrad)
+    : Adam(lr, beta_1, beta_2, epsilon, weight_decay, amsgrad) {}
+
+Optimizer *AdamFused::clone() { AdamFused *n = new AdamFused(lr, beta_1, beta_2, epsilon, weight_decay, amsgrad); n->clip_val = clip_val; return n; }
+Optimizer *AdamFused::share() {
+    AdamFused *n = new AdamFused(lr, beta_1, beta_2, epsilon, weight_decay, amsgrad);
+    n->orig = this; n->isshared = true; n->clip_val = clip_val;
+    return n;
+}
+
+void AdamFused::applygrads(int batch) {
+    if (isshared) { orig->applygrads(batch); return; }
+    bool on_gpu = !layers.empty();
+    for (Layer *l : layers) for (Tensor *t : l->params) if (!t->isGPU()) on_gpu = false;
+    bool accumulates = false;
+    for (Layer *l : layers) if (!l->acc_gradients.empty()) accumulates = true;
+    if (!on_gpu || accumulates) { Adam::applygrads(batch); return; }
+    clip();
+    t++;
+    std::vector<float *> p, g, m, v; std::vector<size_t> sizes;
+    int dev = -1, q = 0;
+    for (size_t i = 0; i < layers.size(); i++) {
+        const int ntr = layers[i]->get_trainable_params_count();
+        if (layers[i]->trainable)
+            for (int j = 0; j < ntr; j++) {
+                Tensor *pt = layers[i]->params[j];
+                if (dev < 0) dev = pt->gpu_device;
+                p.push_back(pt->ptr); g.push_back(layers[i]->gradients[j]->ptr); m.push_back(mT[q + j]->ptr); v.push_back(vT[q + j]->ptr);
+                sizes.push_back(pt->size);
+            }
+        q += ntr;
+    }
+    if (p.empty()) return;
+    eddlb200_shim_flush(dev);
+    ok(eddlb200_adam_multi(dev, p.data(), g.data(), m.data(), v.data(), sizes.data(), (int)p.size(), lr, beta_1, beta_2, epsilon, t),
+       "AdamFused::applygrads");
+}
+
 }  // namespace eddl_b200

@@ -115,14 +115,27 @@ void gpu_delete_tensor(int dev, float *p) { flush(dev); ok(eddlb200_free(dev, p)
 void gpu_delete_tensor_int(int dev, int *p) { flush(dev); ok(eddlb200_free(dev, p), "gpu_delete_tensor_int"); }
 
 // ---- copies / fills ---------------------------------------------------------------------
-void gpu_copy_to_gpu(float *nptr, Tensor *B) { ok(eddlb200_memcpy_h2d(dev_of(B), B->ptr, nptr, B->size * sizeof(float)), "gpu_copy_to_gpu"); }
+// Host -> device copies go through the library's pinned staging ring, so that Net::train_batch's per-step copies of inputs
+// and targets (src/net/net_api.cpp:1273-1283; blocking cudaMemcpy in the reference, gpu_core.cu:49-53) neither wait for the
+// previous step's kernels nor keep the GPU idle while they run.  EDDL_B200_STAGED_H2D=0 restores the blocking copy.
+namespace {
+bool staged_h2d() {
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("EDDL_B200_STAGED_H2D"); v = (e && e[0] == '0') ? 0 : 1; }
+    return v == 1;
+}
+}
+void gpu_copy_to_gpu(float *nptr, Tensor *B) {
+    const int dev = dev_of(B);
+    if (staged_h2d()) ok(eddlb200_memcpy_h2d_staged(dev, B->ptr, nptr, B->size * sizeof(float)), "gpu_copy_to_gpu");
+    else ok(eddlb200_memcpy_h2d(dev, B->ptr, nptr, B->size * sizeof(float)), "gpu_copy_to_gpu");
+}
 void gpu_copy_from_gpu(Tensor *A, float *nptr) { ok(eddlb200_memcpy_d2h(dev_of(A), nptr, A->ptr, A->size * sizeof(float)), "gpu_copy_from_gpu"); }
 void gpu_copy_gpu(Tensor *A, Tensor *B) {
     if (A->gpu_device != B->gpu_device) {
-        // peer copy between two replicas: stage through the host like Net::sync_weights does
-        std::vector<float> tmp(A->size);
-        ok(eddlb200_memcpy_d2h(dev_of(A), tmp.data(), A->ptr, A->size * sizeof(float)), "gpu_copy_gpu");
-        ok(eddlb200_memcpy_h2d(dev_of(B), B->ptr, tmp.data(), B->size * sizeof(float)), "gpu_copy_gpu");
+        // two replicas of one process (CS_GPU({1,1,...})): a direct peer copy instead of the host round trip
+        const int src = dev_of(A), dst = dev_of(B);
+        ok(eddlb200_memcpy_peer(dst, B->ptr, src, A->ptr, A->size * sizeof(float)), "gpu_copy_gpu");
         return;
     }
     ok(eddlb200_memcpy_d2d(dev_of(A), B->ptr, A->ptr, A->size * sizeof(float)), "gpu_copy_gpu");

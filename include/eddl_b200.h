@@ -43,11 +43,22 @@ int eddlb200_free(int dev, void *p);
 int eddlb200_memcpy_h2d(int dev, void *dst, const void *src, size_t bytes);  /* blocking */
 int eddlb200_memcpy_d2h(int dev, void *dst, const void *src, size_t bytes);  /* blocking */
 int eddlb200_memcpy_d2d(int dev, void *dst, const void *src, size_t bytes);
+/* Copy between two devices of this process (gpu_copy_gpu with tensors on different devices: the single-process
+ * multi-GPU path of Net::sync_weights / Net::load, src/net/net_func.cpp:111-127).  A direct peer copy over NVLink,
+ * ordered after the work already enqueued on both devices' streams and before what is enqueued on either afterwards. */
+int eddlb200_memcpy_peer(int dst_dev, void *dst, int src_dev, const void *src, size_t bytes);
 /* Pinned-host staged copies for a caller that overlaps transfers itself
  * (Net::train_batch does blocking copies: src/net/net_api.cpp:1269-1285). */
 int eddlb200_host_alloc(size_t bytes, void **out);
 int eddlb200_host_free(void *p);
 int eddlb200_memcpy_h2d_async(int dev, void *dst, const void *src, size_t bytes);
+/* Host->device copy from ordinary (pageable) host memory that does not wait for the GPU: the bytes are copied into a
+ * pinned staging buffer of the library (the call returns as soon as `src` may be reused), travel to a device staging
+ * buffer on a separate copy stream while the compute stream keeps working, and a device-side copy ordered on the compute
+ * stream delivers them to `dst`.  A ring of four staging pairs, grown to the largest copy seen; a call waits only when
+ * the pair it is about to reuse has not been delivered yet.  This is how the drop-in's gpu_copy_to_gpu feeds
+ * Net::train_batch's per-step input and target copies (src/net/net_api.cpp:1273-1283). */
+int eddlb200_memcpy_h2d_staged(int dev, void *dst, const void *src, size_t bytes);
 int eddlb200_stream(int dev, void **cuda_stream);
 int eddlb200_sync(int dev);                                  /* blocking */
 int eddlb200_mem_info(int dev, size_t *in_use, size_t *cached);
@@ -100,10 +111,15 @@ int eddlb200_softmax_bwd_nd(int dev, const float *d, const float *s, float *pd, 
 
 /* ---- losses / metrics (src/hardware/gpu/nn/gpu_losses.cu:49-92, gpu_metrics.cu:26-49;
  *      src/hardware/cpu/nn/cpu_losses.cpp:29-57, cpu_metrics.cpp:17-29) */
-/* value = -sum_rows sum_cols y*logf(p + 1e-7)   (a SUM over the batch). Blocking. */
+/* value = -sum_rows sum_cols y*logf(p + 1e-7)   (a SUM over the batch).
+ * Net::train_batch asks for the loss and the metric of the same (target, prediction) pair twice per step
+ * (src/net/net_func.cpp:78-90, called from net_api.cpp:46 and :1300): the first of these calls computes BOTH scalars and
+ * reads them back with one blocking copy; eddlb200_cce_value / eddlb200_accuracy calls that follow with the same pointers
+ * and shape return the remembered values without touching the GPU, until an entry point of this library writes either
+ * tensor.  Values are those a fresh evaluation would give. */
 int eddlb200_cce_value(int dev, const float *y_true, const float *y_pred, int rows, int cols, float *host_out);
 int eddlb200_cce_delta(int dev, const float *y_true, const float *y_pred, float *delta, size_t n);
-/* rows whose argmax(y_true) == argmax(y_pred), first maximum wins. Blocking. */
+/* rows whose argmax(y_true) == argmax(y_pred), first maximum wins.  Blocking unless remembered (see above). */
 int eddlb200_accuracy(int dev, const float *y_true, const float *y_pred, int rows, int cols, int *host_out);
 
 /* ---- batch normalisation (src/hardware/gpu/nn/gpu_bn.cu:65-117;
@@ -125,12 +141,18 @@ int eddlb200_bn_fwd(int dev, int b, int z, int rc,
  * inside the library image, and the work is enqueued on the caller's `cuda_stream` (a cudaStream_t; null is
  * the default stream).  Intended for hosts whose device memory is wholly owned by another allocator, or
  * that cannot accept the device-wide synchronisation cudaMalloc / cudaFree imply.  Limits and rules:
- *   - channels x slices must not exceed 262144 (slices <= 64 per channel, chosen from the shape; any
- *     z <= 4096 fits); larger shapes return EDDLB200_ELIMIT;
+ *   - in training mode channels x slices must not exceed 262144, else EDDLB200_ELIMIT.  The slice count (1..256 per
+ *     channel) follows from the shape and from the "bn_waves" / "bn_min_items" options in force at the call: channels x
+ *     slices stays below 1184 x bn_waves + z, so with the defaults every z up to 243200 fits.  Inference mode
+ *     (trmode = 0) uses no partial sums and has no such limit;
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress): make
  *     that call before any stream capture starts;
- *   - all calls on a device share the array; calls that overlap on the GPU race on it, so order them.
- * Results are identical to eddlb200_bn_fwd (same kernels, same slicing). */
+ *   - all calls on a device share the array; calls that overlap on the GPU race on it, so order them;
+ *   - if the library's device context exists (eddlb200_init or any other entry point was used on `dev`), work that it
+ *     still owes -- deferred zero fills, a recorded first term of a sum -- is settled on the LIBRARY's compute stream
+ *     first, and a different `cuda_stream` is then made to wait for that stream, so these kernels see every buffer as
+ *     the earlier library calls left it.  Ordering work that follows on other streams after this call is the caller's job.
+ * Results are identical to eddlb200_bn_fwd called with the same options (same kernels, same slicing). */
 int eddlb200_bn_fwd_noalloc(int dev, int b, int z, int rc,
                             const float *input, float *output, float *opa,
                             float *global_mean, float *global_variance,
@@ -223,6 +245,11 @@ int eddlb200_sgd_momentum_multi(int dev, float *const *p, const float *const *g,
  * p -= lr * (m/(1-b1^t)) / sqrt(v/(1-b2^t) + eps)      (eps inside the sqrt) */
 int eddlb200_adam(int dev, float *p, float *g, float *m, float *v,
                   float lr, float beta1, float beta2, float eps, int t, size_t n);
+/* Multi-tensor form of the same step (Adam::applygrads walks every trainable tensor with ten launches each:
+ * src/optimizers/optim_adam.cpp:85-120): ntensors quadruples (p[i], g[i], m[i], v[i]) of sizes[i] floats, one launch,
+ * every tensor bit-identical to eddlb200_adam. */
+int eddlb200_adam_multi(int dev, float *const *p, float *const *g, float *const *m, float *const *v,
+                        const size_t *sizes, int ntensors, float lr, float beta1, float beta2, float eps, int t);
 
 /* ---- cross-replica averaging (replaces Net::sync_weights, src/net/net_func.cpp:111-127:
  *      acc = sum over replicas in fp32, acc *= 1.0f/N, every replica receives acc).

@@ -40,4 +40,16 @@ public:
     void applygrads(int batch) override;
 };
 
+// Adam whose applygrads is ONE multi-tensor kernel launch instead of ten elementwise launches per parameter tensor
+// (src/optimizers/optim_adam.cpp:85-120).  Parameters, both moment tensors and the squared gradient the reference leaves
+// in the gradient tensor are bit-identical to Adam::applygrads; its two scratch tensors (mCap, vCap) are not written.
+class AdamFused : public Adam {
+public:
+    explicit AdamFused(float lr = 0.01f, float beta_1 = 0.9f, float beta_2 = 0.999f, float epsilon = 1e-8f, float weight_decay = 0.0f,
+                       bool amsgrad = false);
+    Optimizer *clone() override;
+    Optimizer *share() override;
+    void applygrads(int batch) override;
+};
+
 }  // namespace eddl_b200

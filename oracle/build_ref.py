@@ -1,91 +1,27 @@
-"""TEST INFRASTRUCTURE ONLY: compile the reference's own host sources in place.
+"""TEST INFRASTRUCTURE ONLY: the reference's own CPU implementation as a shared library.
 
-Compiles the EDDL v1.1 C++ sources where they lie (the directory
-``$EDDL_REFERENCE`` names) with plain g++ -- the reference's CMake superbuild needs
-network access and Eigen, so it is not used -- into objects under a git-ignored
-``_ref`` directory.  Two flavours:
-
-* ``cpu``  : no ``-DcGPU``; linked with ``oracle/ref_capi.cpp`` into
-  ``oracle/_ref/libeddl_ref_cpu.so``.  This is the parity checker (the
-  reference's ``cpu_*`` functions and its ``Net`` driven on ``CS_CPU``) and the
-  timed CPU baseline.
-* ``gpu_host`` : ``-DcGPU`` (never ``-DcCUDNN``: cuDNN calls are inlined in the
-  layer code and would bypass the ``gpu_*`` boundary); objects only, under
-  ``baseline/_ref/obj_gpu``.  ``eddl_b200/build.py`` links them with the B200
-  backend so the reference's ``Net`` runs on ``CS_GPU`` unmodified.
-
-Eigen 3.4.0 (cmake/eigen.CMakeLists.txt.in:8) is replaced by the stand-in header
-in ``oracle/eigen_standin``.  Excluded sources: FPGA backend, the socket
-"distributed" draft, the reference's own CUDA backend (``src/hardware/gpu``),
-and the generated protobuf file (ONNX compiles to stubs without ``-DcPROTO``).
-No ``-Ofast/-ffast-math`` (the reference disables them for correctness runs,
-CMakeLists.txt:14,189-198).
+Links the EDDL v1.1 host sources, compiled in place WITHOUT ``-DcGPU`` by the recipe in ``baseline/build_host.py``, with
+``oracle/ref_capi.cpp`` and the net harness into ``oracle/_ref/libeddl_ref_cpu.so``: the parity checker (the
+reference's ``cpu_*`` functions and its ``Net`` driven on ``CS_CPU``) and the timed CPU baseline.
 """
-import concurrent.futures as cf
 import os
 import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF = os.environ.get("EDDL_REFERENCE", "/root/reference")
-CUDA_INC = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
+sys.path.insert(0, os.path.join(ROOT, "baseline"))
+import build_host  # noqa: E402
 
-COMMON = ["-std=c++14", "-O2", "-fopenmp", "-fPIC", "-w", "-DEDDL_LINUX",
-          "-mavx2", "-mfma", "-ffp-contract=off",
-          "-I" + os.path.join(HERE, "eigen_standin"),
-          "-I" + os.path.join(REF, "include"), "-I" + os.path.join(REF, "src")]
-
-
-def reference_sources():
-    out = []
-    for d, _, fs in os.walk(os.path.join(REF, "src")):
-        for f in fs:
-            p = os.path.join(d, f)
-            if not f.endswith(".cpp"):
-                continue
-            rel = os.path.relpath(p, REF)
-            if ("hardware/fpga" in rel or "hardware/gpu" in rel or "distributed" in rel
-                    or "onnx.pb" in rel or "layers/fpga" in rel or rel.endswith("apis/fpga.cpp")):
-                continue
-            out.append(p)
-    return sorted(out)
-
-
-def _compile(args):
-    src, obj, flags = args
-    if os.path.exists(obj) and os.path.getmtime(obj) >= os.path.getmtime(src):
-        return None
-    os.makedirs(os.path.dirname(obj), exist_ok=True)
-    extra = ["-include", "stdexcept"]  # descriptor_reduce.cpp:100 relies on a transitive include
-    cmd = ["g++"] + flags + extra + ["-c", src, "-o", obj]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        return "FAILED %s\n%s" % (src, r.stderr[-3000:])
-    return None
-
-
-def compile_objects(objdir, flags, jobs=None):
-    srcs = reference_sources()
-    tasks = []
-    for s in srcs:
-        rel = os.path.relpath(s, os.path.join(REF, "src")).replace("/", "__")
-        tasks.append((s, os.path.join(objdir, rel[:-4] + ".o"), flags))
-    with cf.ThreadPoolExecutor(max_workers=jobs or os.cpu_count()) as ex:
-        errs = [e for e in ex.map(_compile, tasks) if e]
-    if errs:
-        raise RuntimeError("\n".join(errs[:5]))
-    return [t[1] for t in tasks]
-
-
-def have_reference():
-    return os.path.isdir(os.path.join(REF, "src"))
+REF = build_host.REF
+COMMON = build_host.COMMON
+have_reference = build_host.have_reference
 
 
 def build_cpu():
-    """oracle/_ref/libeddl_ref_cpu.so = reference CPU objects + oracle/ref_capi.cpp + oracle/net_harness.cpp."""
+    """oracle/_ref/libeddl_ref_cpu.so = reference CPU objects + oracle/ref_capi.cpp + the net harness."""
     outdir = os.path.join(HERE, "_ref")
-    objs = compile_objects(os.path.join(outdir, "obj_cpu"), COMMON)
+    objs = build_host.compile_objects(os.path.join(outdir, "obj_cpu"), COMMON)
     lib = os.path.join(outdir, "libeddl_ref_cpu.so")
     mine = [os.path.join(HERE, "ref_capi.cpp"), os.path.join(ROOT, "eddl_b200", "host", "net_harness.cpp")]
     newest = max(os.path.getmtime(p) for p in objs + mine)
@@ -96,17 +32,7 @@ def build_cpu():
     return lib
 
 
-def build_gpu_host_objects():
-    """baseline/_ref/obj_gpu/*.o : the reference host code compiled with -DcGPU."""
-    outdir = os.path.join(ROOT, "baseline", "_ref", "obj_gpu")
-    return compile_objects(outdir, COMMON + ["-DcGPU", "-I" + CUDA_INC])
-
-
 if __name__ == "__main__":
     if not have_reference():
         sys.exit("reference sources not found at " + REF)
-    what = sys.argv[1:] or ["cpu"]
-    if "cpu" in what:
-        print(build_cpu())
-    if "gpu_host" in what:
-        print(len(build_gpu_host_objects()), "objects")
+    print(build_cpu())

@@ -111,6 +111,66 @@ def conv2d_bwd_data(dy, w, x_shape, dx0=None, stride=(1, 1), padding=(0, 0, 0, 0
     return dx if dx0 is None else np.asarray(dx0, F) + dx
 
 
+def conv2d_samples(x, w, dy, stride, padding, count, seed):
+    """float64 values of `count` randomly chosen elements of each of the three conv results, for tensors too large to
+    evaluate whole on the host: returns {"y": (flat indices, values), "gw": ..., "dx": ...} with the same index
+    arithmetic as conv2d_fwd / conv2d_bwd_weight / conv2d_bwd_data above (cpu_conv.cpp:114-280)."""
+    x = np.asarray(x, F); w = np.asarray(w, F); dy = np.asarray(dy, F)
+    n, c, ih, iw = x.shape
+    k, _, kr, kc = w.shape
+    sr, sc = stride
+    oh, ow, pads = resolve(padding, ih, iw, kr, kc, sr, sc)
+    pt, pl = pads[0], pads[2]
+    rng = np.random.default_rng(seed)
+    x64 = None
+
+    def patch(img, p, q):          # [c, kr, kc] window of image `img` under output pixel (p, q), zero padded
+        out = np.zeros((c, kr, kc), np.float64)
+        y0, x0 = p * sr - pt, q * sc - pl
+        ya, yb, xa, xb = max(y0, 0), min(y0 + kr, ih), max(x0, 0), min(x0 + kc, iw)
+        if ya < yb and xa < xb:
+            out[:, ya - y0:yb - y0, xa - x0:xb - x0] = x[img, :, ya:yb, xa:xb]
+        return out
+
+    res = {}
+    idx = rng.integers(0, n * k * oh * ow, count)
+    vals = np.empty(count, np.float64)
+    for i, f in enumerate(idx):
+        img, kk, p, q = np.unravel_index(f, (n, k, oh, ow))
+        vals[i] = np.sum(patch(img, p, q) * w[kk].astype(np.float64))
+    res["y"] = (idx, vals)
+    idx = rng.integers(0, k * c * kr * kc, count)
+    vals = np.empty(count, np.float64)
+    for i, f in enumerate(idx):
+        kk, cc, r, s = np.unravel_index(f, (k, c, kr, kc))
+        # x[n, cc, p*sr + r - pt, q*sc + s - pl] over all (n, p, q) with the tap inside the image
+        p_lo = max(0, -(-(pt - r) // sr)); p_hi = min(oh, (ih - 1 + pt - r) // sr + 1)
+        q_lo = max(0, -(-(pl - s) // sc)); q_hi = min(ow, (iw - 1 + pl - s) // sc + 1)
+        if p_lo >= p_hi or q_lo >= q_hi:
+            vals[i] = 0.0
+            continue
+        xs = x[:, cc, p_lo * sr + r - pt:(p_hi - 1) * sr + r - pt + 1:sr, q_lo * sc + s - pl:(q_hi - 1) * sc + s - pl + 1:sc]
+        vals[i] = np.sum(xs.astype(np.float64) * dy[:, kk, p_lo:p_hi, q_lo:q_hi].astype(np.float64))
+    res["gw"] = (idx, vals)
+    idx = rng.integers(0, n * c * ih * iw, count)
+    vals = np.empty(count, np.float64)
+    for i, f in enumerate(idx):
+        img, cc, yy, xx = np.unravel_index(f, (n, c, ih, iw))
+        acc = 0.0
+        for r in range(kr):
+            pn = yy + pt - r
+            if pn % sr or not 0 <= pn // sr < oh:
+                continue
+            for s in range(kc):
+                qn = xx + pl - s
+                if qn % sc or not 0 <= qn // sc < ow:
+                    continue
+                acc += float(np.dot(dy[img, :, pn // sr, qn // sc].astype(np.float64), w[:, cc, r, s].astype(np.float64)))
+        vals[i] = acc
+    res["dx"] = (idx, vals)
+    return res
+
+
 # ---- pooling: src/hardware/cpu/nn/cpu_pool.cpp:74-145 (max), 226-304 (avg) ---------------------------
 def _windows(ih, iw, kr, kc, sr, sc, pads):
     pt, pb, pl, pr = pads

@@ -1,5 +1,5 @@
 """Regenerates the golden fixtures of this directory.  Needs the EDDL source tree
-(the directory ``$EDDL_REFERENCE`` names) and the reference CPU build
+(the directory ``$EDDL_REFERENCE`` names, or a checkout called ``reference`` beside this repository) and the reference CPU build
 (``python oracle/build_ref.py cpu``); the fixtures themselves are committed so that the tests run
 where neither is present.
 
@@ -21,7 +21,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("EDDL_REFERENCE", "/root/reference")
+REF = os.environ.get("EDDL_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
 sys.path.insert(0, ROOT)
 
 

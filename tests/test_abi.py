@@ -48,7 +48,8 @@ def test_product_code_never_touches_the_oracle():
         for f in fs:
             if f.endswith((".py", ".cpp", ".cu", ".cuh", ".h")):
                 t = open(os.path.join(d, f), errors="ignore").read()
-                if re.search(r"^\s*(from|import)\s+oracle|oracle/_ref|eddl_oracle", t, flags=re.M):
+                # no import of the oracle package, none of its modules by name (also not through a sys.path entry), no path into it
+                if re.search(r"^\s*(from|import)\s+oracle|oracle/_ref|eddl_oracle|build_ref|ref_capi|[\"']oracle[\"']|oracle/", t, flags=re.M):
                     bad.append(f)
     assert not bad, bad
 

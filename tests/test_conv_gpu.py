@@ -150,3 +150,40 @@ def test_conv_empty_batch_and_long_reduction(lib):
     x = rng.standard_normal((2, 1024, 6, 6)).astype(F); w = rng.standard_normal((32, 1024, 3, 3)).astype(F)
     got = run_conv(lib, x, w, None, None, None, None, None, (1, 1), (1, 1, 1, 1))
     assert relerr(got["y"], orc.conv2d_fwd(x, w, None, (1, 1), (1, 1, 1, 1))) <= 1e-5
+
+
+BENCH_SHAPES = [  # the four microbenchmark shapes at their full batch: n, c, h, w, k, kr, kc, stride, pads
+    (64, 256, 56, 56, 256, 3, 3, 1, (1, 1, 1, 1)),
+    (64, 1024, 14, 14, 256, 1, 1, 1, (0, 0, 0, 0)),
+    (64, 3, 224, 224, 64, 7, 7, 2, (3, 3, 3, 3)),
+    (32, 512, 7, 7, 512, 3, 3, 1, (1, 1, 1, 1)),
+]
+
+
+@pytest.mark.parametrize("shape", BENCH_SHAPES)
+def test_benchmark_shapes_at_full_batch(lib, shape):
+    """The shapes whose TFLOP/s are quoted, at the quoted size (they take split-K and persistent-tile routes the small
+    stand-ins do not): the tensor-core result of all three passes is compared on the FULL tensors with the exact-fp32 FMA
+    kernel (itself checked against the oracle above), and on 1000 sampled elements per tensor with a float64 evaluation
+    of the reference's index arithmetic.  Bound: 1e-5 of the largest magnitude."""
+    n, c, h, w, k, kr, kc, st, pads = shape
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal((n, c, h, w), dtype=F); wt = rng.standard_normal((k, c, kr, kc), dtype=F)
+    oh, ow, _ = orc.resolve(pads, h, w, kr, kc, st, st)
+    dy = rng.standard_normal((n, k, oh, ow), dtype=F)
+    try:
+        lib.call("set_option", b"conv_path", 1)
+        a = run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads)
+    finally:
+        lib.call("set_option", b"conv_path", 0)
+    b = run_conv(lib, x, wt, None, dy, None, None, None, (st, st), pads)
+    lib.call("sync", 0)
+    samples = orc.conv2d_samples(x, wt, dy, (st, st), pads, 1000, seed=43)
+    for key in ("y", "gw", "dx"):
+        scale = float(np.max(np.abs(a[key])))
+        full = float(np.max(np.abs(b[key].astype(np.float64) - a[key].astype(np.float64)))) / scale
+        idx, want = samples[key]
+        sampled = float(np.max(np.abs(b[key].ravel()[idx].astype(np.float64) - want))) / scale
+        print(key, "vs FMA path %.2e   vs float64 samples %.2e" % (full, sampled))
+        assert full <= 1e-5, (key, full)
+        assert sampled <= 1e-5, (key, sampled)

@@ -383,3 +383,70 @@ def test_fill_multi_and_profile_records(lib):
     lib.call("profile_read", 0, 7, ctypes.byref(calls), ctypes.byref(tot), ctypes.byref(work))
     assert calls.value == 3 and abs(tot.value - sum(ms[i] for i in range(3))) < 1e-9
     lib.call("profile_reset", 0)
+
+
+def test_adam_multi_tensor_equals_per_tensor(lib):
+    """One launch over ragged, unaligned and empty tensors; every tensor bit-identical to the restated ten-call chain of
+    Adam::applygrads (parameters, both moments, and the squared gradient left in the gradient tensor)."""
+    rng = np.random.default_rng(31)
+    sizes = [1, 3, 64, 1000, 16384, 16385, 70001, 0, 5]
+    ps, gs, ms = [rnd(rng, s) for s in sizes], [rnd(rng, s) for s in sizes], [rnd(rng, s) for s in sizes]
+    vs = [np.abs(rnd(rng, s)) for s in sizes]
+    dps, dgs, dms, dvs = ([dev(lib, a) for a in group] for group in (ps, gs, ms, vs))
+    arr = lambda ds: (ctypes.c_void_p * len(ds))(*[d.ptr.value for d in ds])
+    csz = (ctypes.c_size_t * len(sizes))(*sizes)
+    before = lib.launches()
+    lib.call("adam_multi", 0, arr(dps), arr(dgs), arr(dms), arr(dvs), csz, len(sizes), 0.01, 0.9, 0.999, 1e-6, 4)
+    assert lib.launches() - before == 1
+    for p, g, m, v, dp, dg, dm, dv in zip(ps, gs, ms, vs, dps, dgs, dms, dvs):
+        ap, ag, am, av = orc.adam_step(p, g, m, v, 0.01, 0.9, 0.999, 1e-6, 4)
+        np.testing.assert_array_equal(dp.numpy(), ap); np.testing.assert_array_equal(dg.numpy(), ag)
+        np.testing.assert_array_equal(dm.numpy(), am); np.testing.assert_array_equal(dv.numpy(), av)
+
+
+def test_loss_and_metric_are_read_back_once_per_pair(lib):
+    """The first request for the loss (or the metric) of a (target, prediction) pair computes both; repeats are answered
+    without a launch until either tensor is written through the library, and then give the new values."""
+    rng = np.random.default_rng(32)
+    rows, cols = 64, 1000
+    p = rng.random((rows, cols)).astype(F); p /= p.sum(axis=1, keepdims=True)
+    lab = rng.integers(0, cols, rows); y = np.eye(cols, dtype=F)[lab]
+    dy, dp = dev(lib, y), dev(lib, p)
+    loss, hits = ctypes.c_float(), ctypes.c_int()
+    lib.call("cce_value", 0, dy, dp, rows, cols, ctypes.byref(loss))
+    first = loss.value
+    assert abs(first - orc.cce_value(y, p)) <= 2e-6 * abs(first)
+    before = lib.launches()
+    lib.call("accuracy", 0, dy, dp, rows, cols, ctypes.byref(hits))
+    lib.call("cce_value", 0, dy, dp, rows, cols, ctypes.byref(loss))
+    lib.call("accuracy", 0, dy, dp, rows, cols, ctypes.byref(hits))
+    assert lib.launches() == before and loss.value == first and hits.value == orc.accuracy(y, p)
+    # a write to the prediction (here: through a copy) invalidates what was remembered
+    p2 = np.roll(p, 1, axis=1).copy()
+    lib.call("memcpy_h2d", 0, dp, p2.ctypes.data_as(ctypes.c_void_p), p2.nbytes)
+    lib.call("cce_value", 0, dy, dp, rows, cols, ctypes.byref(loss))
+    lib.call("accuracy", 0, dy, dp, rows, cols, ctypes.byref(hits))
+    assert lib.launches() > before
+    assert abs(loss.value - orc.cce_value(y, p2)) <= 2e-6 * abs(loss.value) and hits.value == orc.accuracy(y, p2)
+    # so does an in-place kernel on the target
+    lib.call("scale", 0, dy, dy, 2.0, rows * cols)
+    lib.call("cce_value", 0, dy, dp, rows, cols, ctypes.byref(loss))
+    assert abs(loss.value - orc.cce_value(2 * y, p2)) <= 2e-6 * abs(loss.value)
+
+
+def test_staged_host_to_device_copy_and_peer_copy(lib):
+    """Copies through the pinned staging ring deliver the bytes (more copies in a row than the ring has pairs, growing and
+    shrinking sizes, the source overwritten right after the call); a peer copy with both ends on one device is a plain copy."""
+    rng = np.random.default_rng(33)
+    keep = []
+    for n in (5, 300000, 17, 1 << 20, 3, 2500001, 64, 99999, 1):
+        src = rnd(rng, n); want = src.copy()
+        d = lib.empty((n,))
+        lib.call("memcpy_h2d_staged", 0, d, src.ctypes.data_as(ctypes.c_void_p), src.nbytes)
+        src[...] = -1.0                                     # the caller's buffer is free as soon as the call returns
+        keep.append((d, want))
+    for d, want in keep:
+        np.testing.assert_array_equal(d.numpy(), want)
+    a = dev(lib, rnd(rng, 4097)); b = lib.zeros((4097,))
+    lib.call("memcpy_peer", 0, b, 0, a, 4097 * 4)
+    np.testing.assert_array_equal(b.numpy(), a.numpy())

@@ -183,3 +183,18 @@ def test_reference_outputs_fixture_is_current(ref, refout):
     st, pt, pb, pl, pr, ub = [int(v) for v in r["conv_b_meta"]]
     y, _, _, _ = ref.conv2d(r["conv_b_x"], r["conv_b_w"], None, stride=(st, st), pads=(pt, pb, pl, pr))
     np.testing.assert_allclose(y, r["conv_b_y"], rtol=1e-6, atol=1e-6)
+
+
+def test_sampled_conv_evaluation_agrees_with_the_full_restatement():
+    """conv2d_samples (used on tensors too large for the host) follows the same index arithmetic as the full functions."""
+    rng = np.random.default_rng(0)
+    for (n, c, h, w, k, kr, kc, st, pads) in [(2, 3, 9, 8, 5, 3, 3, 1, (1, 1, 1, 1)), (3, 4, 11, 11, 6, 3, 3, 2, (1, 1, 1, 1)),
+                                                (2, 3, 14, 14, 4, 7, 7, 2, (3, 3, 3, 3)), (2, 5, 7, 9, 3, 2, 3, 1, (0, 1, 1, 1))]:
+        x = rng.standard_normal((n, c, h, w)).astype(np.float32); wt = rng.standard_normal((k, c, kr, kc)).astype(np.float32)
+        y = orc.conv2d_fwd(x, wt, None, (st, st), pads); dy = rng.standard_normal(y.shape).astype(np.float32)
+        gw, _ = orc.conv2d_bwd_weight(x, dy, None, None, (st, st), pads, (kr, kc))
+        dx = orc.conv2d_bwd_data(dy, wt, x.shape, None, (st, st), pads)
+        s = orc.conv2d_samples(x, wt, dy, (st, st), pads, 100, seed=1)
+        for key, full in (("y", y), ("gw", gw), ("dx", dx)):
+            idx, v = s[key]
+            np.testing.assert_allclose(full.ravel()[idx], v, rtol=0, atol=2e-6 * max(1.0, float(np.max(np.abs(full)))))

@@ -39,12 +39,12 @@ int set_error(int code, const char *fmt, ...);
 enum ProfKind { PROF_CONV_FWD = 0, PROF_CONV_BWD_DATA, PROF_CONV_BWD_WEIGHT, PROF_BN_FWD, PROF_BN_BWD,
                 PROF_ELEMENTWISE, PROF_POOL, PROF_GEMM, PROF_OPTIM, PROF_COMM, PROF_NKINDS };
 bool prof_enabled(DevCtx *c);
-void prof_begin(DevCtx *c, int kind, double work);
-void prof_end(DevCtx *c);
+int prof_begin(DevCtx *c, int kind, double work);        // returns the index of the record it opened
+void prof_end(DevCtx *c, int record);
 struct ProfScope {
-    DevCtx *c; bool on;
-    ProfScope(DevCtx *cx, int kind, double work) : c(cx), on(prof_enabled(cx)) { if (on) prof_begin(c, kind, work); }
-    ~ProfScope() { if (on) prof_end(c); }
+    DevCtx *c; bool on; int rec = -1;
+    ProfScope(DevCtx *cx, int kind, double work) : c(cx), on(prof_enabled(cx)) { if (on) rec = prof_begin(c, kind, work); }
+    ~ProfScope() { if (on) prof_end(c, rec); }      // scopes nest (a conv call that first writes owed zeros): each closes its own record
 };
 int cuda_status(cudaError_t e, const char *what);
 

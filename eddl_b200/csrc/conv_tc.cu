@@ -39,6 +39,7 @@
 // four whole rows; the tap-shifted x operand of larger filters keeps one lane per k.
 // Every wait on an mbarrier is bounded; on time-out the kernel records a status code, leaves
 // its loops, frees its tensor memory and returns.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <array>
 #include <map>
@@ -82,6 +83,13 @@ struct TcParams {
     int nmain;              // rotating hi*hi accumulators in use: 1 for short chains, NMAIN otherwise
     int pf_rows;            // > 0: warp 13 prefetches the A operand into L2, one line per pf_rows tile rows and k (0 = off)
     int *status;
+    // TMA-fed 1x1 stride-1 layers (ATMA kernels): the activation tensor and the output tensor as [image][channel][pixel]
+    // tensor maps with boxes of 32 pixels x 32 channels; a tile row is a pixel of a 32-pixel CHUNK of one image, so the row
+    // space is images x chunks_per_image x 32 (rows past the end of an image are zero on the way in and clipped on the way out)
+    int chunks_per_image, images;
+    int reduce_out;         // the output is added into (TMA reduce) instead of stored
+    alignas(64) CUtensorMap mapA;
+    alignas(64) CUtensorMap mapOut;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -98,15 +106,21 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2 s of SM clock and reports false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: gives up after ~2 s of SM clock, or as soon as another role of the CTA has given up (the abort flag), and
+// reports false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 256; i++) if (mbar_try(bar, parity)) return true;
-        if (clock64() - t0 > 4000000000LL) return false;
+        if (*abort_flag || clock64() - t0 > 4000000000LL) return false;
     }
+}
+// The same for a whole warp: every lane waits, and the warp leaves together if any lane gave up, so that no warp-wide
+// (.sync.aligned, shuffle) instruction that follows is reached by part of a warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -116,6 +130,24 @@ __device__ __forceinline__ void tma_bulk_g2s(uint32_t dst_smem, const void *src,
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// TMA tensor copy global -> shared: a [1][32 channels][32 pixels] box of a 3-D tensor map; coordinates may lie outside the
+// tensor (the missing elements arrive as zeros), x must be a multiple of 4 elements
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst_smem), "l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+// TMA tensor copy shared -> global (elements outside the tensor are dropped), plain store or fp32 add into global memory
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src_smem) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                 ::"l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(src_smem) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src_smem) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                 ::"l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(src_smem) : "memory");
+}
+__device__ __forceinline__ void tma_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tma_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void tma_wait_group() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -181,14 +213,22 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t k) {
     return row * 128u + ((((k >> 2) ^ row) & 7u) << 4) + ((k & 3u) << 2);
 }
 
-template <int BN_, bool SPLIT3>
+// Shared memory of a CTA.  Gather kernels: the operand ring only.  ATMA kernels add a ring of RAW_STAGES raw activation
+// tiles ([4 chunks][32 channels][32 pixels] fp32, written by TMA) in front of the converters and two 4 KB staging buffers
+// per epilogue warp behind them, and keep a shorter operand ring in exchange.
+template <int BN_, bool SPLIT3, bool ATMA = false>
 struct Layout {
     static constexpr int A_BYTES = BM * BK * 4;
     static constexpr int B_BYTES = BN_ * BK * 4;
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (SPLIT3 ? 2 : 1);
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 4 ? 4 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int TABLE_BYTES = 2 * (BM * 8 + BN_ * 4);     // backward-weight row tables, one copy per producer group
-    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + TABLE_BYTES + 256;
+    static constexpr int RAW_BYTES = BM * BK * 4;                  // one K-block of raw activations
+    static constexpr int RAW_STAGES = ATMA ? 4 : 0;
+    static constexpr int OUT_BYTES = ATMA ? 4 * 2 * 32 * 32 * 4 : 0;
+    // 227 KB per CTA minus the alignment slack and the barrier words; gather kernels keep their 200 KB ring
+    static constexpr int RING_BUDGET = ATMA ? 232448 - 1024 - 256 - RAW_STAGES * RAW_BYTES - OUT_BYTES : 200 * 1024;
+    static constexpr int STAGES = (RING_BUDGET / STAGE_BYTES) > 4 ? 4 : (RING_BUDGET / STAGE_BYTES);
+    static_assert(STAGES >= 2, "the operand ring needs two stages");
+    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + RAW_STAGES * RAW_BYTES + OUT_BYTES + 256;
 };
 
 // Persistent, warp-specialised kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the
@@ -204,21 +244,28 @@ struct Layout {
 // prepared once per call by pack_b_kernel.  WGRAD = true (backward-weight): A and B are gathered with one lane per k.
 // BGATHER (backward-weight of 1x1 stride-1 unpadded convolutions): both operands are contiguous along k = (n, p, q) inside an
 // image, so the producers gather BOTH with 16-byte loads -- eight lanes per 128-byte row, four rows per instruction -- and no TMA.
-template <int BN_, int PREC, bool WGRAD, bool BGATHER = false>
-__global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P) {
+// ATMA (forward / backward-data of 1x1 stride-1 unpadded convolutions whose planes are a multiple of 4 pixels): the
+// activation operand is not gathered from global memory.  Warp 13 issues TMA tensor copies of raw [32 channels x 32 pixels]
+// boxes into a ring that runs several K-blocks ahead (the gather's one-K-block-per-round-trip latency bound is gone), the
+// producer warps read their rows out of that ring instead of global memory, and the epilogue warps hand 32 x 32 output
+// blocks to TMA stores (or TMA fp32 adds) through shared memory instead of issuing one 128-byte store per column.
+template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, bool ATMA = false>
+__global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_constant__ TcParams P) {
     constexpr bool SPLIT3 = PREC != 1;                   // operands staged as hi / lo planes
     constexpr bool CROSS_BF16 = PREC == 2 && !WGRAD && !BGATHER;     // cross terms as one bf16 MMA chain
-    using L = Layout<BN_, SPLIT3>;
+    static_assert(!ATMA || (!WGRAD && !BGATHER), "the TMA-fed variant covers forward and backward-data");
+    using L = Layout<BN_, SPLIT3, ATMA>;
     constexpr int STAGES = L::STAGES;
+    constexpr int RAWS = L::RAW_STAGES;
     constexpr bool A_ROWMAJOR = !WGRAD;
     constexpr bool B_TMA = !WGRAD && !BGATHER;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *stage_base = smem;
-    int2 *sRowA = (int2 *)(smem + STAGES * L::STAGE_BYTES);          // backward-weight: row entries of the current tile
-    int *sRowB = (int *)(sRowA + 2 * BM);
-    uint64_t *bars = (uint64_t *)(sRowB + 2 * BN_);                      // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
-    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
+    uint8_t *raw_base = smem + STAGES * L::STAGE_BYTES;                       // ATMA: raw activation ring
+    uint8_t *out_base = raw_base + RAWS * L::RAW_BYTES;                       // ATMA: epilogue staging, 2 x 4 KB per warp
+    uint64_t *bars = (uint64_t *)(out_base + L::OUT_BYTES);    // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], raw_full[RAWS], raw_empty[RAWS]
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4 + 2 * RAWS);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     volatile int *progress = abort_flag + 1;              // last K-block (CTA sequence number) producer group 0 has stored
 
@@ -234,10 +281,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
 
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
     const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES), bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
+    const uint32_t bar_raw_full = smem_u32(bars + 2 * STAGES + 4), bar_raw_empty = smem_u32(bars + 2 * STAGES + 4 + RAWS);
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD / 64 + (B_TMA ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); }
         for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, NEPI / 32); }
+        // a raw tile is filled by one expect_tx arrival plus the TMA bytes, and released by the four warps of the group that read it
+        for (int s = 0; s < RAWS; s++) { mbar_init(bar_raw_full + 8 * s, 1); mbar_init(bar_raw_empty + 8 * s, 4); }
         *abort_flag = 0;
         *progress = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -317,7 +367,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             for (int g = group; t < total_tiles; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true; break; }
                 store(s);
                 fence_async_smem();
                 __syncwarp();
@@ -335,7 +385,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             int2 myRow = make_int2(0, INVALID_Y << 16);
             int ry = INVALID_Y, rx = 0, row_tile = -1;
 
-            auto load_row = [&](int t, int kb0, int it) {
+            auto load_row = [&](int t, int kb0, int it, int gseq) -> bool {
+                if constexpr (ATMA) {
+                    // this thread's row of K-block number gseq of the CTA's sequence: 32 values, one per channel, out of the raw
+                    // tile TMA has delivered (chunk = warp of the group, pixel = lane: conflict-free 128-byte reads)
+                    const int rs = gseq % RAWS;
+                    if (!mbar_wait_warp(bar_raw_full + 8 * rs, (gseq / RAWS) & 1, abort_flag)) return false;
+                    const float *raw = (const float *)(raw_base + rs * L::RAW_BYTES) + (warp & 3) * (BK * 32) + lane;
+#pragma unroll
+                    for (int i = 0; i < BK; i++) av[i] = raw[i * 32];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_raw_empty + 8 * rs);       // this warp has read its chunk
+                    return true;
+                }
                 const int mn = t % tiles_mn;
                 if (mn != row_tile) {
                     row_tile = mn;
@@ -374,6 +436,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                         av[i] = ok ? __ldg(base + ke.x) : 0.f;
                     }
                 }
+                return true;
             };
             auto store_row = [&](int s) {
                 uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
@@ -420,11 +483,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 }
             };
             settle();
-            if (t < total_tiles) load_row(t, kb0, it);
-            for (int g = group; t < total_tiles; g += 2) {
+            if (t < total_tiles && !load_row(t, kb0, it, group)) failed = true;
+            for (int g = group; t < total_tiles && !failed; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true; break; }
                 if (arow == 0) {
                     // packed weights of this K-block / filter tile: one bulk copy into the stage's B_hi|B_lo area
                     const int n_tile = (t % tiles_mn) / P.tiles_m;
@@ -439,15 +502,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);      // one arrive per warp: 32 lanes on one barrier word serialise
                 if (tid == 0) *progress = g;        // paces the prefetch warp
                 it += 2; settle();
-                if (t < total_tiles) load_row(t, kb0, it);
+                if (t < total_tiles && !load_row(t, kb0, it, g + 2)) failed = true;
             }
         } else {
             // backward-weight: one lane per k.  As above, two groups of four warps take alternate K-blocks; a warp gathers
-            // 32 A rows and BN/4 B rows of its group's block.  Each group keeps its own copy of the tile's row tables.
+            // 32 A rows and BN/4 B rows of its group's block.  A warp needs only ITS rows' table entries: lane r keeps entry r
+            // in registers and the gather loop broadcasts it with shuffles, so no warp waits on another one here.
             constexpr int RA = BM / 4, RB = BN_ / 4;
-            const int group = warp >> 2, wq = warp & 3, gtid = tid & 127;
-            int2 *rowsA = sRowA + group * BM;
-            int *rowsB = sRowB + group * BN_;
+            static_assert(RA == 32 && RB <= 32, "one table entry per lane");
+            const int group = warp >> 2, wq = warp & 3;
+            int2 myRowA = make_int2(0, INVALID_Y << 16);
+            int myRowB = -1;
             float av[RA], bv[BGATHER ? 1 : RB];
             // WGRAD with BGATHER: the dy operand (contiguous along k inside an image) is gathered with 16-byte loads, a
             // quarter warp per 128-byte row; the x operand (shifted by the filter taps) keeps one lane per k
@@ -458,13 +523,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             int row_tile = -1;
             auto load_tiles = [&](int mn, int kblock) {
                 if (mn != row_tile) {
-                    // new tile: refresh the group's row tables (all 128 threads of the group take this branch together)
+                    // new tile: refresh this warp's row entries (a warp-uniform branch)
                     row_tile = mn;
                     const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
-                    asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");      // nobody still reads the previous tile's tables
-                    rowsA[gtid] = (m0 + gtid < P.M_total) ? __ldg(P.rowA + m0 + gtid) : make_int2(0, INVALID_Y << 16);
-                    if (!BGATHER && gtid < BN_) rowsB[gtid] = (n0 + gtid < P.N_total) ? __ldg(P.rowB + n0 + gtid) : -1;
-                    asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
+                    const int ma = m0 + wq * RA + lane, nb = n0 + wq * RB + lane;
+                    myRowA = ma < P.M_total ? __ldg(P.rowA + ma) : make_int2(0, INVALID_Y << 16);
+                    if (!BGATHER) myRowB = (lane < RB && nb < P.N_total) ? __ldg(P.rowB + nb) : -1;
                     if constexpr (BGATHER) {
 #pragma unroll
                         for (int i = 0; i < BI; i++) { const int n = n0 + wq * RB + 4 * i + sub; offB[i] = n < P.N_total ? __ldg(P.rowB + n) : 0; }
@@ -476,7 +540,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                 const float *base = P.srcA + ke.x;
 #pragma unroll
                 for (int r = 0; r < RA; r++) {
-                    const int2 re = rowsA[wq * RA + r];
+                    const int2 re = make_int2(__shfl_sync(0xffffffffu, myRowA.x, r), __shfl_sync(0xffffffffu, myRowA.y, r));
                     const int y = (re.y >> 16) + ky, x = (int)(short)(re.y & 0xffff) + kx;
                     const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
                     av[r] = ok ? __ldg(base + re.x) : 0.f;
@@ -490,7 +554,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
 #pragma unroll
                     for (int r = 0; r < RB; r++) {
-                        const int ro = rowsB[wq * RB + r];
+                        const int ro = __shfl_sync(0xffffffffu, myRowB, r);
                         bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
                     }
                 }
@@ -542,7 +606,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             for (int g = group; t < total_tiles; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (*abort_flag || !mbar_wait(bar_empty + 8 * s, par)) { failed = true; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true; break; }
                 store_tiles(s);
                 fence_async_smem();
                 __syncwarp();
@@ -559,12 +623,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
             for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x, local++) {
                 int kb0, nkb; kb_range(t, kb0, nkb);
                 const int set = local % nsets;
-                if (*abort_flag || !mbar_wait(bar_acc_empty + 8 * set, ((local / nsets) & 1) ^ 1)) { failed = true; break; }
+                if (!mbar_wait(bar_acc_empty + 8 * set, ((local / nsets) & 1) ^ 1, abort_flag)) { failed = true; break; }
                 tc_fence_after();
                 const uint32_t set_base = tmem_base + (uint32_t)(set * set_cols);
                 for (int it = 0; it < nkb; it++, g++) {
                     const int s = g % STAGES;
-                    if (*abort_flag || !mbar_wait(bar_full + 8 * s, (g / STAGES) & 1)) { failed = true; break; }
+                    if (!mbar_wait(bar_full + 8 * s, (g / STAGES) & 1, abort_flag)) { failed = true; break; }
                     tc_fence_after();
                     const uint32_t a_hi = smem_u32(stage_base + s * L::STAGE_BYTES);
                     const uint32_t a_lo = a_hi + L::A_BYTES;
@@ -600,7 +664,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
         // PF_AHEAD blocks ahead of producer group 0 and touches one address per (pf_rows consecutive tile rows, k): the
         // rows are consecutive pixels, so that is every line the producers will read, and their loads then hit in L2.
         // Nothing waits on this warp; its own wait on the producers' progress is bounded and it simply stops on a time-out.
-        if constexpr (A_ROWMAJOR && B_TMA) {
+        if constexpr (ATMA) {
+            // ATMA: this warp's lane 0 feeds the raw activation ring: per K-block four boxes of [32 channels][32 pixels], one per
+            // 32-pixel chunk of the tile's rows (a chunk lies inside one image; what lies past the image, the channels or the
+            // batch arrives as zeros).  It runs RAWS K-blocks ahead of the producers across tile boundaries.
+            if (lane == 0) {
+                int g = 0;
+                for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
+                    int kb0, nkb; kb_range(t, kb0, nkb);
+                    const int cm0 = ((t % tiles_mn) % P.tiles_m) * (BM / 32);
+                    int xs[4], zs[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) { zs[j] = (cm0 + j) / P.chunks_per_image; xs[j] = ((cm0 + j) % P.chunks_per_image) * 32; }
+                    for (int it = 0; it < nkb; it++, g++) {
+                        const int rs = g % RAWS;
+                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((g / RAWS) & 1) ^ 1, abort_flag)) { failed = true; break; }
+                        mbar_expect_tx(bar_raw_full + 8 * rs, (uint32_t)L::RAW_BYTES);
+                        const uint32_t dst = smem_u32(raw_base + rs * L::RAW_BYTES);
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            tma_load_3d(dst + j * (BK * 32 * 4), &P.mapA, xs[j], (kb0 + it) * BK, zs[j], bar_raw_full + 8 * rs);
+                    }
+                }
+            }
+            __syncwarp();
+        } else if constexpr (A_ROWMAJOR && B_TMA) {
             if (P.pf_rows > 0) {
                 const int nr = (BM + P.pf_rows - 1) / P.pf_rows;          // <= 32
                 int g = 0;
@@ -614,12 +702,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     if (mrow >= P.M_total) mrow = P.M_total - 1;
                     const int roff = (lane <= nr && mrow >= m0) ? __ldg(P.rowA + mrow).x : -1;
                     for (int it = 0; it < nkb; it++, g++) {
-                        int spins = 0;
-                        while (g > *progress + PF_AHEAD) {
-                            if (*abort_flag || ++spins > (1 << 18)) { stop = true; break; }
-                            __nanosleep(128);
+                        // lane 0 paces the warp; its verdict is broadcast so that the shuffles below are reached by all lanes or none
+                        int give_up = 0;
+                        if (lane == 0) {
+                            int spins = 0;
+                            while (g > *progress + PF_AHEAD) {
+                                if (*abort_flag || ++spins > (1 << 18)) { give_up = 1; break; }
+                                __nanosleep(128);
+                            }
                         }
-                        if (stop) break;
+                        give_up = __shfl_sync(0xffffffffu, give_up, 0);
+                        if (give_up) { stop = true; break; }
                         const float *pk = P.srcA + __ldg(P.kC + (kb0 + it) * BK + lane);
                         for (int j = 0; j <= nr && j < 32; j++) {
                             const int ro = __shfl_sync(0xffffffffu, roff, j);
@@ -633,12 +726,66 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
         // ============================ epilogue (warps 9-12) ============================
         const int quarter = warp & 3;                     // the TMEM lane quarter this warp may access
         int local = 0;
+        int out_count = 0;                                // ATMA: output blocks this warp has handed to TMA
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, local++) {
             const int mn = t % tiles_mn, split = t / tiles_mn;
             const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
             const int set = local % nsets;
-            if (*abort_flag || !mbar_wait(bar_acc_full + 8 * set, (local / nsets) & 1)) { failed = true; break; }
+            if (!mbar_wait_warp(bar_acc_full + 8 * set, (local / nsets) & 1, abort_flag)) { failed = true; break; }
             tc_fence_after();
+            if constexpr (ATMA) {
+                // This warp's 32 rows are one 32-pixel chunk of one image.  Per 32 columns: drain the accumulators, write the
+                // [32 columns][32 pixels] block into one of the warp's two staging buffers (lane = pixel: conflict-free), and
+                // let TMA store it -- or add it -- into out[image][n0 + 32c ...][x0 ...]; pixels past the end of the image and
+                // columns past the last filter are dropped by the copy.
+                const int cm = m0 / 32 + quarter;
+                const int img = cm / P.chunks_per_image, x0 = (cm % P.chunks_per_image) * 32;
+                const uint32_t set_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(set * set_cols);
+                float *stage2 = (float *)(out_base + quarter * (2 * 32 * 32 * 4));
+#pragma unroll 1
+                for (int c = 0; c < (BN_ + 31) / 32; c++) {
+                    uint32_t r[32], tt[32];
+                    tmem_ld32(set_base + (uint32_t)(c * 32), r);
+#pragma unroll 1
+                    for (int a = 1; a < nacc; a++) {
+                        tmem_ld32(set_base + (uint32_t)(a * BN_ + c * 32), tt);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(tt[j])));
+                    }
+                    if (c == (BN_ + 31) / 32 - 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * set);
+                    }
+                    const int col0 = n0 + c * 32;
+                    if (col0 < P.N_total && img < P.images) {             // warp-uniform
+                        float *sb = stage2 + (out_count & 1) * (32 * 32);
+                        // the copy that used this buffer two blocks ago must have read it; the latest one may still be in flight
+                        if (lane == 0) tma_wait_group_read<1>();
+                        __syncwarp();
+                        if (P.bias) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                sb[j * 32 + lane] = __fadd_rn(__uint_as_float(r[j]), col0 + j < P.N_total ? __ldg(P.bias + col0 + j) : 0.f);
+                        } else if (P.add_zero) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) sb[j * 32 + lane] = __fadd_rn(0.f, __uint_as_float(r[j]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) sb[j * 32 + lane] = __uint_as_float(r[j]);
+                        }
+                        fence_async_smem();                 // generic-proxy stores -> visible to the copy engine
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (P.reduce_out) tma_reduce_add_3d(&P.mapOut, x0, col0, img, smem_u32(sb));
+                            else tma_store_3d(&P.mapOut, x0, col0, img, smem_u32(sb));
+                            tma_commit_group();
+                        }
+                        out_count++;
+                    }
+                }
+                continue;
+            }
             const int m = m0 + quarter * 32 + lane;
             const bool m_ok = m < P.M_total;
             float *obase = P.out + (long long)split * P.split_stride + (m_ok ? (long long)__ldg(P.outM + m) : 0);
@@ -724,6 +871,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const TcParams P)
                     }
                 }
             }
+        }
+        if constexpr (ATMA) {
+            // the staging buffers must outlive the copies that read them
+            if (lane == 0) tma_wait_group<0>();
+            __syncwarp();
         }
     }
     if (failed) { *abort_flag = 1; atomicExch(P.status, 1); }
@@ -976,13 +1128,20 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     // Split the reduction so that the persistent CTAs finish together: the makespan of `tiles * splits` work items dealt
     // round-robin to the SMs is ceil(items / SMs) rounds of (K-blocks per split + one epilogue); splitting also costs a
     // write and a read of every partial output.  Pick the split count with the smallest estimate (microseconds).
-    int splits = 1;
+    // The tensor core truncates when it adds into the accumulator, so a chain of accumulations drifts toward zero in
+    // proportion to its length (measured on backward-weight of N=64, 256 channels, 56x56: 2000 k-steps per accumulator
+    // gave 3e-5 of the largest gradient).  kMaxChainBlocks K-blocks per split keep every accumulator's chain at about
+    // 200 k-steps (a few 1e-6); the partial sums of the splits are added in fp32 with rounding.
+    constexpr int kMaxChainBlocks = 160;
     const int tiles = tiles_m * tiles_n;
+    const int sp_min = allow_split ? (kblocks + kMaxChainBlocks - 1) / kMaxChainBlocks : 1;
+    int splits = sp_min;
     if (allow_split && kblocks >= 8) {
         const double t_kblock = mode == 2 ? 2.5 : 1.0, t_epilogue = 3.0;
-        const int max_splits = kblocks / 4 < 128 ? kblocks / 4 : 128;
+        int max_splits = kblocks / 4 < 128 ? kblocks / 4 : 128;
+        if (max_splits < sp_min) max_splits = sp_min + sp_min / 4;
         double best = 1e30;
-        for (int sp = 1; sp <= max_splits; sp++) {
+        for (int sp = sp_min; sp <= max_splits; sp++) {
             const int kb = (kblocks + sp - 1) / sp;
             const int sp_eff = (kblocks + kb - 1) / kb;
             if (sp_eff != sp) continue;

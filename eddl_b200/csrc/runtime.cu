@@ -116,12 +116,15 @@ static cudaEvent_t prof_event(DevCtx *c) {
     if (!c->prof_pool.empty()) { cudaEvent_t e = c->prof_pool.back(); c->prof_pool.pop_back(); return e; }
     cudaEvent_t e; cudaEventCreate(&e); return e;
 }
-void prof_begin(DevCtx *c, int kind, double work) {
+int prof_begin(DevCtx *c, int kind, double work) {
     DevCtx::ProfRec r{kind, work, prof_event(c), prof_event(c)};
     cudaEventRecord(r.a, c->stream);
     c->prof_recs.push_back(r);
+    return (int)c->prof_recs.size() - 1;
 }
-void prof_end(DevCtx *c) { if (!c->prof_recs.empty()) cudaEventRecord(c->prof_recs.back().b, c->stream); }
+void prof_end(DevCtx *c, int record) {
+    if (record >= 0 && record < (int)c->prof_recs.size()) cudaEventRecord(c->prof_recs[record].b, c->stream);
+}
 
 void set_comm(DevCtx *c, ncclComm *comm, int nranks, int rank) { c->comm = comm; c->nranks = nranks; c->rank = rank; }
 int comm_rank(DevCtx *c) { return c->rank; }
@@ -483,6 +486,7 @@ int eddlb200_profile_read(int dev, int kind, unsigned long long *calls, double *
         if (r.kind != kind) continue;
         float t = 0.f;
         if (cudaEventElapsedTime(&t, r.a, r.b) == cudaSuccess) { ms += t; work += r.work; n++; }
+        else cudaGetLastError();       // a record that was never closed: do not leave the error for the next launch check
     }
     if (calls) *calls = n; if (total_ms) *total_ms = ms; if (total_work) *total_work = work;
     return 0;
@@ -497,7 +501,7 @@ int eddlb200_profile_records(int dev, int kind, double *ms, double *work, int ca
     for (auto &r : cx->prof_recs) {
         if (r.kind != kind) continue;
         float t = 0.f;
-        if (cudaEventElapsedTime(&t, r.a, r.b) != cudaSuccess) continue;
+        if (cudaEventElapsedTime(&t, r.a, r.b) != cudaSuccess) { cudaGetLastError(); continue; }
         if (n < capacity && ms && work) { ms[n] = t; work[n] = r.work; }
         n++;
     }

@@ -26,6 +26,16 @@ int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const flo
 
 // 1 (default): the tensor-core kernel's prefetch warp pulls the activation operand of 1x1 layers into L2 ahead of the gather.
 int conv_tc_set_prefetch(int on);
+// 2 (default): 1x1 stride-1 forward / backward-data layers are fed and drained by TMA tensor copies, accumulating outputs by
+// TMA fp32 adds; 1: only where the output is stored; 0: every layer takes the gather kernel.
+int conv_tc_set_tma(int level);
+// 1 (default): backward-weight of those layers has both operands copied by TMA into the operand ring; 2: in addition the landed
+// values serve as the hi plane unmasked; 0: the 16-byte gather.
+int conv_tc_set_tma_wgrad(int level);
+int conv_tc_set_ablate(int v);
+// 1 (default): packed weight images are kept per (weight tensor, tiling) and re-packed, all stale ones in one launch, only after
+// the tensor has been written; 0: every call packs its own.
+int conv_tc_set_pack_cache(int on);
 
 // Reads and clears the device's time-out flag of the tensor-core kernels (blocking).
 int conv_tc_status(int dev, cudaStream_t st, int *out);

@@ -44,6 +44,7 @@
 #include <array>
 #include <map>
 #include <mutex>
+#include <vector>
 #include "common.cuh"
 #include "conv_common.cuh"
 
@@ -55,7 +56,11 @@ constexpr int BM = 128;             // UMMA M (TMEM lanes)
 constexpr int BK = 32;              // fp32 per 128-byte swizzle row
 constexpr int NPROD = 256;          // producer threads (warps 0-7); warp 8 issues the MMAs; warps 9-12 run the epilogue
 constexpr int NEPI = 128;           // epilogue threads (warps 9-12)
-constexpr int NTHREADS = NPROD + 32 + NEPI + 32;     // + warp 13: L2 prefetch of the activation operand
+constexpr int NTHREADS = NPROD + 32 + NEPI + 32;     // + warp 13: L2 prefetch of the activation operand / TMA issue
+// TMA-fed forward / backward-data kernels run a second set of four epilogue warps (warps 14-17): their short-reduction,
+// output-heavy layers are bound by the epilogue's chain of tensor-memory reads, and two warps per lane quarter halve it
+constexpr int NTHREADS_ATMA = NTHREADS + NEPI;
+constexpr int threads_of(int tma) { return tma == 1 ? NTHREADS_ATMA : NTHREADS; }
 constexpr int PF_AHEAD = 8;         // K-blocks the prefetch warp may run ahead of the producers
 constexpr int INVALID_Y = -20000;
 constexpr int NMAIN = 3;             // rotating hi*hi accumulators; a fourth holds the cross terms
@@ -88,6 +93,8 @@ struct TcParams {
     // space is images x chunks_per_image x 32 (rows past the end of an image are zero on the way in and clipped on the way out)
     int chunks_per_image, images;
     int reduce_out;         // the output is added into (TMA reduce) instead of stored
+    int ablate;             // TEMP experiment switches
+    int raw_hi;             // WTMA: leave the landed fp32 values as the hi plane (the tensor core reads only their upper 19 bits)
     alignas(64) CUtensorMap mapA;
     alignas(64) CUtensorMap mapOut;
 };
@@ -223,12 +230,13 @@ struct Layout {
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (SPLIT3 ? 2 : 1);
     static constexpr int RAW_BYTES = BM * BK * 4;                  // one K-block of raw activations
     static constexpr int RAW_STAGES = ATMA ? 4 : 0;
-    static constexpr int OUT_BYTES = ATMA ? 4 * 2 * 32 * 32 * 4 : 0;
+    static constexpr int OUT_BYTES = ATMA ? 8 * 32 * 32 * 4 : 0;       // one 32 x 32 staging block per epilogue warp
     // 227 KB per CTA minus the alignment slack and the barrier words; gather kernels keep their 200 KB ring
     static constexpr int RING_BUDGET = ATMA ? 232448 - 1024 - 256 - RAW_STAGES * RAW_BYTES - OUT_BYTES : 200 * 1024;
     static constexpr int STAGES = (RING_BUDGET / STAGE_BYTES) > 4 ? 4 : (RING_BUDGET / STAGE_BYTES);
     static_assert(STAGES >= 2, "the operand ring needs two stages");
-    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + RAW_STAGES * RAW_BYTES + OUT_BYTES + 256;
+    static constexpr int TABLE_BYTES = ATMA ? 0 : 8 * 32 * 12;     // backward-weight: 32 row entries of A (8 bytes) and of B (4 bytes) per producer warp
+    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + RAW_STAGES * RAW_BYTES + OUT_BYTES + TABLE_BYTES + 256;
 };
 
 // Persistent, warp-specialised kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the
@@ -249,8 +257,14 @@ struct Layout {
 // boxes into a ring that runs several K-blocks ahead (the gather's one-K-block-per-round-trip latency bound is gone), the
 // producer warps read their rows out of that ring instead of global memory, and the epilogue warps hand 32 x 32 output
 // blocks to TMA stores (or TMA fp32 adds) through shared memory instead of issuing one 128-byte store per column.
-template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, bool ATMA = false>
-__global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_constant__ TcParams P) {
+// WTMA (TMA = 2: backward-weight of the same layers): both operands are [image][channel][pixel] tensors whose rows are
+// contiguous along k = (image, pixel), so warp 13 lets TMA write them straight into the operand ring in the K-major
+// SWIZZLE_128B layout the MMA reads (a K-block = 32 pixels of one image; pixels past the end of the image arrive as
+// zeros and add nothing), and the producer warps only split what has landed into its hi / lo planes, in place.
+template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, int TMA = 0>
+__global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __grid_constant__ TcParams P) {
+    constexpr bool ATMA = TMA == 1, WTMA = TMA == 2;
+    static_assert(!WTMA || (!WGRAD && BGATHER), "the TMA-fed backward-weight variant replaces the both-operands gather");
     constexpr bool SPLIT3 = PREC != 1;                   // operands staged as hi / lo planes
     constexpr bool CROSS_BF16 = PREC == 2 && !WGRAD && !BGATHER;     // cross terms as one bf16 MMA chain
     static_assert(!ATMA || (!WGRAD && !BGATHER), "the TMA-fed variant covers forward and backward-data");
@@ -264,8 +278,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
     uint8_t *stage_base = smem;
     uint8_t *raw_base = smem + STAGES * L::STAGE_BYTES;                       // ATMA: raw activation ring
     uint8_t *out_base = raw_base + RAWS * L::RAW_BYTES;                       // ATMA: epilogue staging, 2 x 4 KB per warp
-    uint64_t *bars = (uint64_t *)(out_base + L::OUT_BYTES);    // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], raw_full[RAWS], raw_empty[RAWS]
-    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4 + 2 * RAWS);
+    // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], then ATMA: raw_full[RAWS], raw_empty[RAWS]; WTMA: landed[STAGES]
+    uint8_t *table_base = out_base + L::OUT_BYTES;                            // backward-weight: per-warp row tables
+    uint64_t *bars = (uint64_t *)(table_base + L::TABLE_BYTES);
+    constexpr int XBARS = WTMA ? STAGES : 2 * RAWS;
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4 + XBARS);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     volatile int *progress = abort_flag + 1;              // last K-block (CTA sequence number) producer group 0 has stored
 
@@ -285,9 +302,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD / 64 + (B_TMA ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, NEPI / 32); }
+        for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, (ATMA ? 2 : 1) * NEPI / 32); }
         // a raw tile is filled by one expect_tx arrival plus the TMA bytes, and released by the four warps of the group that read it
         for (int s = 0; s < RAWS; s++) { mbar_init(bar_raw_full + 8 * s, 1); mbar_init(bar_raw_empty + 8 * s, 4); }
+        if constexpr (WTMA) for (int s = 0; s < STAGES; s++) mbar_init(bar_raw_full + 8 * s, 1);       // "landed": one expect_tx arrival + the bytes
         *abort_flag = 0;
         *progress = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -309,7 +327,46 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
     if (warp < 8) {
         // ============================ producers ============================
         constexpr uint32_t B_IMAGE = (uint32_t)L::B_BYTES * (SPLIT3 ? 2u : 1u);
-        if constexpr (BGATHER && !WGRAD) {
+        if constexpr (WTMA) {
+            // The raw fp32 tiles of K-block g have landed in stage g % STAGES (A rows where the hi plane of A lives, B rows
+            // where the hi plane of B lives, both already swizzled by the copy).  The group's 128 threads walk them 16 bytes
+            // at a time -- the split is elementwise, so the swizzle does not matter -- and write lo = v - hi to the lo plane
+            // and, unless the tensor core is known to ignore the low mantissa bits itself, hi back in place.
+            const int group = warp >> 2, gtid = tid & 127;
+            int t = blockIdx.x, kb0 = 0, nkb = 0, it = group;
+            auto settle = [&]() {
+                while (t < total_tiles) {
+                    kb_range(t, kb0, nkb);
+                    if (it < nkb) return;
+                    it -= nkb; t += gridDim.x;
+                }
+            };
+            settle();
+            for (int g = group; t < total_tiles; g += 2) {
+                const int s = g % STAGES;
+                if (!mbar_wait_warp(bar_raw_full + 8 * s, (g / STAGES) & 1, abort_flag)) { failed = true; break; }
+                uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
+                if constexpr (SPLIT3) {
+                    uint8_t *sB_hi = sA_hi + 2 * L::A_BYTES;
+                    auto split_plane = [&](uint8_t *hi_plane, uint8_t *lo_plane, int bytes) {
+#pragma unroll 4
+                        for (int off = gtid * 16; off < bytes; off += 128 * 16) {
+                            const float4 v = *(const float4 *)(hi_plane + off);
+                            float4 hi, lo;
+                            split_tf32(v.x, hi.x, lo.x); split_tf32(v.y, hi.y, lo.y); split_tf32(v.z, hi.z, lo.z); split_tf32(v.w, hi.w, lo.w);
+                            *(float4 *)(lo_plane + off) = lo;
+                            if (!P.raw_hi) *(float4 *)(hi_plane + off) = hi;
+                        }
+                    };
+                    split_plane(sA_hi, sA_hi + L::A_BYTES, L::A_BYTES);
+                    split_plane(sB_hi, sB_hi + L::B_BYTES, L::B_BYTES);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                it += 2; settle();
+            }
+        } else if constexpr (BGATHER && !WGRAD) {
             // Two groups of four warps on alternate K-blocks, as below.  Warp wq of a group gathers rows [32 wq, 32 wq + 32) of
             // A and its share of B: a quarter warp covers one 128-byte row (lane & 7 = the 16-byte chunk), so every load
             // instruction reads four whole rows, coalesced, and every store instruction fills four whole swizzle rows.
@@ -493,10 +550,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
                     const int n_tile = (t % tiles_mn) / P.tiles_m;
                     const uint32_t dstB = smem_u32(stage_base + s * L::STAGE_BYTES + (SPLIT3 ? 2 : 1) * L::A_BYTES);
                     const char *srcB = (const char *)P.packedB + ((size_t)(kb0 + it) * P.tiles_n + n_tile) * B_IMAGE;
+                    if (P.ablate & 1) mbar_arrive(bar_full + 8 * s);
+                    else {
                     mbar_expect_tx(bar_full + 8 * s, B_IMAGE);
                     tma_bulk_g2s(dstB, srcB, B_IMAGE, bar_full + 8 * s);
+                    }
                 }
-                store_row(s);
+                if (!(P.ablate & 16)) store_row(s);
                 fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
                 __syncwarp();                       // orders the other lanes' stores and fences before lane 0's arrive
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);      // one arrive per warp: 32 lanes on one barrier word serialise
@@ -506,13 +566,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
             }
         } else {
             // backward-weight: one lane per k.  As above, two groups of four warps take alternate K-blocks; a warp gathers
-            // 32 A rows and BN/4 B rows of its group's block.  A warp needs only ITS rows' table entries: lane r keeps entry r
-            // in registers and the gather loop broadcasts it with shuffles, so no warp waits on another one here.
+            // 32 A rows and BN/4 B rows of its group's block.  A warp needs only ITS rows' table entries, so every warp keeps
+            // a private copy of them in shared memory (written by its own lanes, read back as broadcasts): no warp waits on
+            // another one here.
             constexpr int RA = BM / 4, RB = BN_ / 4;
             static_assert(RA == 32 && RB <= 32, "one table entry per lane");
             const int group = warp >> 2, wq = warp & 3;
-            int2 myRowA = make_int2(0, INVALID_Y << 16);
-            int myRowB = -1;
+            int2 *rowsA = (int2 *)(table_base + warp * (32 * 12));
+            int *rowsB = (int *)(rowsA + 32);
             float av[RA], bv[BGATHER ? 1 : RB];
             // WGRAD with BGATHER: the dy operand (contiguous along k inside an image) is gathered with 16-byte loads, a
             // quarter warp per 128-byte row; the x operand (shifted by the filter taps) keeps one lane per k
@@ -527,8 +588,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
                     row_tile = mn;
                     const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
                     const int ma = m0 + wq * RA + lane, nb = n0 + wq * RB + lane;
-                    myRowA = ma < P.M_total ? __ldg(P.rowA + ma) : make_int2(0, INVALID_Y << 16);
-                    if (!BGATHER) myRowB = (lane < RB && nb < P.N_total) ? __ldg(P.rowB + nb) : -1;
+                    __syncwarp();                       // every lane has finished reading the previous tile's entries
+                    rowsA[lane] = ma < P.M_total ? __ldg(P.rowA + ma) : make_int2(0, INVALID_Y << 16);
+                    if (!BGATHER) rowsB[lane] = (lane < RB && nb < P.N_total) ? __ldg(P.rowB + nb) : -1;
+                    __syncwarp();
                     if constexpr (BGATHER) {
 #pragma unroll
                         for (int i = 0; i < BI; i++) { const int n = n0 + wq * RB + 4 * i + sub; offB[i] = n < P.N_total ? __ldg(P.rowB + n) : 0; }
@@ -540,7 +603,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
                 const float *base = P.srcA + ke.x;
 #pragma unroll
                 for (int r = 0; r < RA; r++) {
-                    const int2 re = make_int2(__shfl_sync(0xffffffffu, myRowA.x, r), __shfl_sync(0xffffffffu, myRowA.y, r));
+                    const int2 re = rowsA[r];
                     const int y = (re.y >> 16) + ky, x = (int)(short)(re.y & 0xffff) + kx;
                     const bool ok = (unsigned)y < (unsigned)P.limY && (unsigned)x < (unsigned)P.limX;
                     av[r] = ok ? __ldg(base + re.x) : 0.f;
@@ -554,7 +617,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
                     const float *bbase = P.srcB + (kb < 0 ? 0 : kb);
 #pragma unroll
                     for (int r = 0; r < RB; r++) {
-                        const int ro = __shfl_sync(0xffffffffu, myRowB, r);
+                        const int ro = rowsB[r];
                         bv[r] = (kb >= 0 && ro >= 0) ? __ldg(bbase + ro) : 0.f;
                     }
                 }
@@ -617,54 +680,91 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
         }
     } else if (warp == 8) {
         // ============================ MMA issuer (one thread) ============================
+        // One thread feeds the tensor core, so its instruction stream is kept short: shared-memory descriptors differ only
+        // in their 14-bit address field, which is advanced by adding constants (no field of the low word can carry into the
+        // next: shared addresses stay below 256 KB), and stage / phase / accumulator rotation are running counters.
         if (lane == 0) {
             const uint32_t idesc = make_idesc(BN_);
-            int g = 0, local = 0;
+            constexpr uint32_t DESC_HI = 64u | (1u << 14) | (2u << 29);       // upper word of make_desc()
+            auto desc = [&](uint32_t lo) { return ((uint64_t)DESC_HI << 32) | lo; };
+            const uint32_t stage0_lo = ((smem_u32(stage_base) >> 4) & 0x3FFFu) | (1u << 16);
+            constexpr uint32_t STAGE_STEP = (uint32_t)L::STAGE_BYTES >> 4, A_STEP = (uint32_t)L::A_BYTES >> 4, B_STEP = (uint32_t)L::B_BYTES >> 4;
+            int local = 0, set = 0;
+            uint32_t s = 0, full_phase = 0, set_phase = 1;
+            const int nmain = P.nmain;
+            const bool no_mma = (P.ablate & 8) != 0;
             for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x, local++) {
                 int kb0, nkb; kb_range(t, kb0, nkb);
-                const int set = local % nsets;
-                if (!mbar_wait(bar_acc_empty + 8 * set, ((local / nsets) & 1) ^ 1, abort_flag)) { failed = true; break; }
+                if (!mbar_wait(bar_acc_empty + 8 * set, set_phase, abort_flag)) { failed = true; break; }
                 tc_fence_after();
                 const uint32_t set_base = tmem_base + (uint32_t)(set * set_cols);
-                for (int it = 0; it < nkb; it++, g++) {
-                    const int s = g % STAGES;
-                    if (!mbar_wait(bar_full + 8 * s, (g / STAGES) & 1, abort_flag)) { failed = true; break; }
+                const uint32_t d_small = set_base + (uint32_t)small_off;
+                int rot = 0;                   // which of the rotating main accumulators the next k-step adds into
+                int fresh = nmain + 1;         // accumulators not written yet in this tile: the mains' first k-steps and the cross terms' first
+                for (int it = 0; it < nkb; it++) {
+                    if (!mbar_wait(bar_full + 8 * s, full_phase, abort_flag)) { failed = true; break; }
                     tc_fence_after();
-                    const uint32_t a_hi = smem_u32(stage_base + s * L::STAGE_BYTES);
-                    const uint32_t a_lo = a_hi + L::A_BYTES;
-                    const uint32_t b_hi = a_hi + (SPLIT3 ? 2 : 1) * L::A_BYTES;
-                    const uint32_t b_lo = b_hi + L::B_BYTES;
+                    const uint32_t a_hi = stage0_lo + s * STAGE_STEP;
+                    const uint32_t a_lo = a_hi + A_STEP;
+                    const uint32_t b_hi = a_hi + (SPLIT3 ? 2u : 1u) * A_STEP;
+                    const uint32_t b_lo = b_hi + B_STEP;
+                    if (!no_mma) {
 #pragma unroll
                     for (int ks = 0; ks < BK / 8; ks++) {
-                        const uint32_t o = ks * 32;      // 8 fp32 = 32 bytes along K inside the swizzle row
-                        const int step = it * (BK / 8) + ks;
-                        const uint32_t d_main = set_base + (uint32_t)((step % P.nmain) * BN_);
+                        const uint32_t o = 2u * ks;      // 8 fp32 = 32 bytes along K inside the swizzle row = 2 units of 16 bytes
+                        const bool first = (it == 0 && ks == 0);
                         if (SPLIT3) {
-                            const uint32_t d_small = set_base + (uint32_t)small_off;
                             if (!CROSS_BF16) {
-                                umma_tf32(d_small, make_desc(a_lo + o), make_desc(b_hi + o), idesc, step > 0 ? 1u : 0u);
-                                umma_tf32(d_small, make_desc(a_hi + o), make_desc(b_lo + o), idesc, 1u);
+                                umma_tf32(d_small, desc(a_lo + o), desc(b_hi + o), idesc, first ? 0u : 1u);
+                                umma_tf32(d_small, desc(a_hi + o), desc(b_lo + o), idesc, 1u);
                             } else {
                                 // cross terms in bf16: 16 of the 64 [lo | hi] x [hi | lo] columns per instruction
-                                umma_bf16(d_small, make_desc(a_lo + o), make_desc(b_lo + o), make_idesc_bf16(BN_), step > 0 ? 1u : 0u);
+                                umma_bf16(d_small, desc(a_lo + o), desc(b_lo + o), make_idesc_bf16(BN_), first ? 0u : 1u);
                             }
                         }
-                        umma_tf32(d_main, make_desc(a_hi + o), make_desc(b_hi + o), idesc, step >= P.nmain ? 1u : 0u);
+                        umma_tf32(set_base + (uint32_t)(rot * BN_), desc(a_hi + o), desc(b_hi + o), idesc, fresh > 1 ? 0u : 1u);
+                        if (fresh > 1) fresh--;
+                        if (++rot == nmain) rot = 0;
+                    }
                     }
                     umma_commit(bar_empty + 8 * s);      // frees the stage when these MMAs have read it
+                    if (++s == (uint32_t)STAGES) { s = 0; full_phase ^= 1u; }
                 }
                 if (!failed) umma_commit(bar_acc_full + 8 * set);     // this tile's accumulators are complete
+                if (++set == nsets) { set = 0; set_phase ^= 1u; }
             }
         }
         __syncwarp();
-    } else if (warp >= 13) {
+    } else if (warp == 13) {
         // ============================ L2 prefetch of the A operand (warp 13) ============================
         // Layers with a short reduction and no padding (1x1) are bound by the latency of the producers' gather: a group
         // has one K-block (16 KB) in flight per round trip to HBM.  This warp walks the CTA's K-block sequence up to
         // PF_AHEAD blocks ahead of producer group 0 and touches one address per (pf_rows consecutive tile rows, k): the
         // rows are consecutive pixels, so that is every line the producers will read, and their loads then hit in L2.
         // Nothing waits on this warp; its own wait on the producers' progress is bounded and it simply stops on a time-out.
-        if constexpr (ATMA) {
+        if constexpr (WTMA) {
+            // lane 0 fills the operand ring: for K-block number g of the CTA's sequence, 32 pixels of one image for the
+            // tile's 128 channel rows of x (A) and its BN filter rows of dy (B), as soon as the MMAs have released the stage
+            if (lane == 0) {
+                int g = 0;
+                for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
+                    int kb0, nkb; kb_range(t, kb0, nkb);
+                    const int mn = t % tiles_mn;
+                    const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
+                    for (int it = 0; it < nkb; it++, g++) {
+                        const int s = g % STAGES;
+                        if (!mbar_wait(bar_empty + 8 * s, ((g / STAGES) & 1) ^ 1, abort_flag)) { failed = true; break; }
+                        const int kbi = kb0 + it, img = kbi / P.chunks_per_image, x0 = (kbi % P.chunks_per_image) * 32;
+                        const uint32_t dstA = smem_u32(stage_base + s * L::STAGE_BYTES);
+                        const uint32_t dstB = dstA + (SPLIT3 ? 2 : 1) * L::A_BYTES;
+                        mbar_expect_tx(bar_raw_full + 8 * s, (uint32_t)(L::A_BYTES + L::B_BYTES));
+                        tma_load_3d(dstA, &P.mapA, x0, m0, img, bar_raw_full + 8 * s);
+                        tma_load_3d(dstB, &P.mapOut, x0, n0, img, bar_raw_full + 8 * s);
+                    }
+                }
+            }
+            __syncwarp();
+        } else if constexpr (ATMA) {
             // ATMA: this warp's lane 0 feeds the raw activation ring: per K-block four boxes of [32 channels][32 pixels], one per
             // 32-pixel chunk of the tile's rows (a chunk lies inside one image; what lies past the image, the channels or the
             // batch arrives as zeros).  It runs RAWS K-blocks ahead of the producers across tile boundaries.
@@ -679,6 +779,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
                     for (int it = 0; it < nkb; it++, g++) {
                         const int rs = g % RAWS;
                         if (!mbar_wait(bar_raw_empty + 8 * rs, ((g / RAWS) & 1) ^ 1, abort_flag)) { failed = true; break; }
+                        if (P.ablate & 2) { mbar_arrive(bar_raw_full + 8 * rs); continue; }
                         mbar_expect_tx(bar_raw_full + 8 * rs, (uint32_t)L::RAW_BYTES);
                         const uint32_t dst = smem_u32(raw_base + rs * L::RAW_BYTES);
 #pragma unroll
@@ -726,7 +827,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
         // ============================ epilogue (warps 9-12) ============================
         const int quarter = warp & 3;                     // the TMEM lane quarter this warp may access
         int local = 0;
-        int out_count = 0;                                // ATMA: output blocks this warp has handed to TMA
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, local++) {
             const int mn = t % tiles_mn, split = t / tiles_mn;
             const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
@@ -741,9 +841,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
                 const int cm = m0 / 32 + quarter;
                 const int img = cm / P.chunks_per_image, x0 = (cm % P.chunks_per_image) * 32;
                 const uint32_t set_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(set * set_cols);
-                float *stage2 = (float *)(out_base + quarter * (2 * 32 * 32 * 4));
+                // two warps share a lane quarter: warps 9-12 take the even 32-column chunks, warps 14-17 the odd ones
+                const int half = warp >= 14 ? 1 : 0;
+                constexpr int NCHUNK = (BN_ + 31) / 32;
+                float *sb = (float *)(out_base + (half * 4 + quarter) * (32 * 32 * 4));
+                if (half >= NCHUNK) {                       // BN = 32: nothing for the second set to drain
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_acc_empty + 8 * set);
+                    continue;
+                }
 #pragma unroll 1
-                for (int c = 0; c < (BN_ + 31) / 32; c++) {
+                for (int c = half; c < NCHUNK; c += 2) {
                     uint32_t r[32], tt[32];
                     tmem_ld32(set_base + (uint32_t)(c * 32), r);
 #pragma unroll 1
@@ -752,16 +861,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(tt[j])));
                     }
-                    if (c == (BN_ + 31) / 32 - 1) {
+                    if (c + 2 >= NCHUNK) {                  // this warp's last chunk of the set
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * set);
                     }
                     const int col0 = n0 + c * 32;
                     if (col0 < P.N_total && img < P.images) {             // warp-uniform
-                        float *sb = stage2 + (out_count & 1) * (32 * 32);
-                        // the copy that used this buffer two blocks ago must have read it; the latest one may still be in flight
-                        if (lane == 0) tma_wait_group_read<1>();
+                        // the copy that last used this warp's staging buffer must have read it (it had the whole
+                        // tensor-memory round trip above to do so)
+                        if (lane == 0) tma_wait_group_read<0>();
                         __syncwarp();
                         if (P.bias) {
 #pragma unroll
@@ -776,12 +885,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_tc_kernel(const __grid_cons
                         }
                         fence_async_smem();                 // generic-proxy stores -> visible to the copy engine
                         __syncwarp();
-                        if (lane == 0) {
+                        if (lane == 0 && !(P.ablate & 4)) {
                             if (P.reduce_out) tma_reduce_add_3d(&P.mapOut, x0, col0, img, smem_u32(sb));
                             else tma_store_3d(&P.mapOut, x0, col0, img, smem_u32(sb));
                             tma_commit_group();
                         }
-                        out_count++;
                     }
                 }
                 continue;
@@ -975,13 +1083,11 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
 // plane, so the main kernel fetches it with a single 16-byte-aligned TMA bulk copy.  The tile is read with consecutive
 // threads along the dimension that is contiguous in the weight tensor -- k for forward (w[f][c*r*s]), the in-channel row
 // for backward-data (w[f][c][r][s] with k = (f, r, s)) -- staged in shared memory, and written out 16 bytes per thread.
-template <int PREC>
-__global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ src, const int *__restrict__ rowB, const int *__restrict__ kB,
-                                                     float *__restrict__ packed, int bn, int n_total, int tiles_n, int row_fastest) {
-    constexpr bool SPLIT3 = PREC != 1;
-    __shared__ float tile[128][BK + 1];
-    const int kb = blockIdx.x, nt = blockIdx.y;
-    const size_t image_floats = (size_t)bn * BK * (SPLIT3 ? 2 : 1);
+__device__ __forceinline__ void pack_b_tile(const float *__restrict__ src, const int *__restrict__ rowB, const int *__restrict__ kB,
+                                            float *__restrict__ packed, int bn, int n_total, int tiles_n, int row_fastest, int prec, int kb, int nt,
+                                            float (*tile)[BK + 1]) {
+    const bool split3 = prec != 1;
+    const size_t image_floats = (size_t)bn * BK * (split3 ? 2 : 1);
     char *img = (char *)(packed + ((size_t)kb * tiles_n + nt) * image_floats);
     // blockDim.x = 256 is a multiple of BK and of bn, so one of the two coordinates is fixed per thread: its table entry is
     // looked up once, and the loop's loads are independent of each other (several in flight per thread)
@@ -1008,16 +1114,16 @@ __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ s
         const int row = q / (BK / 4), c = q % (BK / 4);
         const float4 v = make_float4(tile[row][4 * c], tile[row][4 * c + 1], tile[row][4 * c + 2], tile[row][4 * c + 3]);
         const uint32_t off = swz(row, 4 * c);
-        if (SPLIT3) {
+        if (split3) {
             float4 hi, lo;
             split_tf32(v.x, hi.x, lo.x); split_tf32(v.y, hi.y, lo.y); split_tf32(v.z, hi.z, lo.z); split_tf32(v.w, hi.w, lo.w);
             *(float4 *)(img + off) = hi;
-            if (PREC == 0) *(float4 *)(plane1 + off) = lo;
+            if (prec == 0) *(float4 *)(plane1 + off) = lo;
         } else {
             *(float4 *)(img + off) = v;
         }
     }
-    if (PREC == 2) {
+    if (prec == 2) {
         // plane 1: bf16 row of 64 = [hi(0..31) | lo(0..31)], the partner of the A rows' [lo | hi]; one 16-byte chunk = 8 values
         for (int q = threadIdx.x; q < bn * 8; q += blockDim.x) {
             const int row = q / 8, c = q % 8, k0 = (c & 3) * 8;
@@ -1033,27 +1139,79 @@ __global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ s
     }
 }
 
-template <int BN_, int PREC, bool WGRAD, bool BGATHER = false>
+__global__ void __launch_bounds__(256) pack_b_kernel(const float *__restrict__ src, const int *__restrict__ rowB, const int *__restrict__ kB,
+                                                     float *__restrict__ packed, int bn, int n_total, int tiles_n, int row_fastest, int prec) {
+    __shared__ float tile[128][BK + 1];
+    pack_b_tile(src, rowB, kB, packed, bn, n_total, tiles_n, row_fastest, prec, blockIdx.x, blockIdx.y, tile);
+}
+
+// Many weight tensors in ONE launch.  The weights of a net change once per step (the optimizer), while every layer needs
+// them packed twice (the forward and the backward-data tilings): the packed images are kept per (tensor, tiling), and the
+// first convolution call that finds its image out of date re-packs every image that is out of date with this kernel.
+struct PackJob { const float *src; const int *rowB, *kB; float *dst; int bn, n_total, tiles_n, row_fastest, prec, kblocks; };
+constexpr int kMaxPackJobs = 256;
+struct MultiPackArgs { const PackJob *jobs; int n; unsigned short slot[kMaxPackJobs]; unsigned start[kMaxPackJobs + 1]; };
+
+__global__ void __launch_bounds__(256) pack_b_multi_kernel(const __grid_constant__ MultiPackArgs A) {
+    __shared__ float tile[128][BK + 1];
+    // which job does this block belong to: the last one whose first block is <= blockIdx.x
+    int lo = 0, hi = A.n - 1;
+    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (A.start[mid] <= blockIdx.x) lo = mid; else hi = mid - 1; }
+    const PackJob j = A.jobs[A.slot[lo]];
+    const unsigned local = blockIdx.x - A.start[lo];
+    pack_b_tile(j.src, j.rowB, j.kB, j.dst, j.bn, j.n_total, j.tiles_n, j.row_fastest, j.prec, (int)(local / j.tiles_n), (int)(local % j.tiles_n), tile);
+}
+
+template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, int TMA = 0>
 int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
-    using L = Layout<BN_, PREC != 1>;
+    using L = Layout<BN_, PREC != 1, TMA == 1>;
     static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
     bool &configured = configured_dev[dev];
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e, "conv_tc(smem attribute)");
         configured = true;
     }
-    igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER><<<grid, NTHREADS, L::SMEM_BYTES, st>>>(P);
+    igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER, TMA><<<grid, threads_of(TMA), L::SMEM_BYTES, st>>>(P);
     EB_LAUNCH_CHECK("conv_tc");
     return 0;
 }
 
-template <int PREC, bool WGRAD, bool BGATHER = false>
+template <int PREC, bool WGRAD, bool BGATHER = false, int TMA = 0>
 int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn, int dev) {
-    if (bn == 32) return launch_variant<32, PREC, WGRAD, BGATHER>(cx, st, P, grid, dev);
-    if (bn == 64) return launch_variant<64, PREC, WGRAD, BGATHER>(cx, st, P, grid, dev);
-    return launch_variant<128, PREC, WGRAD, BGATHER>(cx, st, P, grid, dev);
+    if (bn == 32) return launch_variant<32, PREC, WGRAD, BGATHER, TMA>(cx, st, P, grid, dev);
+    if (bn == 64) return launch_variant<64, PREC, WGRAD, BGATHER, TMA>(cx, st, P, grid, dev);
+    return launch_variant<128, PREC, WGRAD, BGATHER, TMA>(cx, st, P, grid, dev);
 }
+
+// [images][channels][pixels] fp32 tensor as a 3-D tensor map with boxes of 32 pixels x 32 channels of one image, no swizzle:
+// the box lands in shared memory as [32 channels][32 pixels].  Needs a 16-byte aligned base and pixels % 4 == 0.
+// With swizzle128 the box (box_rows channels x 32 pixels = box_rows rows of 128 bytes) lands in the K-major SWIZZLE_128B layout
+// of an MMA operand whose k runs along the pixels.
+bool encode_plane_map(CUtensorMap *map, const float *base, int pixels, int channels, int images, int box_rows = 32, bool swizzle128 = false) {
+    const cuuint64_t dims[3] = {(cuuint64_t)pixels, (cuuint64_t)channels, (cuuint64_t)images};
+    const cuuint64_t strides[2] = {(cuuint64_t)pixels * 4, (cuuint64_t)pixels * channels * 4};
+    const cuuint32_t box[3] = {32, (cuuint32_t)box_rows, 1}, elem[3] = {1, 1, 1};
+    // the driver entry point is looked up at run time: the library must load (and refuse work) on a machine without a driver
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                 const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    static bool looked_up = false;
+    if (!looked_up) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) encode = (EncodeFn)fn;
+        else cudaGetLastError();
+        looked_up = true;
+    }
+    if (!encode) return false;
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), dims, strides, box, elem,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+int g_conv_tma = 2;            // eddlb200_set_option("conv_tma", 0 off / 1 stores only / 2 stores and adds)
+int g_conv_ablate = 0;
+int g_conv_wtma = 2;           // eddlb200_set_option("conv_tma_wgrad", 0 off / 1 on / 2 on, landed values used as the hi plane as they are)
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
 int g_conv_prefetch = 1;       // eddlb200_set_option("conv_prefetch", 0 / 1)
@@ -1073,6 +1231,77 @@ std::array<int, 24> table_key(const TableArgs &T) {
     const ConvGeom &g = T.g;
     return {T.mode, g.n, g.c, g.ih, g.iw, g.k, g.kr, g.kc, g.oh, g.ow, g.sr, g.sc, g.pt, g.pl,
             T.ca, T.cb, T.y0, T.x0, T.hc, T.wc, T.rt, T.st_, T.check, T.K_pad};
+}
+
+// Packed weight images, one per (weight tensor, tiling), valid while the tensor's write-observer version stands.
+struct PackEntry {
+    std::array<int, 24> tkey; int bn, precision; const float *src; size_t src_bytes;
+    float *packed; size_t packed_bytes;
+    unsigned blocks;                       // K-blocks x filter tiles = thread blocks that pack it
+    unsigned long long version;            // version of src the image was made from (0 = never)
+};
+struct PackCache {
+    std::mutex mu;
+    std::vector<PackEntry> entries;        // slot = index, also the index into the device job table
+    PackJob *jobs = nullptr;               // device memory, kMaxPackJobs entries
+};
+PackCache g_packs[EDDLB200_MAX_DEVICES];
+int g_conv_pack_cache = 1;                 // eddlb200_set_option("conv_pack_cache", 0 / 1)
+
+// The packed image of `src` for this tiling, re-packing every out-of-date image of the device in one launch when this
+// one is out of date.  nullptr = not cached (the caller packs into scratch for this call).  rowB / kB must be cached tables.
+const float *packed_weights(DevCtx *cx, cudaStream_t st, int dev, const std::array<int, 24> &tkey, int bn, int precision, const float *src,
+                            size_t src_bytes, const int *rowB, const int *kB, int kblocks, int tiles_n, int n_total, int row_fastest) {
+    if (!g_conv_pack_cache) return nullptr;
+    PackCache &pc = g_packs[dev];
+    std::lock_guard<std::mutex> lock(pc.mu);
+    if (!pc.jobs && cudaMalloc((void **)&pc.jobs, sizeof(PackJob) * kMaxPackJobs) != cudaSuccess) { cudaGetLastError(); pc.jobs = nullptr; return nullptr; }
+    int slot = -1;
+    for (size_t i = 0; i < pc.entries.size(); i++) {
+        const PackEntry &e = pc.entries[i];
+        if (e.src == src && e.bn == bn && e.precision == precision && e.tkey == tkey) { slot = (int)i; break; }
+    }
+    const size_t packed_bytes = (size_t)kblocks * tiles_n * bn * BK * sizeof(float) * (precision != 1 ? 2 : 1);
+    if (slot < 0) {
+        // a new image: take a free slot, or the slot of an image whose tensor is gone (released memory is no longer observed)
+        if ((int)pc.entries.size() < kMaxPackJobs) { pc.entries.push_back(PackEntry{}); slot = (int)pc.entries.size() - 1; }
+        else {
+            for (size_t i = 0; i < pc.entries.size() && slot < 0; i++)
+                if (watch_version(cx, pc.entries[i].src) == 0) slot = (int)i;
+            if (slot < 0) return nullptr;
+            cudaStreamSynchronize(st);                  // kernels already enqueued may still read the old image
+            cudaFree(pc.entries[slot].packed);
+            pc.entries[slot] = PackEntry{};
+        }
+        PackEntry &e = pc.entries[slot];
+        if (cudaMalloc((void **)&e.packed, packed_bytes) != cudaSuccess) { cudaGetLastError(); e = PackEntry{}; return nullptr; }
+        e.tkey = tkey; e.bn = bn; e.precision = precision; e.src = src; e.src_bytes = src_bytes; e.packed_bytes = packed_bytes;
+        e.blocks = (unsigned)kblocks * (unsigned)tiles_n; e.version = 0;
+        const PackJob job{src, rowB, kB, e.packed, bn, n_total, tiles_n, row_fastest, precision, kblocks};
+        // pageable source: staged before the call returns
+        if (cudaMemcpyAsync(pc.jobs + slot, &job, sizeof(job), cudaMemcpyHostToDevice, st) != cudaSuccess) { cudaGetLastError(); cudaFree(e.packed); e = PackEntry{}; return nullptr; }
+    }
+    PackEntry &me = pc.entries[slot];
+    const unsigned long long now = watch_add(cx, src, src_bytes);         // registers the tensor on first use
+    if (me.version != 0 && me.version == now) return me.packed;
+    // out of date: this image and every other one whose tensor has been written since it was packed
+    MultiPackArgs A;
+    A.jobs = pc.jobs; A.n = 0;
+    unsigned total = 0;
+    std::vector<unsigned long long> seen(pc.entries.size(), 0);
+    for (size_t i = 0; i < pc.entries.size(); i++) {
+        PackEntry &e = pc.entries[i];
+        if (!e.packed) continue;
+        const unsigned long long v = (int)i == slot ? now : watch_version(cx, e.src);
+        if (v == 0 || v == e.version) continue;         // tensor no longer observed (released), or image up to date
+        A.slot[A.n] = (unsigned short)i; A.start[A.n] = total; total += e.blocks; seen[i] = v; A.n++;
+    }
+    A.start[A.n] = total;
+    pack_b_multi_kernel<<<total, 256, 0, st>>>(A);
+    count_launch(cx);
+    if (cudaGetLastError() != cudaSuccess) return nullptr;
+    for (int i = 0; i < A.n; i++) pc.entries[A.slot[i]].version = seen[A.slot[i]];
+    return me.packed;
 }
 
 // out[i] = sum_s part[s][i] (+ bias[(i / plane) % nbias])      (split-K forward)
@@ -1111,8 +1340,35 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
                                g.ih == g.oh && g.iw == g.ow && (g.oh * g.ow) % 4 == 0 && T.K_total % BK == 0 &&
                                aligned16(srcA) && aligned16(srcB);
     if (both_rowmajor) T.check = 0;
+    // ... and, when the planes are at least one K-block long, both can be copied by TMA straight into the operand ring; the
+    // reduction then runs over (image, 32-pixel chunk) and needs neither k nor row tables
+    const int w_chunks = (g.oh * g.ow + 31) / 32;
+    bool wtma = both_rowmajor && g_conv_wtma > 0 && g.oh * g.ow >= 32 && g.c >= 32 && g.k >= 32;
+    int w_bn = 0;
+    if (wtma) {
+        w_bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);
+        P.chunks_per_image = w_chunks; P.images = g.n; P.raw_hi = g_conv_wtma > 1;
+        if (!encode_plane_map(&P.mapA, srcA, g.oh * g.ow, g.c, g.n, BM, true) || !encode_plane_map(&P.mapOut, srcB, g.oh * g.ow, g.k, g.n, w_bn, true)) wtma = false;
+    }
+    if (wtma) { T.check = 4; T.K_total = 0; T.K_pad = 0; }             // no k tables; check 4 keeps these tables apart in the cache
+    const int k_pad = wtma ? g.n * w_chunks * BK : T.K_pad;
     // any backward-weight: dy alone has that property whatever the filter and stride
     const bool b_vector = mode == 2 && (g.oh * g.ow) % 4 == 0 && T.K_total % BK == 0 && aligned16(srcB);
+    // forward / backward-data of a 1x1 stride-1 unpadded convolution: rows are pixels of one image plane, k is the channel,
+    // so the activation operand and the output are plain [image][channel][pixel] tensors that TMA can move
+    const int pq_ = g.oh * g.ow;
+    const int a_channels = mode == 0 ? g.c : g.k, o_channels = mode == 0 ? g.k : g.c;
+    const int chunks = (pq_ + 31) / 32;
+    bool atma = g_conv_tma > 0 && (mode == 0 || mode == 1) && g.kr == 1 && g.kc == 1 && g.sr == 1 && g.sc == 1 && g.pt == 0 && g.pl == 0 &&
+                g.ih == g.oh && g.iw == g.ow && pq_ % 4 == 0 && pq_ >= 32 && a_channels >= 32 && o_channels >= 32 &&
+                aligned16(srcA) && aligned16(out) && (long long)g.n * chunks * 32 < 0x7fffffffLL &&
+                (mode == 0 || out_zero || g_conv_tma > 1);
+    if (atma) {
+        P.chunks_per_image = chunks; P.images = g.n;
+        if (!encode_plane_map(&P.mapA, srcA, pq_, a_channels, g.n) || !encode_plane_map(&P.mapOut, out, pq_, o_channels, g.n)) atma = false;
+    }
+    if (atma) { T.check = 3; T.M_total = 0; allow_split = false; }      // no row tables; check 3 keeps these tables apart in the cache
+    const int m_rows = atma ? g.n * chunks * 32 : T.M_total;
     // the compact k table keeps 27 bits of offset beside the 5-bit tap number
     if (T.check == 1 && (long long)(g.c > g.k ? g.c : g.k) * (g.ih * g.iw > g.oh * g.ow ? g.ih * g.iw : g.oh * g.ow) + (long long)(g.kr + 1) * (g.iw + g.ow) >= (1ll << 26)) T.check = 2;
     P.check = T.check;
@@ -1123,8 +1379,8 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         else if (mode == 0) P.pf_rows = g.sc == 1 ? 32 : (g.sc == 2 ? 16 : 0);
     }
     const int bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);
-    const int tiles_m = (T.M_total + BM - 1) / BM, tiles_n = (T.N_total + bn - 1) / bn;
-    const int kblocks = T.K_pad / BK;
+    const int tiles_m = (m_rows + BM - 1) / BM, tiles_n = (T.N_total + bn - 1) / bn;
+    const int kblocks = k_pad / BK;
     // Split the reduction so that the persistent CTAs finish together: the makespan of `tiles * splits` work items dealt
     // round-robin to the SMs is ceil(items / SMs) rounds of (K-blocks per split + one epilogue); splitting also costs a
     // write and a read of every partial output.  Pick the split count with the smallest estimate (microseconds).
@@ -1172,6 +1428,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         } else { tb = nullptr; cudaGetLastError(); }
     }
     if (tb) off = 0;
+    const bool tb_cached = tb != nullptr;
     const size_t o_part = carve(splits > 1 ? out_total * splits * sizeof(float) : 0),
                  o_pack = carve(mode != 2 ? (size_t)kblocks * tiles_n * bn * BK * sizeof(float) * (precision != 1 ? 2 : 1) : 0);
     char *ws = (char *)scratch(cx, off ? off : 256);
@@ -1189,16 +1446,20 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     }
     P.packedB = nullptr;
     if (mode != 2) {
-        dim3 pgrid(kblocks, tiles_n);
-        if (precision == 0) pack_b_kernel<0><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, mode == 1);
-        else if (precision == 2) pack_b_kernel<2><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, mode == 1);
-        else pack_b_kernel<1><<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, mode == 1);
-        EB_LAUNCH_CHECK("conv_tc(pack weights)");
-        P.packedB = (const float *)(ws + o_pack);
+        const float *img = tb_cached ? packed_weights(cx, st, dev, table_key(T), bn, precision, srcB, (size_t)g.k * g.c * g.kr * g.kc * sizeof(float),
+                                                       T.rowB, T.kB, kblocks, tiles_n, T.N_total, mode == 1) : nullptr;
+        if (!img) {
+            // no cached image (tables not cached, cache full, or allocation failed): pack into the scratch arena for this call
+            dim3 pgrid(kblocks, tiles_n);
+            pack_b_kernel<<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, mode == 1, precision);
+            EB_LAUNCH_CHECK("conv_tc(pack weights)");
+            img = (const float *)(ws + o_pack);
+        }
+        P.packedB = img;
     }
     P.srcA = srcA; P.srcB = srcB;
     P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM; P.kC = T.kC;
-    P.M_total = T.M_total; P.N_total = T.N_total; P.K_pad = T.K_pad;
+    P.M_total = m_rows; P.N_total = T.N_total; P.K_pad = k_pad;
     P.kblocks_per_split = kbs;
     P.tiles_m = tiles_m; P.tiles_n = tiles_n; P.splits = splits;
     // a single accumulator drifts by ~2.5e-6 at 64 k-steps (K = 512); longer chains rotate over three
@@ -1206,13 +1467,18 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     P.status = g_status[dev];
     if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
     else { P.out = out; P.split_stride = 0; P.accumulate = (mode == 1 || mode == 2) && !out_zero; P.add_zero = out_zero; P.bias = bias; }
+    P.reduce_out = atma && P.accumulate;
+    P.ablate = g_conv_ablate;
     const long long total_tiles = (long long)tiles_m * tiles_n * splits;
     dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
     int r;
     // backward-weight has no bf16 variant: precision 2 runs it as precision 0
-    if (mode == 2 && both_rowmajor) r = precision != 1 ? launch_bn<0, false, true>(cx, st, P, grid, bn, dev) : launch_bn<1, false, true>(cx, st, P, grid, bn, dev);
+    if (wtma) r = precision != 1 ? launch_bn<0, false, true, 2>(cx, st, P, grid, bn, dev) : launch_bn<1, false, true, 2>(cx, st, P, grid, bn, dev);
+    else if (mode == 2 && both_rowmajor) r = precision != 1 ? launch_bn<0, false, true>(cx, st, P, grid, bn, dev) : launch_bn<1, false, true>(cx, st, P, grid, bn, dev);
     else if (mode == 2 && b_vector) r = precision != 1 ? launch_bn<0, true, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true, true>(cx, st, P, grid, bn, dev);
     else if (mode == 2) r = precision != 1 ? launch_bn<0, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true>(cx, st, P, grid, bn, dev);
+    else if (atma) r = precision == 0 ? launch_bn<0, false, false, 1>(cx, st, P, grid, bn, dev)
+                   : precision == 2 ? launch_bn<2, false, false, 1>(cx, st, P, grid, bn, dev) : launch_bn<1, false, false, 1>(cx, st, P, grid, bn, dev);
     else if (precision == 0) r = launch_bn<0, false>(cx, st, P, grid, bn, dev);
     else if (precision == 2) r = launch_bn<2, false>(cx, st, P, grid, bn, dev);
     else r = launch_bn<1, false>(cx, st, P, grid, bn, dev);
@@ -1348,6 +1614,10 @@ int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const flo
 }
 
 int conv_tc_set_prefetch(int on) { g_conv_prefetch = on ? 1 : 0; return 0; }
+int conv_tc_set_tma(int level) { g_conv_tma = level < 0 ? 0 : (level > 2 ? 2 : level); return 0; }
+int conv_tc_set_pack_cache(int on) { g_conv_pack_cache = on ? 1 : 0; return 0; }
+int conv_tc_set_ablate(int v) { g_conv_ablate = v; return 0; }
+int conv_tc_set_tma_wgrad(int level) { g_conv_wtma = level < 0 ? 0 : (level > 2 ? 2 : level); return 0; }
 
 // 0 = no kernel of this file has timed out on the device since the last call
 int conv_tc_status(int dev, cudaStream_t st, int *out) {

@@ -218,7 +218,11 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *          to immediate fills.
  *          "conv_prefetch" 1 (default) = in 1x1 unpadded layers a spare warp of the tensor-core kernel prefetches the
  *          activation operand into L2 ahead of the gather (results unchanged); 0 = off.
- *          "bn_waves" (1..64, default 16) and "bn_min_items" (>= 1024, default 8192): grid sizing of the BatchNorm
+ *          "conv_tma" 2 (default) = forward and backward-data of 1x1 stride-1 unpadded layers (planes of a multiple of 4
+          pixels, at least 32 channels on both sides) are fed by TMA tensor copies of the activations and drained by TMA
+          stores, or TMA fp32 adds where the output accumulates; 1 = only where the output is stored; 0 = the gather
+          kernel everywhere.  Results are the same bits at every level.
+          "bn_waves" (1..64, default 16) and "bn_min_items" (>= 1024, default 8192): grid sizing of the BatchNorm
  *          kernels -- every channel is cut into slices so that a launch has about bn_waves x (8 blocks per SM) blocks
  *          of at least bn_min_items elements each.  Results depend on the slicing only through the fp32 order of the
  *          partial sums (about 1e-7 relative on the statistics). */

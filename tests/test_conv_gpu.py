@@ -2,6 +2,8 @@
 Tolerance: max |got - want| <= 1e-5 * max |want| for the fp32-equivalent mode (precision 0; the requirement is rel 1e-5 of
 the reference's fp32 path) and 1e-3 for plain TF32 (precision 1).  `want` is the float64-accumulated restatement, the
 committed outputs of the reference's CPU code, its golden vectors, and that code run live where oracle/_ref is present."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -187,3 +189,125 @@ def test_benchmark_shapes_at_full_batch(lib, shape):
         print(key, "vs FMA path %.2e   vs float64 samples %.2e" % (full, sampled))
         assert full <= 1e-5, (key, full)
         assert sampled <= 1e-5, (key, sampled)
+
+
+TMA_SHAPES = [  # 1x1 stride-1 layers fed and drained by TMA tensor copies: n, c, h, w, k
+    (2, 64, 8, 8, 96),          # 64 pixels: two whole chunks per image
+    (3, 40, 6, 6, 72),          # 36 pixels: a ragged second chunk; channel counts that are not multiples of 32
+    (5, 96, 14, 14, 160),       # 196 pixels: seven chunks, the last with 4 pixels; rows of a tile from two images
+    (4, 256, 28, 28, 64),       # 784 pixels, 8 K-blocks
+    (2, 1024, 14, 14, 256),     # 32 K-blocks: rotating accumulators, one accumulator set
+]
+
+
+@pytest.mark.parametrize("shape", TMA_SHAPES)
+def test_tma_fed_1x1_layers_match_the_gather_kernel_bit_for_bit(lib, shape):
+    """Forward (with and without bias) and backward-data (into zeros and into a non-zero delta, i.e. TMA store and TMA
+    add) of 1x1 stride-1 layers: the TMA-fed kernel issues the same MMAs in the same order as the gather kernel, so the
+    results are identical bits wherever the gather kernel does not split the reduction; both are within 1e-5 of the oracle."""
+    n, c, h, w, k = shape
+    rng = np.random.default_rng(51)
+    x = rng.standard_normal((n, c, h, w)).astype(F); wt = rng.standard_normal((k, c, 1, 1)).astype(F)
+    b = rng.standard_normal(k).astype(F)
+    dy = rng.standard_normal((n, k, h, w)).astype(F); dx0 = rng.standard_normal(x.shape).astype(F)
+    out = {}
+    for level in (0, 2):
+        try:
+            lib.call("set_option", b"conv_tma", level)
+            r1 = run_conv(lib, x, wt, b, dy, None, None, dx0, (1, 1), (0, 0, 0, 0))
+            r2 = run_conv(lib, x, wt, None, dy, None, None, None, (1, 1), (0, 0, 0, 0))
+        finally:
+            lib.call("set_option", b"conv_tma", 2)
+        out[level] = (r1["y"], r1["dx"], r2["y"], r2["dx"])
+    lib.call("sync", 0)
+    for a, bb, name in zip(out[0], out[2], ("y+bias", "dx accumulated", "y", "dx into zeros")):
+        if c < 256:
+            np.testing.assert_array_equal(a, bb, err_msg=name)
+        else:
+            # reductions of 8 K-blocks or more on a grid this small make the gather kernel split K (another summation order)
+            assert relerr(a, bb) <= 2e-6, name
+    assert relerr(out[2][0], orc.conv2d_fwd(x, wt, b, (1, 1), (0, 0, 0, 0))) <= 1e-5
+    assert relerr(out[2][1], orc.conv2d_bwd_data(dy, wt, x.shape, dx0, (1, 1), (0, 0, 0, 0))) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", TMA_SHAPES + [(16, 64, 56, 56, 256)])
+def test_tma_fed_backward_weight_of_1x1_layers(lib, shape):
+    """Backward-weight of 1x1 stride-1 layers with both operands copied by TMA into the operand ring (reduction over
+    32-pixel chunks of one image, zero-filled past the end of the image): within 1e-5 of the oracle and of the 16-byte
+    gather kernel, accumulating into a non-zero gradient.  Level 2 leaves the landed fp32 values as the hi plane; the tensor
+    core reads only their upper 19 bits, so the result is the same bits as with the explicit mask."""
+    n, c, h, w, k = shape
+    rng = np.random.default_rng(61)
+    x = rng.standard_normal((n, c, h, w)).astype(F); wt = rng.standard_normal((k, c, 1, 1)).astype(F)
+    dy = rng.standard_normal((n, k, h, w)).astype(F); gw0 = rng.standard_normal(wt.shape).astype(F)
+    want, _ = orc.conv2d_bwd_weight(x, dy, gw0, None, (1, 1), (0, 0, 0, 0), (1, 1))
+    got = {}
+    for level in (0, 1, 2):
+        try:
+            lib.call("set_option", b"conv_tma_wgrad", level)
+            got[level] = run_conv(lib, x, wt, None, dy, gw0, None, None, (1, 1), (0, 0, 0, 0))["gw"]
+        finally:
+            lib.call("set_option", b"conv_tma_wgrad", 2)
+    lib.call("sync", 0)
+    for level in (0, 1, 2):
+        assert relerr(got[level], want) <= 1e-5, level
+    print("masked vs unmasked hi plane: max |difference| =", float(np.max(np.abs(got[1] - got[2]))))
+    np.testing.assert_array_equal(got[1], got[2])
+
+
+def test_packed_weight_images_follow_every_write_to_the_weights(lib):
+    """The packed (split, swizzled) weight images are kept between calls and re-made only after the weight tensor has been
+    written: every way of writing it through the library -- a copy, an in-place kernel, an optimizer step, releasing the
+    buffer and getting the same address back with other contents -- must be seen, for the forward and the backward-data
+    tiling alike; with the cache off the results are the same bits."""
+    rng = np.random.default_rng(71)
+    n, c, h, k = 4, 64, 12, 96
+    geo3 = (n, c, h, h, k, 3, 3, h, h, 1, 1, 1, 1, 0)
+    x = rng.standard_normal((n, c, h, h)).astype(F); dy = rng.standard_normal((n, k, h, h)).astype(F)
+    dx_, ddy = lib.to_device(x), lib.to_device(dy)
+    y, dxo = lib.empty((n, k, h, h)), lib.empty((n, c, h, h))
+
+    def both(dw):
+        lib.call("conv2d_fwd", 0, dx_, dw, None, y, *geo3)
+        lib.call("fill", 0, dxo, dxo.size, 0.0)
+        lib.call("conv2d_bwd_data", 0, ddy, dw, dxo, *geo3)
+        return y.numpy(), dxo.numpy()
+
+    def check(dw, w):
+        gy, gdx = both(dw)
+        assert relerr(gy, orc.conv2d_fwd(x, w, None, (1, 1), (1, 1, 1, 1))) <= 1e-5
+        assert relerr(gdx, orc.conv2d_bwd_data(dy, w, x.shape, None, (1, 1), (1, 1, 1, 1))) <= 1e-5
+        return gy, gdx
+
+    w = rng.standard_normal((k, c, 3, 3)).astype(F)
+    dw = lib.to_device(w)
+    first = check(dw, w)
+    before = lib.launches()
+    again = both(dw)                                                 # nothing written: no packing launch this time
+    steady = lib.launches() - before
+    np.testing.assert_array_equal(first[0], again[0]); np.testing.assert_array_equal(first[1], again[1])
+    w2 = rng.standard_normal(w.shape).astype(F)
+    lib.call("memcpy_h2d", 0, dw, w2.ctypes.data_as(ctypes.c_void_p), w2.nbytes)          # a copy
+    before = lib.launches()
+    both(dw)
+    assert lib.launches() - before == steady + 1                    # ONE launch re-packs both tilings
+    check(dw, w2)
+    lib.call("scale", 0, dw, dw, -0.5, w.size)                                            # an in-place kernel
+    check(dw, (w2 * F(-0.5)).astype(F))
+    g_, m_ = lib.to_device(rng.standard_normal(w.size).astype(F)), lib.zeros((w.size,))
+    lib.call("sgd_momentum", 0, dw, g_, m_, 0.1, 0.0, w.size)                               # an optimizer step
+    w3 = dw.numpy()
+    check(dw, w3)
+    try:
+        lib.call("set_option", b"conv_pack_cache", 0)
+        off = both(dw)
+    finally:
+        lib.call("set_option", b"conv_pack_cache", 1)
+    on = both(dw)
+    np.testing.assert_array_equal(off[0], on[0]); np.testing.assert_array_equal(off[1], on[1])
+    addr = dw.ptr.value
+    del dw                                                                                # released ...
+    w4 = rng.standard_normal(w.shape).astype(F)
+    dw4 = lib.to_device(w4)                                                               # ... and (usually) handed out again
+    print("same address reused:", dw4.ptr.value == addr)
+    check(dw4, w4)

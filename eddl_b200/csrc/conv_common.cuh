@@ -32,7 +32,6 @@ int conv_tc_set_tma(int level);
 // 1 (default): backward-weight of those layers has both operands copied by TMA into the operand ring; 2: in addition the landed
 // values serve as the hi plane unmasked; 0: the 16-byte gather.
 int conv_tc_set_tma_wgrad(int level);
-int conv_tc_set_ablate(int v);
 // 1 (default): packed weight images are kept per (weight tensor, tiling) and re-packed, all stale ones in one launch, only after
 // the tensor has been written; 0: every call packs its own.
 int conv_tc_set_pack_cache(int on);

@@ -93,7 +93,6 @@ struct TcParams {
     // space is images x chunks_per_image x 32 (rows past the end of an image are zero on the way in and clipped on the way out)
     int chunks_per_image, images;
     int reduce_out;         // the output is added into (TMA reduce) instead of stored
-    int ablate;             // TEMP experiment switches
     int raw_hi;             // WTMA: leave the landed fp32 values as the hi plane (the tensor core reads only their upper 19 bits)
     alignas(64) CUtensorMap mapA;
     alignas(64) CUtensorMap mapOut;
@@ -550,13 +549,10 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     const int n_tile = (t % tiles_mn) / P.tiles_m;
                     const uint32_t dstB = smem_u32(stage_base + s * L::STAGE_BYTES + (SPLIT3 ? 2 : 1) * L::A_BYTES);
                     const char *srcB = (const char *)P.packedB + ((size_t)(kb0 + it) * P.tiles_n + n_tile) * B_IMAGE;
-                    if (P.ablate & 1) mbar_arrive(bar_full + 8 * s);
-                    else {
                     mbar_expect_tx(bar_full + 8 * s, B_IMAGE);
                     tma_bulk_g2s(dstB, srcB, B_IMAGE, bar_full + 8 * s);
-                    }
                 }
-                if (!(P.ablate & 16)) store_row(s);
+                store_row(s);
                 fence_async_smem();                 // generic-proxy stores -> visible to the tensor core (async proxy)
                 __syncwarp();                       // orders the other lanes' stores and fences before lane 0's arrive
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);      // one arrive per warp: 32 lanes on one barrier word serialise
@@ -692,7 +688,6 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             int local = 0, set = 0;
             uint32_t s = 0, full_phase = 0, set_phase = 1;
             const int nmain = P.nmain;
-            const bool no_mma = (P.ablate & 8) != 0;
             for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x, local++) {
                 int kb0, nkb; kb_range(t, kb0, nkb);
                 if (!mbar_wait(bar_acc_empty + 8 * set, set_phase, abort_flag)) { failed = true; break; }
@@ -708,7 +703,6 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     const uint32_t a_lo = a_hi + A_STEP;
                     const uint32_t b_hi = a_hi + (SPLIT3 ? 2u : 1u) * A_STEP;
                     const uint32_t b_lo = b_hi + B_STEP;
-                    if (!no_mma) {
 #pragma unroll
                     for (int ks = 0; ks < BK / 8; ks++) {
                         const uint32_t o = 2u * ks;      // 8 fp32 = 32 bytes along K inside the swizzle row = 2 units of 16 bytes
@@ -725,7 +719,6 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                         umma_tf32(set_base + (uint32_t)(rot * BN_), desc(a_hi + o), desc(b_hi + o), idesc, fresh > 1 ? 0u : 1u);
                         if (fresh > 1) fresh--;
                         if (++rot == nmain) rot = 0;
-                    }
                     }
                     umma_commit(bar_empty + 8 * s);      // frees the stage when these MMAs have read it
                     if (++s == (uint32_t)STAGES) { s = 0; full_phase ^= 1u; }
@@ -779,7 +772,6 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     for (int it = 0; it < nkb; it++, g++) {
                         const int rs = g % RAWS;
                         if (!mbar_wait(bar_raw_empty + 8 * rs, ((g / RAWS) & 1) ^ 1, abort_flag)) { failed = true; break; }
-                        if (P.ablate & 2) { mbar_arrive(bar_raw_full + 8 * rs); continue; }
                         mbar_expect_tx(bar_raw_full + 8 * rs, (uint32_t)L::RAW_BYTES);
                         const uint32_t dst = smem_u32(raw_base + rs * L::RAW_BYTES);
 #pragma unroll
@@ -885,7 +877,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                         }
                         fence_async_smem();                 // generic-proxy stores -> visible to the copy engine
                         __syncwarp();
-                        if (lane == 0 && !(P.ablate & 4)) {
+                        if (lane == 0) {
                             if (P.reduce_out) tma_reduce_add_3d(&P.mapOut, x0, col0, img, smem_u32(sb));
                             else tma_store_3d(&P.mapOut, x0, col0, img, smem_u32(sb));
                             tma_commit_group();
@@ -1210,7 +1202,6 @@ bool encode_plane_map(CUtensorMap *map, const float *base, int pixels, int chann
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 int g_conv_tma = 2;            // eddlb200_set_option("conv_tma", 0 off / 1 stores only / 2 stores and adds)
-int g_conv_ablate = 0;
 int g_conv_wtma = 2;           // eddlb200_set_option("conv_tma_wgrad", 0 off / 1 on / 2 on, landed values used as the hi plane as they are)
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
@@ -1468,7 +1459,6 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
     else { P.out = out; P.split_stride = 0; P.accumulate = (mode == 1 || mode == 2) && !out_zero; P.add_zero = out_zero; P.bias = bias; }
     P.reduce_out = atma && P.accumulate;
-    P.ablate = g_conv_ablate;
     const long long total_tiles = (long long)tiles_m * tiles_n * splits;
     dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
     int r;
@@ -1616,7 +1606,6 @@ int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const flo
 int conv_tc_set_prefetch(int on) { g_conv_prefetch = on ? 1 : 0; return 0; }
 int conv_tc_set_tma(int level) { g_conv_tma = level < 0 ? 0 : (level > 2 ? 2 : level); return 0; }
 int conv_tc_set_pack_cache(int on) { g_conv_pack_cache = on ? 1 : 0; return 0; }
-int conv_tc_set_ablate(int v) { g_conv_ablate = v; return 0; }
 int conv_tc_set_tma_wgrad(int level) { g_conv_wtma = level < 0 ? 0 : (level > 2 ? 2 : level); return 0; }
 
 // 0 = no kernel of this file has timed out on the device since the last call

@@ -93,6 +93,21 @@ model make_net(const std::string &cfg, Handle *h, int hw, int classes) {
         l = Reshape(l, {-1});
         return Model({in}, {Softmax(Dense(l, h->classes))});
     }
+    if (cfg == "cifar_da") {
+        // the layers EDDL's CIFAR-10 examples add around their conv stacks (examples/nn/2_cifar10/*_da*.cpp): random
+        // crop-scale and flip on the input, Concat, UpSampling, GlobalMaxPool, Dropout
+        h->in_c = 3; h->in_h = h->in_w = hw > 0 ? hw : 32; h->classes = classes > 0 ? classes : 10;
+        in = Input({h->in_c, h->in_h, h->in_w});
+        l = RandomHorizontalFlip(RandomCropScale(in, {0.8f, 1.0f}));
+        l = MaxPool(conv_bn_relu(l, 32, {3, 3}, {1, 1}, "same"), {2, 2}, {2, 2});
+        layer a = conv_bn_relu(l, 16, {1, 1}, {1, 1}, "same"), b = conv_bn_relu(l, 48, {3, 3}, {1, 1}, "same");
+        l = Concat({a, b});
+        l = MaxPool(UpSampling(l, {2, 2}), {2, 2}, {2, 2});
+        l = conv_bn_relu(l, 64, {3, 3}, {1, 1}, "same");
+        l = Reshape(GlobalMaxPool(l), {-1});
+        l = Dropout(l, 0.25f);
+        return Model({in}, {Softmax(Dense(l, h->classes))});
+    }
     throw std::runtime_error("unknown net config '" + cfg + "'");
 }
 

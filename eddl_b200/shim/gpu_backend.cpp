@@ -167,7 +167,14 @@ template <typename D> void fill_random(Tensor *A, D dist) {
 void gpu_rand_uniform(Tensor *A, float v) { std::uniform_real_distribution<float> d(0.f, 1.f); fill_random(A, [&](std::mt19937 &g) { return d(g) * v; }); }
 void gpu_rand_signed_uniform(Tensor *A, float v) { std::uniform_real_distribution<float> d(-1.f, 1.f); fill_random(A, [&](std::mt19937 &g) { return d(g) * v; }); }
 void gpu_rand_normal(Tensor *A, float m, float s) { std::normal_distribution<float> d(m, s); fill_random(A, [&](std::mt19937 &g) { return d(g); }); }
-void gpu_rand_binary(Tensor *A, float v) { std::uniform_real_distribution<float> d(0.f, 1.f); fill_random(A, [&](std::mt19937 &g) { return d(g) < v ? 1.f : 0.f; }); }
+// Dropout's mask (LDropout::forward, src/layers/core/layer_drop.cpp:50-58) is as large as the activations: it is drawn on
+// the device.  The stream position advances by the tensor size, so successive masks are independent.
+void gpu_rand_binary(Tensor *A, float v) {
+    static size_t position[64] = {};
+    const int dev = dev_of(A);
+    ok(eddlb200_rand_binary(dev, A->ptr, A->size, v, 1234, position[dev & 63]), "gpu_rand_binary");
+    position[dev & 63] += A->size;
+}
 
 // ---- elementwise ------------------------------------------------------------------------
 void gpu_add(Tensor *A, Tensor *B, float v) { ok(eddlb200_addc(dev_of(A), A->ptr, B->ptr, v, A->size), "gpu_add"); }
@@ -198,6 +205,49 @@ void gpu_pad(Tensor *A, Tensor *B, vector<int> pads) {
 }
 void gpu_pad_back(Tensor *A, Tensor *B, vector<int> pads) {
     ok(eddlb200_pad_bwd(dev_of(A), A->ptr, B->ptr, A->shape[0], A->shape[1], A->shape[2], A->shape[3], pads[0], pads[2], pads[3], pads[1]), "gpu_pad_back");
+}
+
+// ---- Concat, UpSampling, random flips and crops (the host side draws the random decisions) ----------------------
+void gpu_concat(Tensor *A, vector<Tensor *> t, unsigned int axis, bool derivative) {
+    std::vector<float *> parts; std::vector<size_t> sizes, strides;
+    for (Tensor *p : t) { parts.push_back(p->ptr); sizes.push_back(p->size); strides.push_back((size_t)p->stride[axis] * p->shape[axis]); }
+    ok(eddlb200_concat(dev_of(A), A->ptr, parts.data(), sizes.data(), strides.data(), (int)parts.size(), (size_t)A->stride[axis] * A->shape[axis], derivative),
+       "gpu_concat");
+}
+void gpu_repeat_nn(Tensor *A, Tensor *B, vector<int> size) {
+    ok(eddlb200_repeat_nn(dev_of(A), A->ptr, B->ptr, A->size / A->shape[3], A->shape[3], size[0], size[1]), "gpu_repeat_nn");
+}
+void gpu_d_repeat_nn(Tensor *D, Tensor *A, vector<int> size) {
+    ok(eddlb200_repeat_nn_bwd(dev_of(A), D->ptr, A->ptr, A->size / A->shape[3], A->shape[3], size[0], size[1]), "gpu_d_repeat_nn");
+}
+void gpu_scale(Tensor *A, Tensor *B, vector<int> new_shape, int wrapping_mode, float constant, int transformation_mode) {
+    ok(eddlb200_resize(dev_of(A), A->ptr, B->ptr, A->shape[0], A->shape[1], A->shape[2], A->shape[3], B->shape[2], B->shape[3],
+                      new_shape[0], new_shape[1], wrapping_mode, constant, transformation_mode), "gpu_scale");
+}
+void gpu_scale_back(Tensor *A, Tensor *B, vector<int> new_shape, int wrapping_mode, float constant, int transformation_mode) {
+    ok(eddlb200_resize_bwd(dev_of(A), A->ptr, B->ptr, A->shape[0], A->shape[1], A->shape[2], A->shape[3], B->shape[2], B->shape[3],
+                          new_shape[0], new_shape[1], wrapping_mode, constant, transformation_mode), "gpu_scale_back");
+}
+void gpu_flip_random(Tensor *A, Tensor *B, int axis) {
+    std::uniform_real_distribution<float> u(0.f, 1.f);
+    std::vector<unsigned char> apply(A->shape[0]);
+    for (auto &a : apply) a = u(rng(A->gpu_device)) >= 0.5f;               // cpu_flip_random, src/hardware/cpu/cpu_da.cpp:584-595
+    ok(eddlb200_flip_batch(dev_of(A), A->ptr, B->ptr, A->shape[0], A->shape[1], A->shape[2], A->shape[3], axis, apply.data()), "gpu_flip_random");
+}
+void gpu_crop_scale_random(Tensor *A, Tensor *B, vector<float> factor, int wrapping_mode, float constant) {
+    (void)wrapping_mode; (void)constant;                                    // unused by the reference's arithmetic as well
+    std::vector<int> boxes(4 * (size_t)A->shape[0]);
+    auto &g = rng(A->gpu_device);
+    for (int b = 0; b < A->shape[0]; b++) {
+        // cpu_crop_scale_random, src/hardware/cpu/cpu_da.cpp:625-646
+        const float scale = std::uniform_real_distribution<float>(factor[0], factor[1])(g);
+        const int h = (int)(A->shape[2] * scale), w = (int)(A->shape[3] * scale);
+        const int y = (int)((A->shape[2] - h) * std::uniform_real_distribution<float>(0.f, 1.f)(g));
+        const int x = (int)((A->shape[3] - w) * std::uniform_real_distribution<float>(0.f, 1.f)(g));
+        boxes[4 * b] = y; boxes[4 * b + 1] = x; boxes[4 * b + 2] = y + h; boxes[4 * b + 3] = x + w;
+    }
+    ok(eddlb200_crop_scale_batch(dev_of(A), A->ptr, B->ptr, A->shape[0], A->shape[1], A->shape[2], A->shape[3], B->shape[2], B->shape[3], boxes.data()),
+       "gpu_crop_scale_random");
 }
 
 // ---- activations ------------------------------------------------------------------------

@@ -190,6 +190,39 @@ int eddlb200_pad(int dev, const float *a, float *b, int n, int c, int h, int w,
 int eddlb200_pad_bwd(int dev, float *a_delta, const float *b_delta, int n, int c, int h, int w,
                      int top, int bottom, int left, int right);   /* a_delta += crop(b_delta) */
 
+/* ---- layers beside the benchmark nets that EDDL's own convnet examples use (examples/nn/2_cifar10): Concat, UpSampling,
+ *      Dropout, RandomFlip, RandomCropScale.  gpu_concat (src/hardware/gpu/gpu_core.cu:384-409; cpu_concat,
+ *      src/hardware/cpu/cpu_core.cpp:368-396); gpu_repeat_nn / gpu_d_repeat_nn (src/hardware/cpu/nn/cpu_tensor_nn.cpp:13-50);
+ *      gpu_rand_binary; gpu_flip_random / gpu_crop_scale_random (src/hardware/gpu/gpu_da.cu:250-302; cpu_single_flip and
+ *      cpu_single_crop_scale, src/hardware/cpu/cpu_da.cpp:315-336, 363-384). */
+/* Concatenation along one axis of `a`: part i holds part_sizes[i] floats in runs of part_strides[i] (= stride[axis] *
+ * shape[axis] of that tensor); `steps` is the same product for `a`.  derivative != 0 runs it backwards: part += slice of a. */
+int eddlb200_concat(int dev, float *a, float *const *parts, const size_t *part_sizes, const size_t *part_strides, int nparts,
+                    size_t steps, int derivative);
+/* UpSampling by whole factors: b[row*size_r + i][col*size_c + j] = a[row][col] over rows_a = batch*channels*height rows;
+ * backward adds every block of d into a, one value at a time in row-major order of the block. */
+int eddlb200_repeat_nn(int dev, const float *a, float *b, size_t rows_a, int cols_a, int size_r, int size_c);
+int eddlb200_repeat_nn_bwd(int dev, const float *d, float *a, size_t rows_a, int cols_a, int size_r, int size_c);
+/* Nearest-neighbour resize of a [n,c,ah,aw] to b [n,c,bh,bw] thought of as a (new_h, new_w) image cropped at its centre
+ * (gpu_scale / gpu_scale_back, src/hardware/gpu/gpu_da.cu:61-88; cpu_single_scale(_back), src/hardware/cpu/cpu_da.cpp:88-190):
+ * eddl::UpSampling2D is this with new shape = b's shape.  mode: 0 half-pixel, 2 align-corners, 3 asymmetric (the source index
+ * uses the reference's float arithmetic and truncation).  wrap: where a source index leaves a, 0 writes cval and 5
+ * ("original", forward only) copies a at b's own position; other wrapping modes are accepted only when no index leaves a.
+ * The backward pass adds every b_delta value into its source position of a_delta, in row-major order of b. */
+int eddlb200_resize(int dev, const float *a, float *b, int n, int c, int ah, int aw, int bh, int bw, int new_h, int new_w,
+                   int wrap, float cval, int mode);
+int eddlb200_resize_bwd(int dev, float *a_delta, const float *b_delta, int n, int c, int ah, int aw, int bh, int bw,
+                       int new_h, int new_w, int wrap, float cval, int mode);
+/* Image i of the batch is mirrored along axis (0 = rows, 1 = columns) when apply_host[i] != 0, copied otherwise.
+ * apply_host is a HOST array of n bytes: the caller draws the decisions (uniform >= 0.5 in the reference). */
+int eddlb200_flip_batch(int dev, const float *a, float *b, int n, int c, int h, int w, int axis, const unsigned char *apply_host);
+/* Image i of b [n,c,bh,bw] is the box (y0, x0) .. (y1, x1) of image i of a [n,c,ah,aw], resized by nearest neighbour with
+ * the reference's integer arithmetic Ai = Bi*(y1-y0+1)/bh + y0.  boxes_host is a HOST array of 4n ints (y0, x0, y1, x1). */
+int eddlb200_crop_scale_batch(int dev, const float *a, float *b, int n, int c, int ah, int aw, int bh, int bw, const int *boxes_host);
+/* a[i] = 1 with probability p, else 0: value i of the stream (seed, offset) of a counter-based generator, so equal
+ * arguments give equal masks whatever the launch geometry (the reference draws from cuRAND; no stream is shared with it). */
+int eddlb200_rand_binary(int dev, float *a, size_t n, float p, size_t seed, size_t offset);
+
 /* ---- dense algebra (src/hardware/gpu/gpu_math.cu:457-528; gpu_reduction.cu:232-244;
  *      src/hardware/cpu/cpu_math.cpp:302-325,369-401) */
 /* gpu_mult2D: C[m,n] = (inc_c ? C : 0) + op(A) * op(B), row-major; A is [m,k] (or [k,m]

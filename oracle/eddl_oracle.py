@@ -408,3 +408,90 @@ def sync_weights(reps):
     for r in reps:
         acc = (acc + r).astype(F)
     return (acc * (F(1.0) / F(reps.shape[0]))).astype(F)
+
+
+# ---- Concat / UpSampling / flips and crops: cpu_core.cpp:368-396, nn/cpu_tensor_nn.cpp:13-50, cpu_da.cpp:315-336, 363-384 -----
+def concat(parts, axis):
+    return np.concatenate([np.asarray(p, F) for p in parts], axis=axis)
+
+
+def concat_back(a_delta, parts0, axis):
+    """part_i += its slice of a_delta (cpu_concat with derivative = true)."""
+    out, pos = [], 0
+    for p in parts0:
+        n = p.shape[axis]
+        sl = [slice(None)] * a_delta.ndim; sl[axis] = slice(pos, pos + n)
+        out.append(np.asarray(p, F) + np.asarray(a_delta, F)[tuple(sl)]); pos += n
+    return out
+
+
+def repeat_nn(a, size):
+    return np.repeat(np.repeat(np.asarray(a, F), size[0], axis=2), size[1], axis=3)
+
+
+def d_repeat_nn(d, a0, size):
+    """A[row, col] += every value of its block of D, one by one in row-major order of the block (fp32 adds)."""
+    a = np.asarray(a0, F).copy(); d = np.asarray(d, F)
+    for r in range(size[0]):
+        for c in range(size[1]):
+            a = (a + d[:, :, r::size[0], c::size[1]]).astype(F)
+    return a
+
+
+def _scale_src(b, off, n_new, a_extent, mode):
+    """Source index of output index b: cpu_single_scale's float arithmetic, truncated to int (cpu_da.cpp:95-116)."""
+    a = (np.asarray(b, np.int64) + off).astype(F)
+    if mode == 0:
+        s = F(n_new) / F(a_extent); v = (a + F(0.5)) / s - F(0.5)
+    elif mode == 2:
+        s = F(n_new - 1) / F(a_extent - 1); v = a / s
+    else:
+        s = F(n_new) / F(a_extent); v = a / s
+    return np.trunc(v.astype(F)).astype(np.int64)
+
+
+def scale(a, out_hw, new_shape, mode=3, wrap=0, cval=0.0):
+    """Nearest-neighbour resize (cpu_scale -> cpu_single_scale, cpu_da.cpp:88-138, 407-437)."""
+    a = np.asarray(a, F); bh, bw = out_hw
+    off_y, off_x = int((new_shape[0] - bh) / 2.0), int((new_shape[1] - bw) / 2.0)
+    ai = _scale_src(np.arange(bh), off_y, new_shape[0], a.shape[2], mode); aj = _scale_src(np.arange(bw), off_x, new_shape[1], a.shape[3], mode)
+    oki = (ai >= 0) & (ai < a.shape[2]); okj = (aj >= 0) & (aj < a.shape[3])
+    b = a[:, :, np.clip(ai, 0, a.shape[2] - 1)][:, :, :, np.clip(aj, 0, a.shape[3] - 1)].copy()
+    outside = ~(oki[:, None] & okj[None, :])
+    if outside.any():
+        if wrap == 5:
+            b[:, :, outside] = a[:, :, outside]
+        else:
+            b[:, :, outside] = F(cval)
+    return b
+
+
+def scale_back(a_delta0, b_delta, new_shape, mode=3):
+    """A[ai][aj] += B[bi][bj] for every output element, visited in row-major order (cpu_single_scale_back, cpu_da.cpp:140-190)."""
+    a = np.asarray(a_delta0, F).copy(); b = np.asarray(b_delta, F); bh, bw = b.shape[2:]
+    off_y, off_x = int((new_shape[0] - bh) / 2.0), int((new_shape[1] - bw) / 2.0)
+    ai = _scale_src(np.arange(bh), off_y, new_shape[0], a.shape[2], mode); aj = _scale_src(np.arange(bw), off_x, new_shape[1], a.shape[3], mode)
+    for i in range(bh):
+        for j in range(bw):
+            if 0 <= ai[i] < a.shape[2] and 0 <= aj[j] < a.shape[3]:
+                a[:, :, ai[i], aj[j]] = (a[:, :, ai[i], aj[j]] + b[:, :, i, j]).astype(F)
+    return a
+
+
+def flip_batch(a, apply, axis):
+    a = np.asarray(a, F); b = a.copy()
+    for i, ap in enumerate(apply):
+        if ap:
+            b[i] = a[i, :, ::-1, :] if axis == 0 else a[i, :, :, ::-1]
+    return b
+
+
+def crop_scale_batch(a, boxes, out_hw):
+    """B[n,c,i,j] = A[n,c, i*(y1-y0+1)//BH + y0, j*(x1-x0+1)//BW + x0]  (integer arithmetic of cpu_single_crop_scale)."""
+    a = np.asarray(a, F); bh, bw = out_hw
+    b = np.empty(a.shape[:2] + (bh, bw), F)
+    for n, (y0, x0, y1, x1) in enumerate(boxes):
+        ai = (np.arange(bh) * (y1 - y0 + 1)) // bh + y0
+        aj = (np.arange(bw) * (x1 - x0 + 1)) // bw + x0
+        b[n] = a[n][:, ai][:, :, aj]
+    return b

@@ -63,6 +63,10 @@ struct PoolCase {
 
 }  // namespace
 
+// defined in src/hardware/cpu/cpu_da.cpp, not declared in a public header
+void cpu_single_flip(int b, bool apply, Tensor *A, Tensor *B, int axis);
+void cpu_single_crop_scale(int b, Tensor *A, Tensor *B, vector<int> coords_from, vector<int> coords_to, int wrapping_mode, float constant);
+
 extern "C" {
 
 const char *ref_last_error() { return g_err.c_str(); }
@@ -219,6 +223,37 @@ int ref_sync_weights(const float *reps, int nrep, float *out, long long n) {
         acc->fill_(0.0);
         for (int r = 0; r < nrep; r++) { View w({(int)n}, reps + (size_t)r * n); Tensor::inc(w, acc); }
         acc->div_(nrep);
+    });
+}
+
+// Concat of two tensors along axis 1 and its backward (cpu_concat, src/hardware/cpu/cpu_core.cpp:368-396); UpSampling
+// (cpu_repeat_nn / cpu_d_repeat_nn, nn/cpu_tensor_nn.cpp:13-50); one image's flip and crop-scale (cpu_da.cpp:315-336, 363-384).
+int ref_concat2(float *a, float *p0, float *p1, int n, int c0, int c1, int h, int w, int derivative) {
+    return guarded([&] { View A({n, c0 + c1, h, w}, a), P0({n, c0, h, w}, p0), P1({n, c1, h, w}, p1); cpu_concat(A, {P0.t, P1.t}, 1, derivative != 0); });
+}
+int ref_repeat_nn(const float *a, float *b, float *a_delta, const float *b_delta, int n, int c, int h, int w, int sr, int sc) {
+    return guarded([&] {
+        View A({n, c, h, w}, a), B({n, c, h * sr, w * sc}, b);
+        cpu_repeat_nn(A, B, {sr, sc});
+        if (a_delta) { View AD({n, c, h, w}, a_delta), BD({n, c, h * sr, w * sc}, b_delta); cpu_d_repeat_nn(BD, AD, {sr, sc}); }
+    });
+}
+// Tensor::scale / scale_back (cpu_scale, cpu_scale_back: src/hardware/cpu/cpu_da.cpp:407-459)
+int ref_scale(const float *a, float *b, float *a_delta, const float *b_delta, int n, int c, int ah, int aw, int bh, int bw, int nh, int nw,
+              int wrap, float cval, int mode) {
+    return guarded([&] {
+        View A({n, c, ah, aw}, a), B({n, c, bh, bw}, b);
+        cpu_scale(A, B, {nh, nw}, wrap, cval, mode);
+        if (a_delta) { View AD({n, c, ah, aw}, a_delta), BD({n, c, bh, bw}, b_delta); cpu_scale_back(AD, BD, {nh, nw}, wrap, cval, mode); }
+    });
+}
+int ref_flip_batch(const float *a, float *b, int n, int c, int h, int w, int axis, const unsigned char *apply) {
+    return guarded([&] { View A({n, c, h, w}, a), B({n, c, h, w}, b); for (int i = 0; i < n; i++) cpu_single_flip(i, apply[i] != 0, A, B, axis); });
+}
+int ref_crop_scale_batch(const float *a, float *b, int n, int c, int ah, int aw, int bh, int bw, const int *boxes) {
+    return guarded([&] {
+        View A({n, c, ah, aw}, a), B({n, c, bh, bw}, b);
+        for (int i = 0; i < n; i++) cpu_single_crop_scale(i, A, B, {boxes[4 * i], boxes[4 * i + 1]}, {boxes[4 * i + 2], boxes[4 * i + 3]}, 0, 0.f);
     });
 }
 

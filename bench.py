@@ -247,7 +247,10 @@ def run_b200_arm(args):
     # torchrun exports OMP_NUM_THREADS=1 as a default of its own, not as the user's choice, so it is overridden; an
     # explicit EDDL_B200_HOST_THREADS wins.
     world_env = max(1, int(os.environ.get("WORLD_SIZE", "1")))
-    host_threads = int(os.environ.get("EDDL_B200_HOST_THREADS", "0")) or max(1, (os.cpu_count() or 1) // world_env)
+    # With several ranks on one host two cores per rank stay free for the NCCL proxy and the Python threads: the OpenMP
+    # workers spin between EDDL's short parallel regions and would otherwise starve them.
+    share = (os.cpu_count() or 1) // world_env
+    host_threads = int(os.environ.get("EDDL_B200_HOST_THREADS", "0")) or max(1, share - 2 if world_env > 1 else share)
     os.environ["OMP_NUM_THREADS"] = str(host_threads)
     os.environ.setdefault("OMP_WAIT_POLICY", "active")
     if args.gpus > 1:
@@ -273,6 +276,7 @@ def run_b200_arm(args):
     net = harness.NetHarness(G, "resnet50", device=local, hw=args.hw, classes=args.classes, optimizer=args.optimizer, lr=0.1, mu=0.9)
     net.set_params(harness.init_weights(net.param_info(), seed=1234, mode="he_normal"))
     if world > 1:
+        ebd.check_same_layout([int(np.prod(s)) for _, s in net.param_info()])      # a host-side check: nothing is enqueued if ranks disagree
         net.broadcast_params()
     # this rank's shard of the global batch, in pinned host memory
     start, end = ebd.shard_rows(batch * world, world, rank)

@@ -7,13 +7,20 @@
 // tensors are packed into one contiguous bucket so the collective is sized for launch
 // latency, not for tensor count.
 #include <nccl.h>
+#include <chrono>
 #include <cstring>
+#include <thread>
 #include <vector>
 #include "common.cuh"
 
 namespace eb {
 void set_comm(DevCtx *c, ncclComm *comm, int nranks, int rank);
 int comm_rank(DevCtx *c);
+cudaStream_t comm_stream_of(DevCtx *c);
+cudaEvent_t avg_event(DevCtx *c, size_t index);
+cudaEvent_t comm_start_event(DevCtx *c);
+void avg_register(DevCtx *c, const void *p, size_t bytes, cudaEvent_t done);
+void *avg_buffer(DevCtx *c, size_t bytes);
 }
 
 namespace {
@@ -62,6 +69,26 @@ __global__ void __launch_bounds__(kBlock) bucket_kernel(const Seg *__restrict__ 
     }
 }
 
+// bucket[off + i] = t[i] for the packed segments of a bucket (in-place ones, bucket_off == ~0, are left alone)
+__global__ void __launch_bounds__(kBlock) bucket_pack_kernel(const Seg *__restrict__ segs, int nseg, float *__restrict__ bucket) {
+    for (int s = blockIdx.y; s < nseg; s += gridDim.y) {
+        const Seg sg = segs[s];
+        if (sg.bucket_off == ~0ull) continue;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < sg.n; i += (size_t)gridDim.x * blockDim.x) bucket[sg.bucket_off + i] = sg.ptr[i];
+    }
+}
+
+// Segments of one bucket after its all-reduce: packed ones are copied back times `scale`, the others (reduced in place)
+// are multiplied where they lie.  bucket_off == ~0 marks an in-place segment.
+__global__ void __launch_bounds__(kBlock) bucket_finish_kernel(const Seg *__restrict__ segs, int nseg, const float *__restrict__ bucket, float scale) {
+    for (int s = blockIdx.y; s < nseg; s += gridDim.y) {
+        const Seg sg = segs[s];
+        const bool packed = sg.bucket_off != ~0ull;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < sg.n; i += (size_t)gridDim.x * blockDim.x)
+            sg.ptr[i] = __fmul_rn(packed ? bucket[sg.bucket_off + i] : sg.ptr[i], scale);
+    }
+}
+
 int launch_scale(DevCtx *cx, cudaStream_t st, float *buf, float v, size_t n) {
     const bool vec = aligned16(buf);
     const size_t n4 = vec ? n / 4 : 0;
@@ -102,6 +129,7 @@ int eddlb200_comm_destroy(int dev) {
     ncclComm_t comm = comm_of(cx);
     if (!comm) return 0;
     cudaStreamSynchronize(st);
+    if (cudaStream_t cs = comm_stream_of(cx)) cudaStreamSynchronize(cs);
     ncclResult_t r = ncclCommDestroy(comm);
     set_comm(cx, nullptr, 1, 0);
     return nccl_status(r, "ncclCommDestroy");
@@ -162,6 +190,107 @@ int eddlb200_allreduce_avg_multi(int dev, float *const *bufs, const size_t *size
     bucket_kernel<true><<<grid, kBlock, 0, st>>>((const Seg *)ws, (int)segs.size(), bucket, 1.0f / N);
     EB_LAUNCH_CHECK("allreduce_avg_multi(unpack)");
     return 0;
+}
+
+int eddlb200_allreduce_avg_multi_async(int dev, float *const *bufs, const size_t *sizes, int ntensors, size_t bucket_bytes) {
+    EB_CTX(dev);
+    EB_REQUIRE(ntensors >= 0 && (ntensors == 0 || (bufs && sizes)), "allreduce_avg_multi_async");
+    if (!comm_of(cx)) return eddlb200_allreduce_avg_multi(dev, bufs, sizes, ntensors);        // one rank: times 1.0f, nothing to overlap
+    cudaStream_t cs = comm_stream_of(cx);
+    cudaEvent_t start = comm_start_event(cx);
+    if (!cs || !start) return set_error(EDDLB200_ENOINIT, "allreduce_avg_multi_async: cannot create the communication stream");
+    if (bucket_bytes < (size_t(1) << 20)) bucket_bytes = size_t(32) << 20;
+    constexpr size_t kInPlaceFloats = size_t(1) << 18;          // tensors of 1 MB or more are reduced where they lie
+    // what has been enqueued on the compute stream so far (the optimizer step) comes first; an earlier averaging of the
+    // same buffers that is still in flight is waited for by the declarations below
+    struct Bucket { int first, last; size_t packed; };
+    std::vector<Bucket> buckets;
+    std::vector<Seg> segs((size_t)ntensors);
+    size_t in_bucket = 0, packed_total = 0, limit = size_t(2) << 20;       // a small first bucket: the first layers are needed first
+    for (int i = 0; i < ntensors; i++) {
+        EB_REQUIRE(bufs[i] || !sizes[i], "allreduce_avg_multi_async");
+        EB_MODIFIES(bufs[i], sizes[i] * sizeof(float));
+        if (buckets.empty() || in_bucket >= limit) { if (!buckets.empty()) limit = bucket_bytes; buckets.push_back(Bucket{i, i, 0}); in_bucket = 0; }
+        Bucket &b = buckets.back();
+        b.last = i;
+        const bool in_place = sizes[i] >= kInPlaceFloats;
+        segs[i] = Seg{bufs[i], (unsigned long long)sizes[i], in_place ? ~0ull : (unsigned long long)packed_total};
+        if (!in_place) { const size_t padded = (sizes[i] + 3) & ~size_t(3); packed_total += padded; b.packed += padded; }
+        in_bucket += sizes[i] * sizeof(float);
+    }
+    if (buckets.empty()) return 0;
+    const size_t seg_bytes = (segs.size() * sizeof(Seg) + 255) & ~size_t(255);
+    char *ws = (char *)avg_buffer(cx, seg_bytes + packed_total * sizeof(float));
+    if (!ws) return set_error((int)cudaErrorMemoryAllocation, "allreduce_avg_multi_async: bucket of %zu bytes", seg_bytes + packed_total * sizeof(float));
+    float *bucket = (float *)(ws + seg_bytes);
+    cudaError_t e = cudaEventRecord(start, st);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, start, 0);
+    // pageable source: staged before the call returns; ordered on the communication stream behind the previous call's kernels
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ws, segs.data(), segs.size() * sizeof(Seg), cudaMemcpyHostToDevice, cs);
+    if (e != cudaSuccess) return cuda_status(e, "allreduce_avg_multi_async(set-up)");
+    const int N = comm_nranks(cx);
+    ncclComm_t comm = comm_of(cx);
+    for (size_t bi = 0; bi < buckets.size(); bi++) {
+        const Bucket &b = buckets[bi];
+        const int nseg = b.last - b.first + 1;
+        const Seg *dsegs = (const Seg *)ws + b.first;
+        size_t largest = 0, first_packed = ~size_t(0);
+        for (int i = b.first; i <= b.last; i++) {
+            if (sizes[i] > largest) largest = sizes[i];
+            if (segs[i].bucket_off != ~0ull && first_packed == ~size_t(0)) first_packed = (size_t)segs[i].bucket_off;
+        }
+        int gy = nseg > 1024 ? 1024 : nseg;
+        int gx = (int)ceil_div(largest, (size_t)kBlock * 8); if (gx < 1) gx = 1; if (gx > 64) gx = 64;
+        dim3 grid(gx, gy);
+        if (b.packed) {
+            // the packed segments of a bucket are contiguous in the bucket buffer
+            bucket_pack_kernel<<<grid, kBlock, 0, cs>>>(dsegs, nseg, bucket);
+            EB_LAUNCH_CHECK("allreduce_avg_multi_async(pack)");
+        }
+        if (int r = nccl_status(ncclGroupStart(), "ncclGroupStart")) return r;
+        ncclResult_t nr = ncclSuccess;
+        if (b.packed) nr = ncclAllReduce(bucket + first_packed, bucket + first_packed, b.packed, ncclFloat, ncclSum, comm, cs);
+        for (int i = b.first; i <= b.last && nr == ncclSuccess; i++)
+            if (segs[i].bucket_off == ~0ull && sizes[i]) nr = ncclAllReduce(bufs[i], bufs[i], sizes[i], ncclFloat, ncclSum, comm, cs);
+        const ncclResult_t ne = ncclGroupEnd();
+        if (int r = nccl_status(nr != ncclSuccess ? nr : ne, "ncclAllReduce")) return r;
+        count_launch(cx);
+        bucket_finish_kernel<<<grid, kBlock, 0, cs>>>(dsegs, nseg, bucket, 1.0f / N);
+        EB_LAUNCH_CHECK("allreduce_avg_multi_async(finish)");
+        cudaEvent_t done = avg_event(cx, bi);
+        if (!done) return set_error(EDDLB200_ENOINIT, "allreduce_avg_multi_async: cannot create an event");
+        if ((e = cudaEventRecord(done, cs)) != cudaSuccess) return cuda_status(e, "allreduce_avg_multi_async(record)");
+        for (int i = b.first; i <= b.last; i++) if (sizes[i]) avg_register(cx, bufs[i], sizes[i] * sizeof(float), done);
+    }
+    return 0;
+}
+
+int eddlb200_comm_check(int dev, int wait_ms) {
+    EB_CTX_KEEP_PENDING(dev);
+    ncclComm_t comm = comm_of(cx);
+    if (!comm) return 0;
+    cudaStream_t cs = comm_stream_of(cx);
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        ncclResult_t async = ncclSuccess;
+        const ncclResult_t q = ncclCommGetAsyncError(comm, &async);
+        if (q != ncclSuccess || (async != ncclSuccess && async != ncclInProgress)) {
+            // the communicator is unusable from here on: abort it so that no later call waits on it
+            const int r = nccl_status(q != ncclSuccess ? q : async, "ncclCommGetAsyncError");
+            ncclCommAbort(comm);
+            set_comm(cx, nullptr, 1, 0);
+            return r;
+        }
+        const cudaError_t a = cudaStreamQuery(st), b = cs ? cudaStreamQuery(cs) : cudaSuccess;
+        if (a != cudaErrorNotReady && b != cudaErrorNotReady) {
+            if (a != cudaSuccess) return cuda_status(a, "comm_check");
+            if (b != cudaSuccess) return cuda_status(b, "comm_check");
+            return 0;
+        }
+        if (wait_ms >= 0 && std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() >= wait_ms)
+            return set_error(EDDLB200_ETIMEOUT, "collectives on device %d still running after %d ms", dev, wait_ms);
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
 }
 
 int eddlb200_broadcast(int dev, float *buf, size_t n, int root) {

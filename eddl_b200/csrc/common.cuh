@@ -109,21 +109,35 @@ struct LossCache {
 LossCache &loss_cache(DevCtx *c);
 }  // namespace eb
 
+namespace eb {
+// Buffers with an averaging collective in flight on the communication stream (avg_weights_distributed runs there, bucket by
+// bucket, while the compute stream goes on with the next step).  Every declared access of an entry point to such a buffer
+// first makes the compute stream wait for the bucket's event, so a layer's kernels start as soon as ITS parameters have
+// been averaged, not when the whole collective is done.
+bool avg_any(DevCtx *c);
+int avg_settle(DevCtx *c, cudaStream_t st, const void *p, size_t bytes);
+}  // namespace eb
+
+#define EB_SETTLE(p, bytes)                                                             \
+    do { if ((p) && eb::avg_any(cx)) { if (int r__ = eb::avg_settle(cx, st, (p), (bytes))) return r__; } } while (0)
 #define EB_READS(p, bytes)                                                              \
     do {                                                                                \
+        EB_SETTLE(p, bytes);                                                            \
         if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_read(cx, st, (p), (bytes))) return r__; } \
     } while (0)
 #define EB_WRITES(p, bytes)                                                             \
     do {                                                                                \
+        EB_SETTLE(p, bytes);                                                            \
         if ((p) && eb::watch_any(cx)) eb::note_write(cx, (p), (bytes));                 \
         if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_write(cx, st, (p), (bytes))) return r__; } \
     } while (0)
 // an accumulated-into destination whose deferred zeros are dealt with separately (lz_take): tell the observers only
 #define EB_NOTES(p, bytes)                                                              \
-    do { if ((p) && eb::watch_any(cx)) eb::note_write(cx, (p), (bytes)); } while (0)
+    do { EB_SETTLE(p, bytes); if ((p) && eb::watch_any(cx)) eb::note_write(cx, (p), (bytes)); } while (0)
 // read-modify-write of a destination: zeros owed to it are written first, and observers of the range are told
 #define EB_MODIFIES(p, bytes)                                                           \
     do {                                                                                \
+        EB_SETTLE(p, bytes);                                                            \
         if ((p) && eb::watch_any(cx)) eb::note_write(cx, (p), (bytes));                 \
         if ((p) && eb::lz_any(cx)) { if (int r__ = eb::lz_read(cx, st, (p), (bytes))) return r__; } \
     } while (0)

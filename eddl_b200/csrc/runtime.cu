@@ -52,6 +52,13 @@ struct DevCtx {
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev_peer = nullptr, ev_peer_done = nullptr;
     cudaEvent_t ev_handoff = nullptr;        // created with the context: orders a caller's stream after the compute stream
+    // averaging in flight on the communication stream: start address -> (bytes, event of its bucket)
+    struct AvgRange { size_t bytes; cudaEvent_t done; };
+    std::map<uintptr_t, AvgRange> avg_pending;
+    cudaStream_t comm_stream = nullptr;
+    std::vector<cudaEvent_t> avg_events;     // one per bucket, reused call after call
+    cudaEvent_t ev_comm_start = nullptr;
+    void *avg_bucket = nullptr; size_t avg_bucket_bytes = 0;     // packed small tensors + segment table of the asynchronous averaging
 };
 
 static DevCtx g_ctx[EDDLB200_MAX_DEVICES];
@@ -143,6 +150,49 @@ void *scratch(DevCtx *c, size_t bytes) {
 
 // ---- write observers ----------------------------------------------------------------------------------
 LossCache &loss_cache(DevCtx *c) { return c->loss; }
+
+// ---- averaging in flight ------------------------------------------------------------------------------
+bool avg_any(DevCtx *c) { return !c->avg_pending.empty(); }
+int avg_settle(DevCtx *c, cudaStream_t st, const void *p, size_t bytes) {
+    if (c->avg_pending.empty() || !bytes) return 0;
+    const uintptr_t lo = (uintptr_t)p, hi = lo + bytes;
+    auto it = c->avg_pending.upper_bound(lo);
+    if (it != c->avg_pending.begin()) { auto prev = std::prev(it); if (prev->first + prev->second.bytes > lo) it = prev; }
+    while (it != c->avg_pending.end() && it->first < hi) {
+        cudaError_t e = cudaStreamWaitEvent(st, it->second.done, 0);
+        if (e != cudaSuccess) return cuda_status(e, "averaging(wait for bucket)");
+        it = c->avg_pending.erase(it);
+    }
+    return 0;
+}
+// used by the collectives (comm.cu)
+cudaStream_t comm_stream_of(DevCtx *c) {
+    if (!c->comm_stream && cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking) != cudaSuccess) c->comm_stream = nullptr;
+    return c->comm_stream;
+}
+cudaEvent_t avg_event(DevCtx *c, size_t index) {
+    while (c->avg_events.size() <= index) {
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        c->avg_events.push_back(e);
+    }
+    return c->avg_events[index];
+}
+cudaEvent_t comm_start_event(DevCtx *c) {
+    if (!c->ev_comm_start && cudaEventCreateWithFlags(&c->ev_comm_start, cudaEventDisableTiming) != cudaSuccess) c->ev_comm_start = nullptr;
+    return c->ev_comm_start;
+}
+void avg_register(DevCtx *c, const void *p, size_t bytes, cudaEvent_t done) { c->avg_pending[(uintptr_t)p] = DevCtx::AvgRange{bytes, done}; }
+// persistent buffer of the asynchronous averaging (the shared scratch arena may be re-carved by compute kernels meanwhile)
+void *avg_buffer(DevCtx *c, size_t bytes) {
+    if (bytes <= c->avg_bucket_bytes) return c->avg_bucket;
+    if (c->comm_stream) cudaStreamSynchronize(c->comm_stream);
+    if (c->avg_bucket) cudaFree(c->avg_bucket);
+    c->avg_bucket = nullptr; c->avg_bucket_bytes = 0;
+    if (cudaMalloc(&c->avg_bucket, bytes + bytes / 4) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    c->avg_bucket_bytes = bytes + bytes / 4;
+    return c->avg_bucket;
+}
 bool watch_any(DevCtx *c) { return !c->watch.empty(); }
 template <typename V>
 static void watch_visit(DevCtx *c, const void *p, size_t bytes, V visit) {
@@ -312,6 +362,7 @@ int eddlb200_free(int dev, void *p) {
     size_t sz = it->second;
     cx->live.erase(it);
     cx->bytes_in_use -= sz;
+    EB_SETTLE(p, sz);           // a block handed out again must not still be the operand of a collective
     lz_forget(cx, p, sz);
     watch_forget(cx, p, sz);
     // All work of this library runs on one stream per device, so a block handed out
@@ -446,6 +497,7 @@ int eddlb200_stream(int dev, void **s) {
 int eddlb200_sync(int dev) {
     EB_CTX(dev);
     if (int r = cuda_status(cudaStreamSynchronize(st), "eddlb200_sync")) return r;
+    if (cx->comm_stream) { if (int r = cuda_status(cudaStreamSynchronize(cx->comm_stream), "eddlb200_sync(communication stream)")) return r; cx->avg_pending.clear(); }
     int flag = 0;
     if (int r = conv_tc_status(dev, st, &flag)) return cuda_status((cudaError_t)r, "eddlb200_sync");
     if (flag) return set_error(EDDLB200_ETIMEOUT, "a tensor-core convolution kernel gave up waiting on a pipeline barrier");

@@ -29,15 +29,46 @@ def env_world():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
 
 
-def rendezvous(backend="gloo"):
-    """Initialises torch.distributed from the torchrun environment; returns (rank, world, local_rank)."""
+class RankFailure(RuntimeError):
+    """A rank is missing, or the ranks do not agree on what they are about to exchange.  Raised on the host, before any
+    collective has been enqueued on a GPU."""
+
+
+def rendezvous(backend="gloo", timeout_s=None):
+    """Initialises torch.distributed from the torchrun environment; returns (rank, world, local_rank).
+    A rank that never joins ends the rendezvous of the others with RankFailure after `timeout_s` seconds
+    (default: EDDL_B200_RENDEZVOUS_TIMEOUT or 600)."""
     rank, world, local = env_world()
     if world > 1:
+        import datetime
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if timeout_s is None:
+            timeout_s = float(os.environ.get("EDDL_B200_RENDEZVOUS_TIMEOUT", "600"))
         if not dist.is_initialized():
-            dist.init_process_group(backend=backend, rank=rank, world_size=world)
+            try:
+                dist.init_process_group(backend=backend, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
+            except Exception as e:          # torch raises DistStoreError / DistNetworkError / RuntimeError depending on where it gave up
+                raise RankFailure("rank %d: rendezvous of %d ranks did not complete within %.0f s (%s)" % (rank, world, timeout_s, type(e).__name__)) from e
     return rank, world, local
+
+
+def check_same_layout(sizes, what="parameter tensors"):
+    """Every rank must be about to exchange the same sequence of tensor sizes: a collective whose ranks disagree on the
+    byte count never completes.  Compared over gloo on the host; RankFailure on EVERY rank when they differ."""
+    rank, world, _ = env_world()
+    if world == 1:
+        return
+    import zlib
+    import torch
+    import torch.distributed as dist
+    sizes = [int(s) for s in sizes]
+    mine = torch.tensor([len(sizes), sum(sizes), zlib.crc32(repr(sizes).encode())], dtype=torch.int64)
+    every = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    rows = [tuple(int(v) for v in t) for t in every]
+    if len(set(rows)) != 1:
+        raise RankFailure("%s differ between ranks (count, floats, checksum per rank): %s" % (what, rows))
 
 
 def broadcast_bytes(payload, nbytes, src=0):

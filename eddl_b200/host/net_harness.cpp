@@ -151,6 +151,7 @@ int ebh_create(const char *config, int hw, int classes, int device, int threads,
         else if (o == "adam") opt = adam(lr);
 #ifdef cGPU
         else if (o == "sgd_fused") opt = new eddl_b200::SGDFused(lr, mu);
+        else if (o == "sgd_fused_gradavg") { auto *s = new eddl_b200::SGDFused(lr, mu); s->average_gradients = true; opt = s; }
         else if (o == "adam_fused") opt = new eddl_b200::AdamFused(lr, 0.9f, 0.999f, 0.000001f);      // eddl::adam's defaults
 #endif
         else throw std::runtime_error("unknown optimizer '" + o + "'");
@@ -352,6 +353,7 @@ int ebh_broadcast_params(int id) { return guarded([&] { eddl_b200::broadcast_par
 int ebh_avg_weights(int id, int curr_batch, int batches_per_avg) {
     return guarded([&] { eddl_b200::avg_weights_distributed(get(id)->net, curr_batch, batches_per_avg); });
 }
+int ebh_check_distributed(int wait_ms) { return guarded([&] { eddl_b200::check_distributed(wait_ms); }); }
 int ebh_sync(int id) { return guarded([&] { Handle *h = get(id); eddlb200_shim_flush(h->dev); if (eddlb200_sync(h->dev)) throw std::runtime_error(eddlb200_last_error()); }); }
 #endif
 

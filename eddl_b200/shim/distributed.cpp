@@ -68,13 +68,25 @@ void avg_weights_distributed(Net *net, int curr_batch, int batches_per_avg) {
     std::vector<float *> ptrs; std::vector<size_t> sizes; int dev;
     collect_params(net, ptrs, sizes, dev);
     eddlb200_shim_flush(dev);
-    ok(eddlb200_allreduce_avg_multi(dev, ptrs.data(), sizes.data(), (int)ptrs.size()), "avg_weights_distributed");
+    // layers come in forward order, so the buckets do too: the collective runs on its own stream and the next step's
+    // forward pass waits bucket by bucket (EDDL_B200_AVG_ASYNC=0: one bucket on the compute stream)
+    static const bool async = !(getenv("EDDL_B200_AVG_ASYNC") && getenv("EDDL_B200_AVG_ASYNC")[0] == '0');
+    if (async) ok(eddlb200_allreduce_avg_multi_async(dev, ptrs.data(), sizes.data(), (int)ptrs.size(), 0), "avg_weights_distributed");
+    else ok(eddlb200_allreduce_avg_multi(dev, ptrs.data(), sizes.data(), (int)ptrs.size()), "avg_weights_distributed");
+}
+
+void check_distributed(int wait_ms) {
+    if (g_dev >= 0 && g_nranks > 1) ok(eddlb200_comm_check(g_dev, wait_ms), "check_distributed");
 }
 
 SGDFused::SGDFused(float lr, float momentum, float weight_decay, bool nesterov) : SGD(lr, momentum, weight_decay, nesterov) {}
 
-Optimizer *SGDFused::clone() { SGDFused *n = new SGDFused(lr, mu, weight_decay, nesterov); n->clip_val = clip_val; return n; }
-Optimizer *SGDFused::share() { SGDFused *n = new SGDFused(lr, mu, weight_decay, nesterov); n->orig = this; n->isshared = true; n->clip_val = clip_val; return n; }
+Optimizer *SGDFused::clone() { SGDFused *n = new SGDFused(lr, mu, weight_decay, nesterov); n->clip_val = clip_val; n->average_gradients = average_gradients; return n; }
+Optimizer *SGDFused::share() {
+    SGDFused *n = new SGDFused(lr, mu, weight_decay, nesterov);
+    n->orig = this; n->isshared = true; n->clip_val = clip_val; n->average_gradients = average_gradients;
+    return n;
+}
 
 void SGDFused::applygrads(int batch) {
     if (isshared) { orig->applygrads(batch); return; }
@@ -98,6 +110,13 @@ void SGDFused::applygrads(int batch) {
     }
     if (p.empty()) return;
     eddlb200_shim_flush(dev);
+    if (average_gradients && g_nranks > 1) {
+        // gradient averaging: every rank applies the same averaged gradient, so parameters and momentum stay identical on
+        // all ranks without averaging the weights afterwards
+        std::vector<float *> gm(g.size());
+        for (size_t i = 0; i < g.size(); i++) gm[i] = const_cast<float *>(g[i]);
+        ok(eddlb200_allreduce_avg_multi(dev, gm.data(), sizes.data(), (int)gm.size()), "SGDFused::applygrads(average gradients)");
+    }
     ok(eddlb200_sgd_momentum_multi(dev, p.data(), g.data(), m.data(), sizes.data(), (int)p.size(), lr, mu), "SGDFused::applygrads");
 }
 

@@ -297,6 +297,19 @@ int eddlb200_comm_destroy(int dev);
 int eddlb200_comm_info(int dev, int *nranks, int *rank);
 int eddlb200_allreduce_avg(int dev, float *buf, size_t n);            /* in place */
 int eddlb200_allreduce_avg_multi(int dev, float *const *bufs, const size_t *sizes, int ntensors);
+/* The same averaging, overlapped with whatever the compute stream does next: the tensors are cut, in the order given, into
+ * buckets (a first one of about 2 MB, then `bucket_bytes` each; 0 = 32 MB); each bucket is all-reduced on a separate
+ * communication stream -- tensors of 1 MB or more where they lie, the small ones packed into one message -- and scaled by
+ * 1.0f/N there.  The call returns at once.  Any later entry point of this library that reads or writes one of the tensors
+ * first makes the compute stream wait for THAT tensor's bucket, so with the parameters given in forward order the next
+ * step's first layers start while the last layers are still being averaged.  Code outside the library must call
+ * eddlb200_sync before it touches the tensors. */
+int eddlb200_allreduce_avg_multi_async(int dev, float *const *bufs, const size_t *sizes, int ntensors, size_t bucket_bytes);
+/* Health of the communicator (ncclCommGetAsyncError) and progress of the collectives enqueued so far: 0 = all done;
+ * EDDLB200_ETIMEOUT = still running after wait_ms milliseconds (wait_ms < 0 waits without limit); EDDLB200_ENCCL = NCCL
+ * reported an asynchronous error, in which case the communicator has been aborted and this rank is back to N = 1.  The
+ * wait is a host-side poll: nothing is left waiting on the GPU by this call. */
+int eddlb200_comm_check(int dev, int wait_ms);
 int eddlb200_broadcast(int dev, float *buf, size_t n, int root);
 /* Gradient averaging fused with the SGD-momentum step of an equal-size parameter
  * buffer: g <- allreduce(g)/N ; m = lr*g + mu*m ; p -= m. */

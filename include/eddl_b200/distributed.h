@@ -29,11 +29,24 @@ void broadcast_params_distributed(Net *net);
 // (the trigger of Net::train_batch: tr_batches % lsb == 0).
 void avg_weights_distributed(Net *net, int curr_batch, int batches_per_avg);
 
+// Health check of the communicator and of the averaging collectives in flight: throws std::runtime_error when NCCL reports
+// an asynchronous error (the communicator is then aborted) or when they are still running after wait_ms milliseconds
+// (< 0: no limit).  A host-side poll; nothing waits on the GPU.
+void check_distributed(int wait_ms);
+
+// Averaged parameters live in the replica on the GPU; the coordinator copy (net->layers[*]->params on the host) is not
+// refreshed by avg_weights_distributed or broadcast_params_distributed.  Read parameters through eddl::get_parameters (or
+// Net::save), which collect the device copies first.
+
 // SGD with momentum whose applygrads is ONE multi-tensor kernel launch instead of two
 // elementwise launches per parameter tensor (src/optimizers/optim_sgd.cpp:68-89); results are
 // bit-identical to SGD::applygrads.  Use it as eddl::build(net, new eddl_b200::SGDFused(lr, mu), ...).
 class SGDFused : public SGD {
 public:
+    // true: the gradients are averaged across ranks (all-reduce, times 1.0f/N) before the step, so that every rank applies
+    // the same update and neither parameters nor momentum need averaging afterwards; do not combine it with
+    // avg_weights_distributed.  For SGD with momentum this equals weight averaging up to rounding (the update is linear).
+    bool average_gradients = false;
     explicit SGDFused(float lr = 0.01f, float momentum = 0.0f, float weight_decay = 0.0f, bool nesterov = false);
     Optimizer *clone() override;
     Optimizer *share() override;

@@ -75,3 +75,68 @@ def test_two_gloo_ranks(tmp_path):
     want = orc.sync_weights(np.stack(ws))
     np.testing.assert_allclose(outs[0]["avg"], want[:8], rtol=1e-6)
     assert outs[0]["avg"] == outs[1]["avg"] and abs(outs[0]["avg_sum"] - float(want.astype(np.float64).sum())) < 1e-4
+
+
+LAYOUT_WORKER = textwrap.dedent("""
+    import os, sys
+    sys.path.insert(0, %r)
+    from eddl_b200 import dist as ebd
+    rank, world, local = ebd.rendezvous("gloo", timeout_s=60)
+    ebd.check_same_layout([3, 5, 7])                               # agreed: passes on both
+    try:
+        ebd.check_same_layout([3, 5, 7] if rank == 0 else [3, 5, 8])
+        print("NOT DETECTED")
+    except ebd.RankFailure as e:
+        print("detected on rank %%d" %% rank)
+    ebd.barrier()
+""")
+
+
+def _spawn(script, world, ranks, port, extra_env=None):
+    procs = []
+    for r in ranks:
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="1")
+        env.update(extra_env or {})
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    return procs
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_ranks_that_disagree_on_the_tensor_sizes_are_stopped_on_the_host(tmp_path):
+    """A size mismatch between ranks is found by a host-side comparison over gloo and raised on every rank, before any
+    collective is enqueued (a mismatched collective would wait for ever)."""
+    script = tmp_path / "layout.py"
+    script.write_text(LAYOUT_WORKER % ROOT)
+    for p in _spawn(script, 2, (0, 1), _free_port()):
+        o, e = p.communicate(timeout=180)
+        assert p.returncode == 0, e[-2000:]
+        assert "detected on rank" in o and "NOT DETECTED" not in o
+
+
+LONELY_WORKER = textwrap.dedent("""
+    import os, sys, time
+    sys.path.insert(0, %r)
+    from eddl_b200 import dist as ebd
+    t0 = time.time()
+    try:
+        ebd.rendezvous("gloo", timeout_s=4)
+        print("JOINED?")
+    except ebd.RankFailure as e:
+        print("gave up after %%.1f s" %% (time.time() - t0))
+""")
+
+
+def test_a_rank_that_never_joins_ends_the_rendezvous_with_an_error(tmp_path):
+    """World size 2 but only rank 0 is started: the rendezvous gives up after its deadline with RankFailure instead of
+    waiting for ever (failure made on the host; no GPU involved)."""
+    script = tmp_path / "lonely.py"
+    script.write_text(LONELY_WORKER % ROOT)
+    (p,) = _spawn(script, 2, (0,), _free_port())
+    o, e = p.communicate(timeout=120)
+    assert p.returncode == 0, e[-2000:]
+    assert "gave up after" in o and "JOINED?" not in o

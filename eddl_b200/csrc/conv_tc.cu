@@ -60,7 +60,8 @@ constexpr int NTHREADS = NPROD + 32 + NEPI + 32;     // + warp 13: L2 prefetch o
 // TMA-fed forward / backward-data kernels run a second set of four epilogue warps (warps 14-17): their short-reduction,
 // output-heavy layers are bound by the epilogue's chain of tensor-memory reads, and two warps per lane quarter halve it
 constexpr int NTHREADS_ATMA = NTHREADS + NEPI;
-constexpr int threads_of(int tma) { return tma == 1 ? NTHREADS_ATMA : NTHREADS; }
+constexpr int threads_of(int tma) { return (tma == 1 || tma == 3) ? NTHREADS_ATMA : NTHREADS; }
+constexpr int SLAB_PX = 256;        // pixels per channel of a raw slab (3x3 TMA-fed kernels): 128 rows + a halo of W + 1 either side + alignment
 constexpr int PF_AHEAD = 8;         // K-blocks the prefetch warp may run ahead of the producers
 constexpr int INVALID_Y = -20000;
 constexpr int NMAIN = 3;             // rotating hi*hi accumulators; a fourth holds the cross terms
@@ -93,6 +94,8 @@ struct TcParams {
     // space is images x chunks_per_image x 32 (rows past the end of an image are zero on the way in and clipped on the way out)
     int chunks_per_image, images;
     int reduce_out;         // the output is added into (TMA reduce) instead of stored
+    int img_w;              // STMA: width of the image plane (the halo of a slab is img_w + 1 pixels either side)
+    int tap_sign;           // STMA: +1 forward (tap (r, s) reads pixel + (r-1, s-1)), -1 backward-data (pixel + (1-r, 1-s))
     int raw_hi;             // WTMA: leave the landed fp32 values as the hi plane (the tensor core reads only their upper 19 bits)
     alignas(64) CUtensorMap mapA;
     alignas(64) CUtensorMap mapOut;
@@ -262,7 +265,8 @@ struct Layout {
 // zeros and add nothing), and the producer warps only split what has landed into its hi / lo planes, in place.
 template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, int TMA = 0>
 __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __grid_constant__ TcParams P) {
-    constexpr bool ATMA = TMA == 1, WTMA = TMA == 2;
+    constexpr bool STMA = TMA == 3;                      // 3x3 stride-1 pad-1 layers fed from raw slabs (see load_row)
+    constexpr bool ATMA = TMA == 1 || STMA, WTMA = TMA == 2;
     static_assert(!WTMA || (!WGRAD && BGATHER), "the TMA-fed backward-weight variant replaces the both-operands gather");
     constexpr bool SPLIT3 = PREC != 1;                   // operands staged as hi / lo planes
     constexpr bool CROSS_BF16 = PREC == 2 && !WGRAD && !BGATHER;     // cross terms as one bf16 MMA chain
@@ -303,7 +307,8 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
         for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, NPROD / 64 + (B_TMA ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); }
         for (int s = 0; s < 2; s++) { mbar_init(bar_acc_full + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, (ATMA ? 2 : 1) * NEPI / 32); }
         // a raw tile is filled by one expect_tx arrival plus the TMA bytes, and released by the four warps of the group that read it
-        for (int s = 0; s < RAWS; s++) { mbar_init(bar_raw_full + 8 * s, 1); mbar_init(bar_raw_empty + 8 * s, 4); }
+        // (a slab serves nine K-blocks shared by both groups: all eight producer warps release it)
+        for (int s = 0; s < RAWS; s++) { mbar_init(bar_raw_full + 8 * s, 1); mbar_init(bar_raw_empty + 8 * s, STMA ? 8 : 4); }
         if constexpr (WTMA) for (int s = 0; s < STAGES; s++) mbar_init(bar_raw_full + 8 * s, 1);       // "landed": one expect_tx arrival + the bytes
         *abort_flag = 0;
         *progress = 0;
@@ -441,8 +446,40 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             int2 myRow = make_int2(0, INVALID_Y << 16);
             int ry = INVALID_Y, rx = 0, row_tile = -1;
 
+            // STMA state of this thread's row: position of the row inside the slab for the centre tap, and whether the row's
+            // pixel sits on the left / right edge of the image (its horizontal neighbours then lie in another image row)
+            int slab_pos = 0; bool edge_l = false, edge_r = false;
             auto load_row = [&](int t, int kb0, int it, int gseq) -> bool {
-                if constexpr (ATMA) {
+                if constexpr (STMA) {
+                    // K-blocks come as (32-channel group, tap): the nine taps of a group read the SAME raw slab
+                    // [32 channels][SLAB_PX pixels] -- the tile's 128 pixels plus a halo of img_w + 1 pixels either side --
+                    // each at its own shift, so the activations cross from L2 to shared memory once instead of nine times.
+                    // Pixels before the first / after the last image row are outside the tensor and arrive as zeros; a
+                    // horizontal neighbour outside the row is masked here.
+                    const int mn = t % tiles_mn;
+                    if (mn != row_tile) {
+                        row_tile = mn;
+                        const int tile_in_image = (mn % P.tiles_m) % (P.chunks_per_image / 4);
+                        const int t0 = tile_in_image * BM;
+                        const int base = ((t0 - P.img_w - 1 + 4096) & ~3) - 4096;         // rounded down to 16 bytes, may be negative
+                        slab_pos = t0 - base + arow;
+                        const int q = (t0 + arow) % P.img_w;
+                        edge_l = q == 0; edge_r = q == P.img_w - 1;
+                    }
+                    const int ss = gseq / 9, tap = gseq - 9 * ss, rs = ss & 1;
+                    if (!mbar_wait_warp(bar_raw_full + 8 * rs, (ss >> 1) & 1, abort_flag)) return false;
+                    const int r = tap / 3, s = tap - 3 * r;
+                    const int dr = P.tap_sign * (r - 1), dc = P.tap_sign * (s - 1);
+                    const bool masked = (dc < 0 && edge_l) || (dc > 0 && edge_r);
+                    const float *raw = (const float *)(raw_base + rs * (2 * L::RAW_BYTES)) + slab_pos + dr * P.img_w + dc;
+#pragma unroll
+                    for (int i = 0; i < BK; i++) av[i] = masked ? 0.f : raw[i * SLAB_PX];
+                    if (gseq + 2 > 9 * ss + 8) {            // this group's last K-block of the slab
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_raw_empty + 8 * rs);
+                    }
+                    return true;
+                } else if constexpr (ATMA) {
                     // this thread's row of K-block number gseq of the CTA's sequence: 32 values, one per channel, out of the raw
                     // tile TMA has delivered (chunk = warp of the group, pixel = lane: conflict-free 128-byte reads)
                     const int rs = gseq % RAWS;
@@ -757,6 +794,25 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                 }
             }
             __syncwarp();
+        } else if constexpr (STMA) {
+            // lane 0 feeds the slab ring: one box of [32 channels][SLAB_PX pixels] per (tile, channel group), two slabs deep
+            if (lane == 0) {
+                int ss = 0;
+                const int tiles_per_image = P.chunks_per_image / 4;
+                for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
+                    int kb0, nkb; kb_range(t, kb0, nkb);
+                    const int tm = (t % tiles_mn) % P.tiles_m;
+                    const int img = tm / tiles_per_image, t0 = (tm % tiles_per_image) * BM;
+                    const int base = ((t0 - P.img_w - 1 + 4096) & ~3) - 4096;
+                    for (int cg = 0; cg < nkb / 9; cg++, ss++) {
+                        const int rs = ss & 1;
+                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((ss >> 1) & 1) ^ 1, abort_flag)) { failed = true; break; }
+                        mbar_expect_tx(bar_raw_full + 8 * rs, (uint32_t)(2 * L::RAW_BYTES));
+                        tma_load_3d(smem_u32(raw_base + rs * (2 * L::RAW_BYTES)), &P.mapA, base, (kb0 / 9 + cg) * BK, img, bar_raw_full + 8 * rs);
+                    }
+                }
+            }
+            __syncwarp();
         } else if constexpr (ATMA) {
             // ATMA: this warp's lane 0 feeds the raw activation ring: per K-block four boxes of [32 channels][32 pixels], one per
             // 32-pixel chunk of the tile's rows (a chunk lies inside one image; what lies past the image, the channels or the
@@ -1040,6 +1096,14 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
             }
         } else if (i < (long long)T.M_total + T.K_pad) {
             const int k = (int)(i - T.M_total);
+            if (T.check == 5) {
+                // slab-fed 3x3 kernels: k = (32-channel group, tap, channel in group); only the weight offsets are needed
+                const int cg = k / (9 * BK), rem = k - cg * 9 * BK, tap = rem / BK, ch = cg * BK + (rem - tap * BK);
+                const int nch = T.mode == 0 ? g.c : g.k;
+                T.kA[k] = make_int2(0, 0); T.kC[k] = 0;
+                T.kB[k] = ch >= nch ? -1 : (T.mode == 0 ? ch * rs + tap : ch * g.c * rs + tap);
+                continue;
+            }
             if (k >= T.K_total) { T.kA[k] = make_int2(0, T.check == 1 ? 31 : pack_yx(INVALID_Y, 0)); T.kC[k] = 31; T.kB[k] = -1; continue; }
             if (T.mode == 0) {              // (c, r, s)
                 const int c = k / rs, t = k - c * rs, r = t / g.kc, s = t - r * g.kc;
@@ -1062,7 +1126,7 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
             T.kC[k] = T.check == 0 ? ka.x : T.check == 1 ? (int)(((unsigned)ka.x << 5) | (unsigned)ka.y) : 0;
         } else {
             const int n = (int)(i - T.M_total - T.K_pad);
-            if (T.mode == 0) T.rowB[n] = n * T.K_total;         // filter row of w[f][c*r*s]
+            if (T.mode == 0) T.rowB[n] = n * g.c * rs;          // filter row of w[f][c*r*s]
             else if (T.mode == 1) T.rowB[n] = n * rs;           // in-channel c of w[f][c][r][s]
             else if (T.mode == 3) T.rowB[n] = n;                // (c,r,s) column of w[f][c*r*s]
             else T.rowB[n] = n * pq;                            // filter plane of dy[n][f][p*q]
@@ -1156,7 +1220,7 @@ __global__ void __launch_bounds__(256) pack_b_multi_kernel(const __grid_constant
 
 template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, int TMA = 0>
 int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
-    using L = Layout<BN_, PREC != 1, TMA == 1>;
+    using L = Layout<BN_, PREC != 1, TMA == 1 || TMA == 3>;
     static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
     bool &configured = configured_dev[dev];
     if (!configured) {
@@ -1180,10 +1244,10 @@ int launch_bn(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int bn,
 // the box lands in shared memory as [32 channels][32 pixels].  Needs a 16-byte aligned base and pixels % 4 == 0.
 // With swizzle128 the box (box_rows channels x 32 pixels = box_rows rows of 128 bytes) lands in the K-major SWIZZLE_128B layout
 // of an MMA operand whose k runs along the pixels.
-bool encode_plane_map(CUtensorMap *map, const float *base, int pixels, int channels, int images, int box_rows = 32, bool swizzle128 = false) {
+bool encode_plane_map(CUtensorMap *map, const float *base, int pixels, int channels, int images, int box_rows = 32, bool swizzle128 = false, int box_px = 32) {
     const cuuint64_t dims[3] = {(cuuint64_t)pixels, (cuuint64_t)channels, (cuuint64_t)images};
     const cuuint64_t strides[2] = {(cuuint64_t)pixels * 4, (cuuint64_t)pixels * channels * 4};
-    const cuuint32_t box[3] = {32, (cuuint32_t)box_rows, 1}, elem[3] = {1, 1, 1};
+    const cuuint32_t box[3] = {(cuuint32_t)box_px, (cuuint32_t)box_rows, 1}, elem[3] = {1, 1, 1};
     // the driver entry point is looked up at run time: the library must load (and refuse work) on a machine without a driver
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1202,6 +1266,7 @@ bool encode_plane_map(CUtensorMap *map, const float *base, int pixels, int chann
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 int g_conv_tma = 2;            // eddlb200_set_option("conv_tma", 0 off / 1 stores only / 2 stores and adds)
+int g_conv_tma3 = 1;           // eddlb200_set_option("conv_tma_3x3", 0 / 1)
 int g_conv_wtma = 2;           // eddlb200_set_option("conv_tma_wgrad", 0 off / 1 on / 2 on, landed values used as the hi plane as they are)
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
@@ -1342,7 +1407,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         if (!encode_plane_map(&P.mapA, srcA, g.oh * g.ow, g.c, g.n, BM, true) || !encode_plane_map(&P.mapOut, srcB, g.oh * g.ow, g.k, g.n, w_bn, true)) wtma = false;
     }
     if (wtma) { T.check = 4; T.K_total = 0; T.K_pad = 0; }             // no k tables; check 4 keeps these tables apart in the cache
-    const int k_pad = wtma ? g.n * w_chunks * BK : T.K_pad;
+    int k_pad = wtma ? g.n * w_chunks * BK : T.K_pad;
     // any backward-weight: dy alone has that property whatever the filter and stride
     const bool b_vector = mode == 2 && (g.oh * g.ow) % 4 == 0 && T.K_total % BK == 0 && aligned16(srcB);
     // forward / backward-data of a 1x1 stride-1 unpadded convolution: rows are pixels of one image plane, k is the channel,
@@ -1359,7 +1424,19 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         if (!encode_plane_map(&P.mapA, srcA, pq_, a_channels, g.n) || !encode_plane_map(&P.mapOut, out, pq_, o_channels, g.n)) atma = false;
     }
     if (atma) { T.check = 3; T.M_total = 0; allow_split = false; }      // no row tables; check 3 keeps these tables apart in the cache
-    const int m_rows = atma ? g.n * chunks * 32 : T.M_total;
+    // forward / backward-data of a 3x3 stride-1 "same" convolution: K-blocks ordered (channel group, tap), the nine taps of a group
+    // read one raw slab of the plane (tile + halo) that TMA delivers; tiles are 128 consecutive pixels of ONE image
+    const int tiles_per_image = (pq_ + BM - 1) / BM;
+    bool stma = g_conv_tma > 0 && (mode == 0 || mode == 1) && g.kr == 3 && g.kc == 3 && g.sr == 1 && g.sc == 1 && g.pt == 1 && g.pl == 1 &&
+                g.ih == g.oh && g.iw == g.ow && g.iw >= 3 && 2 * g.iw + BM + 5 <= SLAB_PX && pq_ % 4 == 0 && pq_ >= 64 && a_channels >= 32 && o_channels >= 32 &&
+                aligned16(srcA) && aligned16(out) && (long long)g.n * tiles_per_image * BM < 0x7fffffffLL && (mode == 0 || out_zero || g_conv_tma > 1) &&
+                g_conv_tma3;
+    if (stma) {
+        P.chunks_per_image = 4 * tiles_per_image; P.images = g.n; P.img_w = g.iw; P.tap_sign = mode == 0 ? 1 : -1;
+        if (!encode_plane_map(&P.mapA, srcA, pq_, a_channels, g.n, BK, false, SLAB_PX) || !encode_plane_map(&P.mapOut, out, pq_, o_channels, g.n)) stma = false;
+    }
+    if (stma) { T.check = 5; T.M_total = 0; allow_split = false; T.K_pad = (a_channels + BK - 1) / BK * 9 * BK; T.K_total = T.K_pad; k_pad = T.K_pad; }
+    const int m_rows = atma ? g.n * chunks * 32 : stma ? g.n * tiles_per_image * BM : T.M_total;
     // the compact k table keeps 27 bits of offset beside the 5-bit tap number
     if (T.check == 1 && (long long)(g.c > g.k ? g.c : g.k) * (g.ih * g.iw > g.oh * g.ow ? g.ih * g.iw : g.oh * g.ow) + (long long)(g.kr + 1) * (g.iw + g.ow) >= (1ll << 26)) T.check = 2;
     P.check = T.check;
@@ -1458,7 +1535,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     P.status = g_status[dev];
     if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
     else { P.out = out; P.split_stride = 0; P.accumulate = (mode == 1 || mode == 2) && !out_zero; P.add_zero = out_zero; P.bias = bias; }
-    P.reduce_out = atma && P.accumulate;
+    P.reduce_out = (atma || stma) && P.accumulate;
     const long long total_tiles = (long long)tiles_m * tiles_n * splits;
     dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
     int r;
@@ -1467,6 +1544,8 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     else if (mode == 2 && both_rowmajor) r = precision != 1 ? launch_bn<0, false, true>(cx, st, P, grid, bn, dev) : launch_bn<1, false, true>(cx, st, P, grid, bn, dev);
     else if (mode == 2 && b_vector) r = precision != 1 ? launch_bn<0, true, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true, true>(cx, st, P, grid, bn, dev);
     else if (mode == 2) r = precision != 1 ? launch_bn<0, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true>(cx, st, P, grid, bn, dev);
+    else if (stma) r = precision == 0 ? launch_bn<0, false, false, 3>(cx, st, P, grid, bn, dev)
+                   : precision == 2 ? launch_bn<2, false, false, 3>(cx, st, P, grid, bn, dev) : launch_bn<1, false, false, 3>(cx, st, P, grid, bn, dev);
     else if (atma) r = precision == 0 ? launch_bn<0, false, false, 1>(cx, st, P, grid, bn, dev)
                    : precision == 2 ? launch_bn<2, false, false, 1>(cx, st, P, grid, bn, dev) : launch_bn<1, false, false, 1>(cx, st, P, grid, bn, dev);
     else if (precision == 0) r = launch_bn<0, false>(cx, st, P, grid, bn, dev);
@@ -1606,6 +1685,7 @@ int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const flo
 int conv_tc_set_prefetch(int on) { g_conv_prefetch = on ? 1 : 0; return 0; }
 int conv_tc_set_tma(int level) { g_conv_tma = level < 0 ? 0 : (level > 2 ? 2 : level); return 0; }
 int conv_tc_set_pack_cache(int on) { g_conv_pack_cache = on ? 1 : 0; return 0; }
+int conv_tc_set_tma_3x3(int on) { g_conv_tma3 = on ? 1 : 0; return 0; }
 int conv_tc_set_tma_wgrad(int level) { g_conv_wtma = level < 0 ? 0 : (level > 2 ? 2 : level); return 0; }
 
 // 0 = no kernel of this file has timed out on the device since the last call

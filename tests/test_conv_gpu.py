@@ -311,3 +311,40 @@ def test_packed_weight_images_follow_every_write_to_the_weights(lib):
     dw4 = lib.to_device(w4)                                                               # ... and (usually) handed out again
     print("same address reused:", dw4.ptr.value == addr)
     check(dw4, w4)
+
+
+SLAB_SHAPES = [  # 3x3 stride-1 "same" layers fed from raw slabs by TMA: n, c, h, w, k
+    (2, 64, 8, 8, 96),          # 64 pixels: one ragged tile per image
+    (3, 40, 12, 12, 72),        # 144 pixels: a second tile with 16 valid rows; channel counts that are not multiples of 32
+    (2, 64, 56, 56, 64),        # the widest plane a slab holds comfortably; 25 tiles per image
+    (4, 128, 28, 28, 128),
+    (3, 256, 14, 14, 256),      # 72 K-blocks: rotating accumulators
+    (2, 32, 16, 60, 32),        # a 60-pixel-wide plane: the largest halo
+]
+
+
+@pytest.mark.parametrize("shape", SLAB_SHAPES)
+def test_slab_fed_3x3_layers(lib, shape):
+    """Forward (with bias) and backward-data (into zeros and into a non-zero delta) of 3x3 stride-1 pad-1 layers: the slab-fed
+    kernel orders its reduction (channel group, tap, channel) instead of (channel, tap), so results agree with the gather
+    kernel to rounding, not to the bit; both are within 1e-5 of the oracle."""
+    n, c, h, w, k = shape
+    rng = np.random.default_rng(81)
+    x = rng.standard_normal((n, c, h, w)).astype(F); wt = rng.standard_normal((k, c, 3, 3)).astype(F)
+    b = rng.standard_normal(k).astype(F)
+    dy = rng.standard_normal((n, k, h, w)).astype(F); dx0 = rng.standard_normal(x.shape).astype(F)
+    out = {}
+    for level in (0, 1):
+        try:
+            lib.call("set_option", b"conv_tma_3x3", level)
+            r1 = run_conv(lib, x, wt, b, dy, None, None, dx0, (1, 1), (1, 1, 1, 1))
+            r2 = run_conv(lib, x, wt, None, dy, None, None, None, (1, 1), (1, 1, 1, 1))
+        finally:
+            lib.call("set_option", b"conv_tma_3x3", 1)
+        out[level] = (r1["y"], r1["dx"], r2["y"], r2["dx"])
+    lib.call("sync", 0)
+    want = (orc.conv2d_fwd(x, wt, b, (1, 1), (1, 1, 1, 1)), orc.conv2d_bwd_data(dy, wt, x.shape, dx0, (1, 1), (1, 1, 1, 1)),
+            orc.conv2d_fwd(x, wt, None, (1, 1), (1, 1, 1, 1)), orc.conv2d_bwd_data(dy, wt, x.shape, None, (1, 1), (1, 1, 1, 1)))
+    for a, bb, wv, name in zip(out[0], out[1], want, ("y+bias", "dx accumulated", "y", "dx into zeros")):
+        assert relerr(bb, wv) <= 1e-5, name
+        assert relerr(a, bb) <= 3e-6, name

@@ -1,6 +1,7 @@
 // Conv2D C-ABI entry points: argument checks, kernel selection, bias gradient,
 // split-K combine.  See conv_tc.cu (tcgen05 tensor-core path) and conv_simt.cu
 // (exact-fp32 FMA path).
+#include <cstdint>
 #include <cstdlib>
 #include <cstring>
 #include "common.cuh"
@@ -31,6 +32,98 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict_
     }
     s = block_sum(s, sm);
     if (threadIdx.x == 0) gbias[kk] = __fadd_rn(gbias[kk], s);
+}
+
+// ---- 1x1 convolutions that skip pixels (stride > 1) or whose planes are not a multiple of four pixels long ----
+// Such a layer is a dense 1x1 stride-1 convolution over the pixels it actually reads.  Gathering those pixels into a dense
+// [image][channel][pitch] copy (pitch = pixels rounded up to four, the tail zero) is one pass over the smaller tensor, after which
+// the TMA-fed kernels apply: the strided kernels spend most of their time computing addresses, the copy moves a few tens of MB.
+__global__ void __launch_bounds__(256) plane_gather_kernel(const float *__restrict__ src, float *__restrict__ dst, unsigned total,
+                                                           int ihw, int iw, int sr, int sc, int ow, int npix, int pitch) {
+    const unsigned stride = gridDim.x * blockDim.x;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const unsigned plane = idx / (unsigned)pitch, p = idx - plane * pitch;
+        float v = 0.f;
+        if (p < (unsigned)npix) { const unsigned oy = p / (unsigned)ow, ox = p - oy * ow; v = src[(size_t)plane * ihw + oy * sr * iw + ox * sc]; }
+        dst[idx] = v;
+    }
+}
+
+// dx (full resolution) += the dense result at the pixels the convolution read; the others are left alone
+__global__ void __launch_bounds__(256) plane_scatter_add_kernel(const float *__restrict__ dense, float *__restrict__ dst, unsigned total,
+                                                                int ihw, int iw, int sr, int sc, int ow, int npix, int pitch) {
+    const unsigned stride = gridDim.x * blockDim.x;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const unsigned plane = idx / (unsigned)pitch, p = idx - plane * pitch;
+        if (p >= (unsigned)npix) continue;
+        const unsigned oy = p / (unsigned)ow, ox = p - oy * ow;
+        float *d = dst + (size_t)plane * ihw + oy * sr * iw + ox * sc;
+        *d = __fadd_rn(*d, dense[idx]);
+    }
+}
+
+// dx = the dense result at those pixels and zero everywhere else: every element of dx is written.  V = elements per thread
+// (4 when rows are a multiple of four pixels long and dx is 16-byte aligned)
+template <int V>
+__global__ void __launch_bounds__(256) plane_scatter_store_kernel(const float *__restrict__ dense, float *__restrict__ dst, unsigned total_v,
+                                                                  int ihw, int iw, int sr, int sc, int oh, int ow, int pitch) {
+    const unsigned stride = gridDim.x * blockDim.x, ihw_v = ihw / V, iw_v = iw / V;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total_v; idx += stride) {
+        const unsigned plane = idx / ihw_v, r = idx - plane * ihw_v, y = r / iw_v, x0 = (r - y * iw_v) * V, oy = y / (unsigned)sr;
+        const bool row_hit = oy * sr == y && oy < (unsigned)oh;
+        float v[V];
+#pragma unroll
+        for (int e = 0; e < V; e++) {
+            const unsigned x = x0 + e, ox = x / (unsigned)sc;
+            v[e] = (row_hit && ox * sc == x && ox < (unsigned)ow) ? dense[(size_t)plane * pitch + oy * ow + ox] : 0.f;
+        }
+        if (V == 4) reinterpret_cast<float4 *>(dst)[idx] = make_float4(v[0], v[1], v[2], v[3]);
+        else dst[idx] = v[0];
+    }
+}
+
+struct Dense1x1 { bool on; bool ragged; int pitch; ConvGeom g; };
+
+int g_conv_dense = 1;          // eddlb200_set_option("conv_dense_1x1", 0 / 1)
+
+// exact_out: the output tensor (forward) or dy (backward-data) is used where it lies, so its planes must already be dense
+Dense1x1 dense_1x1(const ConvGeom &g, bool exact_out) {
+    Dense1x1 d{false, false, 0, g};
+    const int pq = g.oh * g.ow;
+    if (!g_conv_dense || g.kr != 1 || g.kc != 1 || g.pt != 0 || g.pl != 0 || g.c < 32 || g.k < 32 || pq < 32) return d;
+    if ((g.oh - 1) * g.sr >= g.ih || (g.ow - 1) * g.sc >= g.iw) return d;
+    const bool strided = g.sr > 1 || g.sc > 1;
+    d.ragged = pq % 4 != 0;
+    if (!strided && !d.ragged) return d;                        // dense already
+    if (d.ragged && exact_out) return d;
+    d.pitch = (pq + 3) & ~3;
+    if (d.pitch >= 16000 && d.ragged) return d;
+    d.g.sr = d.g.sc = 1;
+    d.g.ih = d.g.oh = d.ragged ? 1 : g.oh;
+    d.g.iw = d.g.ow = d.ragged ? d.pitch : g.ow;
+    d.on = true;
+    return d;
+}
+
+// device buffers for the dense copies: slot 0 = gathered x, 1 = gathered dy, 2 = dense dx.  They only grow.
+float *dense_buf(cudaStream_t st, int slot, size_t bytes) {
+    static float *buf[EDDLB200_MAX_DEVICES][3] = {}; static size_t cap[EDDLB200_MAX_DEVICES][3] = {};
+    int dev = 0; cudaGetDevice(&dev);
+    if (cap[dev][slot] < bytes) {
+        cudaStreamSynchronize(st);
+        if (buf[dev][slot]) cudaFree(buf[dev][slot]);
+        buf[dev][slot] = nullptr; cap[dev][slot] = 0;
+        if (cudaMalloc(&buf[dev][slot], bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        cap[dev][slot] = bytes;
+    }
+    return buf[dev][slot];
+}
+
+int gather_planes(DevCtx *cx, cudaStream_t st, const float *src, float *dst, size_t planes, int ih, int iw, int sr, int sc, int oh, int ow, int pitch) {
+    const unsigned total = (unsigned)(planes * pitch);
+    plane_gather_kernel<<<grid_for(total, 256), 256, 0, st>>>(src, dst, total, ih * iw, iw, sr, sc, ow, oh * ow, pitch);
+    EB_LAUNCH_CHECK("conv2D(gather)");
+    return 0;
 }
 
 int check(const char *what, const ConvGeom &g) {
@@ -72,6 +165,7 @@ int eddlb200_set_option(const char *name, int value) {
     if (name && !strcmp(name, "conv_tma") && value >= 0 && value <= 2) return conv_tc_set_tma(value);
     if (name && !strcmp(name, "conv_pack_cache") && (value == 0 || value == 1)) return conv_tc_set_pack_cache(value);
     if (name && !strcmp(name, "conv_tma_3x3") && (value == 0 || value == 1)) return conv_tc_set_tma_3x3(value);
+    if (name && !strcmp(name, "conv_dense_1x1") && (value == 0 || value == 1)) { g_conv_dense = value; return 0; }
     if (name && !strcmp(name, "conv_tma_wgrad") && value >= 0 && value <= 2) return conv_tc_set_tma_wgrad(value);
     if (name && !strcmp(name, "bn_waves") && value >= 1) return bn_set_tuning(value, 0);
     if (name && !strcmp(name, "bn_min_items") && value >= 1) return bn_set_tuning(0, value);
@@ -90,6 +184,13 @@ int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bi
     EB_WRITES(y, (size_t)n * k * oh * ow * sizeof(float));
     ProfScope prof(cx, PROF_CONV_FWD, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
+        const Dense1x1 d = dense_1x1(g, true);
+        float *xs = d.on ? dense_buf(st, 0, (size_t)n * c * d.pitch * sizeof(float)) : nullptr;
+        if (xs) {
+            if (int r = gather_planes(cx, st, x, xs, (size_t)n * c, ih, iw, sr, sc, oh, ow, d.pitch)) return r;
+            int r = conv_tc_fwd(cx, st, d.g, xs, w, bias, y, precision);
+            if (r != 1) return r;
+        }
         int r = conv_tc_fwd(cx, st, g, x, w, bias, y, precision);
         if (r != 1) return r;
     }
@@ -111,6 +212,21 @@ int eddlb200_conv2d_bwd_data(int dev, const float *dy, const float *w, float *dx
     if (lz_any(cx)) { int status = 0; dx_zero = lz_take(cx, st, dx, dx_elems * sizeof(float), &status); if (status) return status; }
     ProfScope prof(cx, PROF_CONV_BWD_DATA, 2.0 * n * (double)k * c * kr * kc * oh * ow);
     if (tc_enabled()) {
+        const Dense1x1 d = dense_1x1(g, true);
+        float *dense = d.on ? dense_buf(st, 2, (size_t)n * c * d.pitch * sizeof(float)) : nullptr;
+        if (dense) {
+            int r = conv_tc_bwd_data(cx, st, d.g, dy, w, dense, precision, true);       // stores every element of the dense dx
+            if (r == 0) {
+                const unsigned dense_elems = (unsigned)((size_t)n * c * d.pitch);
+                if (!dx_zero) plane_scatter_add_kernel<<<grid_for(dense_elems, 256), 256, 0, st>>>(dense, dx, dense_elems, ih * iw, iw, sr, sc, ow, oh * ow, d.pitch);
+                else if (iw % 4 == 0 && ((uintptr_t)dx & 15) == 0)
+                    plane_scatter_store_kernel<4><<<grid_for(dx_elems / 4, 256), 256, 0, st>>>(dense, dx, (unsigned)(dx_elems / 4), ih * iw, iw, sr, sc, oh, ow, d.pitch);
+                else plane_scatter_store_kernel<1><<<grid_for(dx_elems, 256), 256, 0, st>>>(dense, dx, (unsigned)dx_elems, ih * iw, iw, sr, sc, oh, ow, d.pitch);
+                EB_LAUNCH_CHECK("gpu_conv2D_back(scatter)");
+                return 0;
+            }
+            if (r != 1) return r;
+        }
         int r = conv_tc_bwd_data(cx, st, g, dy, w, dx, precision, dx_zero);
         if (r != 1) return r;
     }
@@ -138,6 +254,15 @@ int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *
         EB_LAUNCH_CHECK("gpu_conv2D_grad(bias)");
     }
     if (tc_enabled()) {
+        const Dense1x1 d = dense_1x1(g, false);
+        float *xs = d.on ? dense_buf(st, 0, (size_t)n * c * d.pitch * sizeof(float)) : nullptr;
+        float *dys = d.on && d.ragged ? dense_buf(st, 1, (size_t)n * k * d.pitch * sizeof(float)) : nullptr;
+        if (xs && (dys || !d.ragged)) {
+            if (int r = gather_planes(cx, st, x, xs, (size_t)n * c, ih, iw, sr, sc, oh, ow, d.pitch)) return r;
+            if (dys) { if (int r = gather_planes(cx, st, dy, dys, (size_t)n * k, oh, ow, 1, 1, oh, ow, d.pitch)) return r; }
+            int r = conv_tc_bwd_weight(cx, st, d.g, xs, dys ? dys : dy, gw, precision, gw_zero);
+            if (r != 1) return r;
+        }
         int r = conv_tc_bwd_weight(cx, st, g, x, dy, gw, precision, gw_zero);
         if (r != 1) return r;
     }

@@ -1392,14 +1392,14 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     }
     // backward-weight of a 1x1, stride-1, unpadded convolution: k = (n, p, q) is contiguous inside an image for x and for dy, so
     // both operands can be gathered with 16-byte loads when groups of four k never straddle an image
-    const bool both_rowmajor = mode == 2 && g.kr == 1 && g.kc == 1 && g.sr == 1 && g.sc == 1 && g.pt == 0 && g.pl == 0 &&
-                               g.ih == g.oh && g.iw == g.ow && (g.oh * g.ow) % 4 == 0 && T.K_total % BK == 0 &&
-                               aligned16(srcA) && aligned16(srcB);
+    const bool planes_dense = mode == 2 && g.kr == 1 && g.kc == 1 && g.sr == 1 && g.sc == 1 && g.pt == 0 && g.pl == 0 &&
+                              g.ih == g.oh && g.iw == g.ow && (g.oh * g.ow) % 4 == 0 && aligned16(srcA) && aligned16(srcB);
+    const bool both_rowmajor = planes_dense && T.K_total % BK == 0;
     if (both_rowmajor) T.check = 0;
     // ... and, when the planes are at least one K-block long, both can be copied by TMA straight into the operand ring; the
     // reduction then runs over (image, 32-pixel chunk) and needs neither k nor row tables
     const int w_chunks = (g.oh * g.ow + 31) / 32;
-    bool wtma = both_rowmajor && g_conv_wtma > 0 && g.oh * g.ow >= 32 && g.c >= 32 && g.k >= 32;
+    bool wtma = planes_dense && g_conv_wtma > 0 && g.oh * g.ow >= 32 && g.c >= 32 && g.k >= 32;
     int w_bn = 0;
     if (wtma) {
         w_bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);

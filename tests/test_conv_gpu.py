@@ -348,3 +348,43 @@ def test_slab_fed_3x3_layers(lib, shape):
     for a, bb, wv, name in zip(out[0], out[1], want, ("y+bias", "dx accumulated", "y", "dx into zeros")):
         assert relerr(bb, wv) <= 1e-5, name
         assert relerr(a, bb) <= 3e-6, name
+
+
+DENSE_SHAPES = [  # 1x1 layers that skip pixels or have ragged planes, run as dense 1x1 layers over gathered copies: n, c, h, w, k, stride
+    (3, 64, 16, 16, 96, (2, 2)),     # the ResNet shortcut form: a quarter of the pixels
+    (2, 256, 28, 28, 128, (2, 2)),
+    (4, 96, 14, 14, 64, (2, 2)),     # 7x7 output: ragged planes, backward-weight only
+    (5, 64, 7, 7, 160, (1, 1)),      # stride 1, 49-pixel planes: backward-weight over copies padded to 52 pixels
+    (2, 40, 15, 18, 48, (3, 2)),     # different strides per axis, rows and columns the last window does not reach
+    (1, 32, 9, 9, 32, (1, 1)),       # 81 pixels, a batch of one: the padded reduction is not a multiple of 32
+]
+
+
+@pytest.mark.parametrize("shape", DENSE_SHAPES)
+def test_strided_and_ragged_1x1_layers_as_dense_layers(lib, shape):
+    """All three passes with and without the rewrite, into zeros and into non-zero gradients; both within 1e-5 of the oracle
+    and within rounding of each other (the reduction over channels or pixels is tiled differently)."""
+    n, c, h, w, k, stride = shape
+    rng = np.random.default_rng(91)
+    x = rng.standard_normal((n, c, h, w)).astype(F); wt = rng.standard_normal((k, c, 1, 1)).astype(F)
+    b = rng.standard_normal(k).astype(F)
+    oh, ow, _ = orc.resolve((0, 0, 0, 0), h, w, 1, 1, *stride)
+    dy = rng.standard_normal((n, k, oh, ow)).astype(F)
+    gw0 = rng.standard_normal(wt.shape).astype(F); gb0 = rng.standard_normal(k).astype(F); dx0 = rng.standard_normal(x.shape).astype(F)
+    out = {}
+    for level in (0, 1):
+        try:
+            lib.call("set_option", b"conv_dense_1x1", level)
+            r1 = run_conv(lib, x, wt, b, dy, gw0, gb0, dx0, stride, (0, 0, 0, 0))
+            r2 = run_conv(lib, x, wt, None, dy, None, None, None, stride, (0, 0, 0, 0))
+        finally:
+            lib.call("set_option", b"conv_dense_1x1", 1)
+        out[level] = (r1["y"], r1["gw"], r1["dx"], r2["y"], r2["gw"], r2["dx"])
+    lib.call("sync", 0)
+    pads = (0, 0, 0, 0)
+    want = (orc.conv2d_fwd(x, wt, b, stride, pads), orc.conv2d_bwd_weight(x, dy, gw0, None, stride, pads, (1, 1))[0],
+            orc.conv2d_bwd_data(dy, wt, x.shape, dx0, stride, pads), orc.conv2d_fwd(x, wt, None, stride, pads),
+            orc.conv2d_bwd_weight(x, dy, None, None, stride, pads, (1, 1))[0], orc.conv2d_bwd_data(dy, wt, x.shape, None, stride, pads))
+    for a, bb, wv, name in zip(out[0], out[1], want, ("y+bias", "gw accumulated", "dx accumulated", "y", "gw into zeros", "dx into zeros")):
+        assert relerr(bb, wv) <= 1e-5, name
+        assert relerr(a, bb) <= 3e-6, name

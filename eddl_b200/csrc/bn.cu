@@ -272,7 +272,9 @@ int eddlb200_bn_fwd(int dev, int b, int z, int rc, const float *input, float *ou
         EB_MODIFIES(global_mean, zb); EB_MODIFIES(global_variance, zb); EB_READS(affine_g, zb); EB_READS(affine_b, zb);
         EB_MODIFIES(mean, zb); EB_MODIFIES(variance, zb);
     }
-    ProfScope prof(cx, PROF_BN_FWD, 16.0 * b * (double)z * rc);
+    // algorithmic bytes per element: x once per pass (two passes when the batch statistics are computed), y, and the two
+    // optional outputs -- opa (the normalised value BN backward needs) and the ReLU of y written for the layer that follows
+    ProfScope prof(cx, PROF_BN_FWD, ((trmode ? 8.0 : 4.0) + 4.0 + (opa ? 4.0 : 0.0) + (relu_out ? 4.0 : 0.0)) * b * (double)z * rc);
     const unsigned per = (unsigned)b * rc, S = pick_split(z, per);
     const bool vec = (rc % 4 == 0) && aligned16(input) && aligned16(output) && (!opa || aligned16(opa)) && (!relu_out || aligned16(relu_out));
     dim3 grid(z, S);

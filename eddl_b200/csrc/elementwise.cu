@@ -185,17 +185,23 @@ struct CceDeltaF {
     __device__ float operator()(float y, float p, float) const { return __fmul_rn(-y, __fdiv_rn(1.0f, __fadd_rn(p, 10e-8f))); }
 };
 
-// Copy the interior: one thread per element of the SMALL tensor a[n*c,h,w].
-template <bool BACK>
-__global__ void __launch_bounds__(kBlock) pad_kernel(float *a, float *b, size_t total, int h, int w, int top, int left, int bh, int bw) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        int x = (int)(i % w);
-        size_t t = i / w;
-        int y = (int)(t % h);
-        size_t plane = t / h;
-        size_t j = (plane * bh + (y + top)) * bw + (x + left);
-        if (BACK) a[i] = __fadd_rn(a[i], b[j]); else b[j] = a[i];
+// Copy the interior: one thread per four consecutive elements of a row of the SMALL tensor a[n*c,h,w] (one per element when
+// rows are not a multiple of four long).  32-bit index arithmetic: the entry points refuse tensors of 2^31 elements or more.
+template <bool BACK, int V>
+__global__ void __launch_bounds__(kBlock) pad_kernel(float *a, float *b, unsigned total_v, int h, int w, int top, int left, int bh, int bw) {
+    const unsigned stride = gridDim.x * blockDim.x, wv = (unsigned)w / V;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total_v; i += stride) {
+        const unsigned t = i / wv, x = (i - t * wv) * V, plane = t / (unsigned)h, y = t - plane * h;
+        float *pb = b + ((size_t)plane * bh + (y + top)) * bw + (x + left);
+        if (V == 4) {
+            float4 va = reinterpret_cast<const float4 *>(a)[i];
+            if (BACK) {
+                va.x = __fadd_rn(va.x, pb[0]); va.y = __fadd_rn(va.y, pb[1]); va.z = __fadd_rn(va.z, pb[2]); va.w = __fadd_rn(va.w, pb[3]);
+                reinterpret_cast<float4 *>(a)[i] = va;
+            } else { pb[0] = va.x; pb[1] = va.y; pb[2] = va.z; pb[3] = va.w; }
+        } else {
+            if (BACK) a[i] = __fadd_rn(a[i], pb[0]); else pb[0] = a[i];
+        }
     }
 }
 
@@ -402,7 +408,11 @@ int eddlb200_pad(int dev, const float *a, float *b, int n, int c, int h, int w, 
     EB_READS(a, total * sizeof(float));
     EB_MODIFIES(b, (size_t)n * c * (h + top + bottom) * (w + left + right) * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, 8.0 * total);
-    pad_kernel<false><<<grid_for(total, kBlock), kBlock, 0, st>>>(const_cast<float *>(a), b, total, h, w, top, left, h + top + bottom, w + left + right);
+    EB_REQUIRE(total < 0x7fffffffull, "gpu_pad: tensor larger than 2^31 elements");
+    if (w % 4 == 0 && ((uintptr_t)a & 15) == 0)
+        pad_kernel<false, 4><<<grid_for(total / 4, kBlock), kBlock, 0, st>>>(const_cast<float *>(a), b, (unsigned)(total / 4), h, w, top, left, h + top + bottom, w + left + right);
+    else
+        pad_kernel<false, 1><<<grid_for(total, kBlock), kBlock, 0, st>>>(const_cast<float *>(a), b, (unsigned)total, h, w, top, left, h + top + bottom, w + left + right);
     EB_LAUNCH_CHECK("gpu_pad");
     return 0;
 }
@@ -414,7 +424,11 @@ int eddlb200_pad_bwd(int dev, float *a_delta, const float *b_delta, int n, int c
     EB_MODIFIES(a_delta, total * sizeof(float));
     EB_READS(b_delta, (size_t)n * c * (h + top + bottom) * (w + left + right) * sizeof(float));
     ProfScope prof(cx, PROF_ELEMENTWISE, 12.0 * total);
-    pad_kernel<true><<<grid_for(total, kBlock), kBlock, 0, st>>>(a_delta, const_cast<float *>(b_delta), total, h, w, top, left, h + top + bottom, w + left + right);
+    EB_REQUIRE(total < 0x7fffffffull, "gpu_pad_back: tensor larger than 2^31 elements");
+    if (w % 4 == 0 && ((uintptr_t)a_delta & 15) == 0)
+        pad_kernel<true, 4><<<grid_for(total / 4, kBlock), kBlock, 0, st>>>(a_delta, const_cast<float *>(b_delta), (unsigned)(total / 4), h, w, top, left, h + top + bottom, w + left + right);
+    else
+        pad_kernel<true, 1><<<grid_for(total, kBlock), kBlock, 0, st>>>(a_delta, const_cast<float *>(b_delta), (unsigned)total, h, w, top, left, h + top + bottom, w + left + right);
     EB_LAUNCH_CHECK("gpu_pad_back");
     return 0;
 }

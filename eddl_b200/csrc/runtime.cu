@@ -453,6 +453,16 @@ static cudaEvent_t peer_event(cudaEvent_t &slot) {
     return slot;
 }
 
+// Device code outside this library is about to write (or has written) [p, p + bytes): everything the library still owes
+// the range is written first (deferred zero fills, a pending copy, an average in flight), and whatever the library caches
+// about its contents (packed weight images, the loss / metric pair) is invalidated.
+int eddlb200_notify_write(int dev, void *p, size_t bytes) {
+    EB_CTX(dev);
+    if (!p || !bytes) return 0;
+    EB_MODIFIES(p, bytes);
+    return 0;
+}
+
 int eddlb200_memcpy_peer(int dst_dev, void *dst, int src_dev, const void *src, size_t bytes) {
     if (dst_dev == src_dev) return eddlb200_memcpy_d2d(dst_dev, dst, src, bytes);
     if (bytes == 0) return 0;

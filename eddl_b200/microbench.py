@@ -129,7 +129,7 @@ def run_hbm(args):
         gg, gb, m1, m2 = L.zeros((z,), dev), L.zeros((z,), dev), L.zeros((z,), dev), L.zeros((z,), dev)
         shape = [b, z, hw, hw]
         report("bn_fwd", shape, 16 * E, lambda: L.call("bn_fwd", dev, b, z, rc, x, y, opa, gm, gv, g, bt, mean, var, 1, 1e-3, 0.99, None))
-        report("bn_relu_fwd_fused", shape, 16 * E, lambda: L.call("bn_fwd", dev, b, z, rc, x, y, opa, gm, gv, g, bt, mean, var, 1, 1e-3, 0.99, r))
+        report("bn_relu_fwd_fused", shape, 20 * E, lambda: L.call("bn_fwd", dev, b, z, rc, x, y, opa, gm, gv, g, bt, mean, var, 1, 1e-3, 0.99, r))
         report("bn_bwd", shape, 24 * E, lambda: L.call("bn_bwd", dev, b, z, rc, d, opa, pd, gg, gb, g, var, m1, m2))
         report("relu_fwd", shape, 8 * E, lambda: L.call("relu_fwd", dev, x, y, E))
         report("relu_bwd", shape, 16 * E, lambda: L.call("relu_bwd", dev, d, x, pd, E))

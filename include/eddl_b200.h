@@ -47,6 +47,11 @@ int eddlb200_memcpy_d2d(int dev, void *dst, const void *src, size_t bytes);
  * multi-GPU path of Net::sync_weights / Net::load, src/net/net_func.cpp:111-127).  A direct peer copy over NVLink,
  * ordered after the work already enqueued on both devices' streams and before what is enqueued on either afterwards. */
 int eddlb200_memcpy_peer(int dst_dev, void *dst, int src_dev, const void *src, size_t bytes);
+/* For device code OUTSIDE this library that writes memory this library also works on: call it before enqueueing the write on
+ * the library's stream (eddlb200_stream).  Zeros, copies and averages the library still owes the range are written first, and
+ * what it caches about the range's contents (packed weight images of the convolutions, the loss / metric pair) is dropped.
+ * The reference's host code never needs it: all its device writes are calls of this library. */
+int eddlb200_notify_write(int dev, void *p, size_t bytes);
 /* Pinned-host staged copies for a caller that overlaps transfers itself
  * (Net::train_batch does blocking copies: src/net/net_api.cpp:1269-1285). */
 int eddlb200_host_alloc(size_t bytes, void **out);
@@ -255,6 +260,21 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
           pixels, at least 32 channels on both sides) are fed by TMA tensor copies of the activations and drained by TMA
           stores, or TMA fp32 adds where the output accumulates; 1 = only where the output is stored; 0 = the gather
           kernel everywhere.  Results are the same bits at every level.
+ *          "conv_tma_3x3" 1 (default) = forward and backward-data of 3x3 stride-1 pad-1 layers (planes of a multiple of 4
+ *          pixels and at least 64, rows of at most 125 pixels, at least 32 channels on both sides) read raw slabs of the
+ *          activations delivered by TMA, one per tile and 32-channel group for all nine taps; the reduction is then
+ *          ordered (channel group, tap, channel), so results agree with the gather kernel to rounding (3e-6), not to
+ *          the bit; 0 = the gather kernel.  Needs "conv_tma" >= 1.
+ *          "conv_tma_wgrad" 2 (default) = backward-weight of 1x1 stride-1 unpadded layers: both operands are copied by TMA
+ *          straight into the operand ring and the landed fp32 values serve as the hi planes as they are (the tensor core
+ *          reads only their upper 19 bits: same bits as 1); 1 = the hi planes are rewritten with the low bits cleared;
+ *          0 = the gather kernel.
+ *          "conv_dense_1x1" 1 (default) = 1x1 unpadded layers that skip pixels (stride > 1) or whose planes are not a
+ *          multiple of 4 pixels run as dense 1x1 stride-1 layers over gathered copies of their operands (library-owned
+ *          device buffers that only grow); 0 = the strided gather kernels.  Agreement to rounding.
+ *          "conv_pack_cache" 1 (default) = the packed weight images of forward / backward-data are kept per weight tensor
+ *          and re-packed only after a call of this library has written the tensor; 0 = packed at every call.  Device
+ *          code outside this library that writes weights must go through eddlb200_notify_write or switch this off.
           "bn_waves" (1..64, default 16) and "bn_min_items" (>= 1024, default 8192): grid sizing of the BatchNorm
  *          kernels -- every channel is cut into slices so that a launch has about bn_waves x (8 blocks per SM) blocks
  *          of at least bn_min_items elements each.  Results depend on the slicing only through the fp32 order of the

@@ -311,6 +311,17 @@ def test_packed_weight_images_follow_every_write_to_the_weights(lib):
     dw4 = lib.to_device(w4)                                                               # ... and (usually) handed out again
     print("same address reused:", dw4.ptr.value == addr)
     check(dw4, w4)
+    # a write the library does not see (another CUDA runtime instance copying into the tensor) has to be announced
+    import os
+    rt_path = next((p for p in ("/usr/local/cuda/lib64/libcudart.so", "/usr/local/cuda/lib64/libcudart.so.12") if os.path.exists(p)), None)
+    if rt_path:
+        rt = ctypes.CDLL(rt_path)
+        rt.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+        w5 = rng.standard_normal(w.shape).astype(F)
+        lib.call("notify_write", 0, dw4, w5.nbytes)
+        lib.call("sync", 0)
+        assert rt.cudaMemcpy(dw4.ptr.value, w5.ctypes.data_as(ctypes.c_void_p), w5.nbytes, 1) == 0
+        check(dw4, w5)
 
 
 SLAB_SHAPES = [  # 3x3 stride-1 "same" layers fed from raw slabs by TMA: n, c, h, w, k

@@ -321,6 +321,9 @@ def run_b200_arm(args):
     wall_res = time.perf_counter() - t0
     L.call("timer_elapsed_ms", local, 1, ctypes.byref(ms))
     launches = L.launches(local) - launches0
+    tc_calls, fma_calls = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+    L.call("conv_path_counts", local, ctypes.byref(tc_calls), ctypes.byref(fma_calls))
+    conv_paths = {"tensor_core": int(tc_calls.value), "fp32_fma_fallback": int(fma_calls.value), "since": "process start"}
     res_s = ebd.max_over_ranks(max(ms.value / 1e3, wall_res))
     ebd.barrier()
     # ---- the same steps once more with a CUDA-event pair around every backend call: per-family durations for the roofline
@@ -380,7 +383,7 @@ def run_b200_arm(args):
             "clocks": clocks,
             "e2e": {"value": imgs / e2e_s, "unit": "img/s", "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 8,
                     "ms_per_step": 1e3 * e2e_s / args.steps},
-            "gpu_launches": int(launches), "roofline": roofline, "hbm_kernels": hbm,
+            "gpu_launches": int(launches), "conv_calls": conv_paths, "roofline": roofline, "hbm_kernels": hbm,
             "breakdown_ms_per_step": {k: round(v[1] / args.steps, 3) for k, v in prof.items()},
             "profiled_ms_per_step": round(ms.value / args.steps, 3),
             "loss": {"after_warmup": loss0 if args.warmup else None, "e2e_last": loss_e2e, "resident_last_sum": loss_res}}

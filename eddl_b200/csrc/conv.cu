@@ -86,6 +86,10 @@ struct Dense1x1 { bool on; bool ragged; int pitch; ConvGeom g; };
 
 int g_conv_dense = 1;          // eddlb200_set_option("conv_dense_1x1", 0 / 1)
 
+// Conv2D calls served by the tensor-core kernels [0] and by the fp32 FMA kernels [1], per device: a caller can tell whether
+// any layer of its net left the tensor-core path (a shape the kernel does not take, or the path forced by an option)
+unsigned long long g_conv_calls[EDDLB200_MAX_DEVICES][2] = {};
+
 // exact_out: the output tensor (forward) or dy (backward-data) is used where it lies, so its planes must already be dense
 Dense1x1 dense_1x1(const ConvGeom &g, bool exact_out) {
     Dense1x1 d{false, false, 0, g};
@@ -172,6 +176,13 @@ int eddlb200_set_option(const char *name, int value) {
     return set_error(EDDLB200_EINVAL, "set_option: unknown option or value");
 }
 
+int eddlb200_conv_path_counts(int dev, unsigned long long *tensor_core_calls, unsigned long long *fma_calls) {
+    if (dev < 0 || dev >= EDDLB200_MAX_DEVICES) return set_error(EDDLB200_EINVAL, "conv_path_counts: device ordinal out of range");
+    if (tensor_core_calls) *tensor_core_calls = g_conv_calls[dev][0];
+    if (fma_calls) *fma_calls = g_conv_calls[dev][1];
+    return 0;
+}
+
 int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias, float *y,
                         int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
                         int sr, int sc, int pad_top, int pad_left, int precision) {
@@ -189,11 +200,12 @@ int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bi
         if (xs) {
             if (int r = gather_planes(cx, st, x, xs, (size_t)n * c, ih, iw, sr, sc, oh, ow, d.pitch)) return r;
             int r = conv_tc_fwd(cx, st, d.g, xs, w, bias, y, precision);
-            if (r != 1) return r;
+            if (r != 1) { g_conv_calls[dev][0]++; return r; }
         }
         int r = conv_tc_fwd(cx, st, g, x, w, bias, y, precision);
-        if (r != 1) return r;
+        if (r != 1) { g_conv_calls[dev][0]++; return r; }
     }
+    g_conv_calls[dev][1]++;
     return conv_simt_fwd(cx, st, g, x, w, bias, y);
 }
 
@@ -223,13 +235,15 @@ int eddlb200_conv2d_bwd_data(int dev, const float *dy, const float *w, float *dx
                     plane_scatter_store_kernel<4><<<grid_for(dx_elems / 4, 256), 256, 0, st>>>(dense, dx, (unsigned)(dx_elems / 4), ih * iw, iw, sr, sc, oh, ow, d.pitch);
                 else plane_scatter_store_kernel<1><<<grid_for(dx_elems, 256), 256, 0, st>>>(dense, dx, (unsigned)dx_elems, ih * iw, iw, sr, sc, oh, ow, d.pitch);
                 EB_LAUNCH_CHECK("gpu_conv2D_back(scatter)");
+                g_conv_calls[dev][0]++;
                 return 0;
             }
             if (r != 1) return r;
         }
         int r = conv_tc_bwd_data(cx, st, g, dy, w, dx, precision, dx_zero);
-        if (r != 1) return r;
+        if (r != 1) { g_conv_calls[dev][0]++; return r; }
     }
+    g_conv_calls[dev][1]++;
     if (dx_zero) { if (int r = launch_zero_fill(cx, st, dx, dx_elems)) return r; }     // the FMA kernel adds into dx
     return conv_simt_bwd_data(cx, st, g, dy, w, dx);
 }
@@ -261,11 +275,12 @@ int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *
             if (int r = gather_planes(cx, st, x, xs, (size_t)n * c, ih, iw, sr, sc, oh, ow, d.pitch)) return r;
             if (dys) { if (int r = gather_planes(cx, st, dy, dys, (size_t)n * k, oh, ow, 1, 1, oh, ow, d.pitch)) return r; }
             int r = conv_tc_bwd_weight(cx, st, d.g, xs, dys ? dys : dy, gw, precision, gw_zero);
-            if (r != 1) return r;
+            if (r != 1) { g_conv_calls[dev][0]++; return r; }
         }
         int r = conv_tc_bwd_weight(cx, st, g, x, dy, gw, precision, gw_zero);
-        if (r != 1) return r;
+        if (r != 1) { g_conv_calls[dev][0]++; return r; }
     }
+    g_conv_calls[dev][1]++;
     if (gw_zero) { if (int r = launch_zero_fill(cx, st, gw, gw_elems)) return r; }     // the FMA path adds into gw
     return conv_simt_bwd_weight(cx, st, g, x, dy, gw);
 }

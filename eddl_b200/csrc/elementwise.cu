@@ -234,17 +234,17 @@ int pend_copy_flush(DevCtx *cx, cudaStream_t st) {
     PendCopy &p = pend_copy(cx);
     if (!p.active) return 0;
     p.active = false;
-    if (p.kind == 2) return launch3(cx, st, p.src, p.src2, p.dst, p.n, Sum2IntoZeroF{p.sa, p.sb, p.s2, p.t2}, "gpu_add", 20.0);
+    if (p.kind == 2) return launch3(cx, st, p.src, p.src2, p.dst, p.n, Sum2IntoZeroF{p.sa, p.sb, p.s2, p.t2}, "gpu_add", 12.0);
     if (p.kind == 3) {
         const size_t n = p.n;
         EB_READS(p.src, n * sizeof(float)); EB_WRITES(p.dst, n * sizeof(float)); EB_WRITES(p.dst2, n * sizeof(float));
-        ProfScope prof(cx, PROF_ELEMENTWISE, 24.0 * n);             // canonical: two in-place adds of 12 bytes per element
+        ProfScope prof(cx, PROF_ELEMENTWISE, 12.0 * n);             // one read, two writes (the two in-place adds it replaces move 24)
         const size_t n4 = (aligned16(p.src) && aligned16(p.dst) && aligned16(p.dst2)) ? n / 4 : 0;
         map1_twice_kernel<<<grid_for(n4 ? n4 : n, kBlock), kBlock, 0, st>>>(p.src, p.dst, p.dst2, n4, n, AxpbZeroF{p.sa, p.sb});
         EB_LAUNCH_CHECK("gpu_add (two destinations)");
         return 0;
     }
-    return launch1(cx, st, p.src, p.dst, p.n, AxpbZeroF{p.sa, p.sb}, "gpu_add", 12.0);
+    return launch1(cx, st, p.src, p.dst, p.n, AxpbZeroF{p.sa, p.sb}, "gpu_add", 8.0);
 }
 // writes n zeros at p; used when a deferred zero fill has to be materialised
 int launch_zero_fill(DevCtx *cx, cudaStream_t st, float *p, size_t n) {
@@ -312,7 +312,7 @@ int eddlb200_relu_fwd(int dev, const float *a, float *b, size_t n) {
             p.active = false;
             EB_READS(p.src, n * sizeof(float)); EB_READS(p.src2, n * sizeof(float));
             EB_WRITES(p.dst, n * sizeof(float)); EB_WRITES(b, n * sizeof(float));
-            ProfScope prof(cx, PROF_ELEMENTWISE, 28.0 * n);          // canonical: 8 + 12 for the two adds, 8 for the ReLU
+            ProfScope prof(cx, PROF_ELEMENTWISE, 16.0 * n);          // two reads, two writes (the two adds and the ReLU it replaces move 28)
             const size_t n4 = (aligned16(p.src) && aligned16(p.src2) && aligned16(p.dst) && aligned16(b)) ? n / 4 : 0;
             map3_relu_kernel<<<grid_for(n4 ? n4 : n, kBlock), kBlock, 0, st>>>(p.src, p.src2, p.dst, b, n4, n, Sum2IntoZeroF{p.sa, p.sb, p.s2, p.t2});
             EB_LAUNCH_CHECK("gpu_add + gpu_relu");
@@ -343,7 +343,7 @@ int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b
     }
     if (inc_c && c && c != a && c != b && lz_any(cx)) {
         int status = 0;
-        if (lz_take(cx, st, c, n * sizeof(float), &status)) return launch3(cx, st, a, b, c, n, AxpbyZeroF{sca, scb}, "gpu_add", 16.0);
+        if (lz_take(cx, st, c, n * sizeof(float), &status)) return launch3(cx, st, a, b, c, n, AxpbyZeroF{sca, scb}, "gpu_add", 12.0);
         if (status) return status;
     }
     if (!inc_c && c && (c == b) != (c == a) && lz_any(cx)) {
@@ -357,7 +357,7 @@ int eddlb200_axpby(int dev, float sca, const float *a, float scb, const float *b
                 p.active = true; p.kind = 1; p.dst = c; p.src = a; p.src2 = nullptr; p.sa = sca; p.sb = scb; p.n = n;
                 return 0;
             }
-            return launch1(cx, st, b, c, n, ZeroAxpbF{sca, scb}, "gpu_add", 12.0);
+            return launch1(cx, st, b, c, n, ZeroAxpbF{sca, scb}, "gpu_add", 8.0);
         }
         if (status) return status;
     }
@@ -370,7 +370,7 @@ int eddlb200_inc(int dev, const float *a, float *b, size_t n) {
     if (b && b != a && lz_any(cx)) {
         // b is known to hold zeros: 1*a + 1*0 = a + 0, one read instead of two
         int status = 0;
-        if (lz_take(cx, st, b, n * sizeof(float), &status)) return launch1(cx, st, a, b, n, AddToZeroF{}, "gpu_inc", 12.0);
+        if (lz_take(cx, st, b, n * sizeof(float), &status)) return launch1(cx, st, a, b, n, AddToZeroF{}, "gpu_inc", 8.0);
         if (status) return status;
     }
     return launch3(cx, st, a, b, b, n, AxpbyF<false>{1.f, 1.f}, "gpu_inc");
@@ -389,7 +389,7 @@ int eddlb200_relu_bwd(int dev, const float *d, const float *i, float *pd, size_t
     EB_CTX(dev);
     if (pd && pd != d && pd != i && lz_any(cx)) {
         int status = 0;
-        if (lz_take(cx, st, pd, n * sizeof(float), &status)) return launch3(cx, st, d, i, pd, n, ReluBwdZeroF{}, "gpu_d_relu", 16.0);
+        if (lz_take(cx, st, pd, n * sizeof(float), &status)) return launch3(cx, st, d, i, pd, n, ReluBwdZeroF{}, "gpu_d_relu", 12.0);
         if (status) return status;
     }
     return launch3(cx, st, d, i, pd, n, ReluBwdF{}, "gpu_d_relu");

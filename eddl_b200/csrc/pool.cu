@@ -306,7 +306,7 @@ int eddlb200_maxpool2d_bwd(int dev, const float *d, const float *ind_x, const fl
     int id_zero = 0;
     EB_NOTES(id, total * sizeof(float));
     if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
-    ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + 8.0 * total);     // canonical count, also for the id_zero variant
+    ProfScope prof(cx, PROF_POOL, 12.0 * n * c * oh * ow + (id_zero ? 4.0 : 8.0) * total);     // the delta is stored, or read and written
     const size_t plane_smem = (size_t)8 * oh * ow + (size_t)4 * (ih + iw);
     if (plane_smem <= (size_t)160 * 1024 && ih * iw >= 1024 && oh < 32768 && ow < 32768 && (size_t)n * c < 0x7fffffffu) {
         static bool configured[EDDLB200_MAX_DEVICES] = {};
@@ -359,7 +359,7 @@ int eddlb200_avgpool2d_bwd(int dev, const float *d, float *id, int n, int c, int
     int id_zero = 0;
     EB_NOTES(id, total * sizeof(float));
     if (lz_any(cx) && id != d) { int status = 0; id_zero = lz_take(cx, st, id, total * sizeof(float), &status); if (status) return status; }
-    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + 8.0 * total);
+    ProfScope prof(cx, PROF_POOL, 4.0 * n * c * oh * ow + (id_zero ? 4.0 : 8.0) * total);
     if (total < (size_t(1) << 32)) pool_bwd_kernel<false, unsigned><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g, id_zero);
     else pool_bwd_kernel<false, size_t><<<grid_for(total, kBlock), kBlock, 0, st>>>(d, nullptr, nullptr, id, total, g, id_zero);
     EB_LAUNCH_CHECK("gpu_avgpool2D_back");

@@ -280,6 +280,11 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *          of at least bn_min_items elements each.  Results depend on the slicing only through the fp32 order of the
  *          partial sums (about 1e-7 relative on the statistics). */
 int eddlb200_set_option(const char *name, int value);
+/* Conv2D calls (forward, backward-data, backward-weight alike) that `dev` has served on the tensor-core kernels and on the fp32
+ * FMA kernels since the library was loaded.  The FMA path is taken for shapes the tensor-core kernel refuses (a plane side of
+ * 16000 pixels or more) and when "conv_path" forces it; it is about 100 times slower, so a non-zero fma count in a training
+ * run is worth knowing.  Either pointer may be null. */
+int eddlb200_conv_path_counts(int dev, unsigned long long *tensor_core_calls, unsigned long long *fma_calls);
 int eddlb200_conv2d_fwd(int dev, const float *x, const float *w, const float *bias /* may be null */, float *y,
                         int n, int c, int ih, int iw, int k, int kr, int kc, int oh, int ow,
                         int sr, int sc, int pad_top, int pad_left, int precision);

@@ -399,3 +399,24 @@ def test_strided_and_ragged_1x1_layers_as_dense_layers(lib, shape):
     for a, bb, wv, name in zip(out[0], out[1], want, ("y+bias", "gw accumulated", "dx accumulated", "y", "gw into zeros", "dx into zeros")):
         assert relerr(bb, wv) <= 1e-5, name
         assert relerr(a, bb) <= 3e-6, name
+
+
+def test_conv_path_counts_tell_fallbacks_from_tensor_core_calls(lib):
+    """A call that ends on the fp32 FMA kernels is counted as such, so a training run can check that none of its layers did."""
+    def counts():
+        a, b = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+        lib.call("conv_path_counts", 0, ctypes.byref(a), ctypes.byref(b))
+        return a.value, b.value
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((2, 8, 10, 10)).astype(F); w = rng.standard_normal((16, 8, 3, 3)).astype(F); dy = rng.standard_normal((2, 16, 10, 10)).astype(F)
+    t0, f0 = counts()
+    run_conv(lib, x, w, None, dy, None, None, None, (1, 1), (1, 1, 1, 1))
+    t1, f1 = counts()
+    assert (t1 - t0, f1 - f0) == (3, 0)
+    try:
+        lib.call("set_option", b"conv_path", 1)
+        run_conv(lib, x, w, None, dy, None, None, None, (1, 1), (1, 1, 1, 1))
+    finally:
+        lib.call("set_option", b"conv_path", 0)
+    t2, f2 = counts()
+    assert (t2 - t1, f2 - f1) == (0, 3)

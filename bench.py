@@ -247,12 +247,14 @@ def run_b200_arm(args):
     # torchrun exports OMP_NUM_THREADS=1 as a default of its own, not as the user's choice, so it is overridden; an
     # explicit EDDL_B200_HOST_THREADS wins.
     world_env = max(1, int(os.environ.get("WORLD_SIZE", "1")))
-    # With several ranks on one host two cores per rank stay free for the NCCL proxy and the Python threads: the OpenMP
-    # workers spin between EDDL's short parallel regions and would otherwise starve them.
+    # With several ranks on one host two cores per rank stay free for the NCCL proxy and the Python threads, and the OpenMP
+    # workers sleep between EDDL's short parallel regions instead of spinning: spinning workers starved those threads
+    # (two ranks, VGG-16-BN's 4 ms step: 13 300 img/s end to end with spinning workers, 64 300 with sleeping ones; ResNet-50's
+    # 27 ms step loses 3 % end to end to the wake-ups).  One rank has the host to itself and keeps its workers spinning.
     share = (os.cpu_count() or 1) // world_env
     host_threads = int(os.environ.get("EDDL_B200_HOST_THREADS", "0")) or max(1, share - 2 if world_env > 1 else share)
     os.environ["OMP_NUM_THREADS"] = str(host_threads)
-    os.environ.setdefault("OMP_WAIT_POLICY", "active")
+    os.environ.setdefault("OMP_WAIT_POLICY", "passive" if world_env > 1 else "active")
     if args.gpus > 1:
         import torch  # noqa: F401  (first, so that the process-wide libnccl.so.2 is the one torch was built against)
     from eddl_b200 import capi, harness, dist as ebd

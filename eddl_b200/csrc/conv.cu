@@ -170,6 +170,7 @@ int eddlb200_set_option(const char *name, int value) {
     if (name && !strcmp(name, "conv_pack_cache") && (value == 0 || value == 1)) return conv_tc_set_pack_cache(value);
     if (name && !strcmp(name, "conv_tma_3x3") && (value == 0 || value == 1)) return conv_tc_set_tma_3x3(value);
     if (name && !strcmp(name, "conv_dense_1x1") && (value == 0 || value == 1)) { g_conv_dense = value; return 0; }
+    if (name && !strcmp(name, "conv_tma_wgrad_3x3") && (value == 0 || value == 1)) return conv_tc_set_tma_wgrad_3x3(value);
     if (name && !strcmp(name, "conv_tma_wgrad") && value >= 0 && value <= 2) return conv_tc_set_tma_wgrad(value);
     if (name && !strcmp(name, "bn_waves") && value >= 1) return bn_set_tuning(value, 0);
     if (name && !strcmp(name, "bn_min_items") && value >= 1) return bn_set_tuning(0, value);

@@ -32,6 +32,7 @@ int conv_tc_set_tma(int level);
 // 1 (default): backward-weight of those layers has both operands copied by TMA into the operand ring; 2: in addition the landed
 // values serve as the hi plane unmasked; 0: the 16-byte gather.
 int conv_tc_set_tma_wgrad(int level);
+int conv_tc_set_tma_wgrad_3x3(int on);
 // 1 (default): forward / backward-data of 3x3 stride-1 "same" layers (planes up to 60 pixels wide) read raw slabs delivered by TMA
 int conv_tc_set_tma_3x3(int on);
 // 1 (default): packed weight images are kept per (weight tensor, tiling) and re-packed, all stale ones in one launch, only after

@@ -61,6 +61,10 @@ constexpr int NTHREADS = NPROD + 32 + NEPI + 32;     // + warp 13: L2 prefetch o
 // output-heavy layers are bound by the epilogue's chain of tensor-memory reads, and two warps per lane quarter halve it
 constexpr int NTHREADS_ATMA = NTHREADS + NEPI;
 constexpr int threads_of(int tma) { return (tma == 1 || tma == 3) ? NTHREADS_ATMA : NTHREADS; }
+// backward-weight of 3x3 stride-1 pad-1 layers fed from raw slabs (TMA = 4): a tile's 128 rows are the nine taps of 14 channels
+// (126 rows, the last two stay zero) and a K-block is 32 pixels of one image; one slab of [16 channels][160 pixels] -- the 32
+// pixels plus a halo of W + 1 either side, its start rounded down to 16 bytes -- serves all 126 rows
+constexpr int WS_CH = 14, WS_ROWS = 9 * WS_CH, WS_SLAB_PX = 160, WS_SLAB_CH = 16;
 constexpr int SLAB_PX = 256;        // pixels per channel of a raw slab (3x3 TMA-fed kernels): 128 rows + a halo of W + 1 either side + alignment
 constexpr int PF_AHEAD = 8;         // K-blocks the prefetch warp may run ahead of the producers
 constexpr int INVALID_Y = -20000;
@@ -97,6 +101,7 @@ struct TcParams {
     int img_w;              // STMA: width of the image plane (the halo of a slab is img_w + 1 pixels either side)
     int tap_sign;           // STMA: +1 forward (tap (r, s) reads pixel + (r-1, s-1)), -1 backward-data (pixel + (1-r, 1-s))
     int raw_hi;             // WTMA: leave the landed fp32 values as the hi plane (the tensor core reads only their upper 19 bits)
+    int plane_px;           // WSLAB: pixels of an image plane
     alignas(64) CUtensorMap mapA;
     alignas(64) CUtensorMap mapOut;
 };
@@ -225,7 +230,7 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t k) {
 // Shared memory of a CTA.  Gather kernels: the operand ring only.  ATMA kernels add a ring of RAW_STAGES raw activation
 // tiles ([4 chunks][32 channels][32 pixels] fp32, written by TMA) in front of the converters and two 4 KB staging buffers
 // per epilogue warp behind them, and keep a shorter operand ring in exchange.
-template <int BN_, bool SPLIT3, bool ATMA = false>
+template <int BN_, bool SPLIT3, bool ATMA = false, bool WSLAB = false>
 struct Layout {
     static constexpr int A_BYTES = BM * BK * 4;
     static constexpr int B_BYTES = BN_ * BK * 4;
@@ -234,11 +239,13 @@ struct Layout {
     static constexpr int RAW_STAGES = ATMA ? 4 : 0;
     static constexpr int OUT_BYTES = ATMA ? 8 * 32 * 32 * 4 : 0;       // one 32 x 32 staging block per epilogue warp
     // 227 KB per CTA minus the alignment slack and the barrier words; gather kernels keep their 200 KB ring
-    static constexpr int RING_BUDGET = ATMA ? 232448 - 1024 - 256 - RAW_STAGES * RAW_BYTES - OUT_BYTES : 200 * 1024;
-    static constexpr int STAGES = (RING_BUDGET / STAGE_BYTES) > 4 ? 4 : (RING_BUDGET / STAGE_BYTES);
+    static constexpr int WSLAB_BYTES = WSLAB ? WS_SLAB_CH * WS_SLAB_PX * 4 : 0;    // one raw slab of x beside every stage
+    static constexpr int RING_BUDGET = ATMA ? 232448 - 1024 - 256 - RAW_STAGES * RAW_BYTES - OUT_BYTES : (WSLAB ? 232448 - 1024 - 256 : 200 * 1024);
+    static constexpr int STAGES = (RING_BUDGET / (STAGE_BYTES + WSLAB_BYTES)) > 4 ? 4 : (RING_BUDGET / (STAGE_BYTES + WSLAB_BYTES));
     static_assert(STAGES >= 2, "the operand ring needs two stages");
-    static constexpr int TABLE_BYTES = ATMA ? 0 : 8 * 32 * 12;     // backward-weight: 32 row entries of A (8 bytes) and of B (4 bytes) per producer warp
-    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + RAW_STAGES * RAW_BYTES + OUT_BYTES + TABLE_BYTES + 256;
+    static constexpr int TABLE_BYTES = (ATMA || WSLAB) ? 0 : 8 * 32 * 12;     // backward-weight: 32 row entries of A (8 bytes) and of B (4 bytes) per producer warp
+    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * (STAGE_BYTES + WSLAB_BYTES) + RAW_STAGES * RAW_BYTES + OUT_BYTES + TABLE_BYTES + 256;
+    static_assert(SMEM_BYTES <= 232448, "shared memory of a CTA");
 };
 
 // Persistent, warp-specialised kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the
@@ -266,12 +273,12 @@ struct Layout {
 template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, int TMA = 0>
 __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __grid_constant__ TcParams P) {
     constexpr bool STMA = TMA == 3;                      // 3x3 stride-1 pad-1 layers fed from raw slabs (see load_row)
-    constexpr bool ATMA = TMA == 1 || STMA, WTMA = TMA == 2;
-    static_assert(!WTMA || (!WGRAD && BGATHER), "the TMA-fed backward-weight variant replaces the both-operands gather");
+    constexpr bool ATMA = TMA == 1 || STMA, WTMA = TMA == 2, WSLAB = TMA == 4;
+    static_assert(!(WTMA || WSLAB) || (!WGRAD && BGATHER), "the TMA-fed backward-weight variants replace the both-operands gather");
     constexpr bool SPLIT3 = PREC != 1;                   // operands staged as hi / lo planes
     constexpr bool CROSS_BF16 = PREC == 2 && !WGRAD && !BGATHER;     // cross terms as one bf16 MMA chain
     static_assert(!ATMA || (!WGRAD && !BGATHER), "the TMA-fed variant covers forward and backward-data");
-    using L = Layout<BN_, SPLIT3, ATMA>;
+    using L = Layout<BN_, SPLIT3, ATMA, WSLAB>;
     constexpr int STAGES = L::STAGES;
     constexpr int RAWS = L::RAW_STAGES;
     constexpr bool A_ROWMAJOR = !WGRAD;
@@ -279,12 +286,13 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *stage_base = smem;
-    uint8_t *raw_base = smem + STAGES * L::STAGE_BYTES;                       // ATMA: raw activation ring
-    uint8_t *out_base = raw_base + RAWS * L::RAW_BYTES;                       // ATMA: epilogue staging, 2 x 4 KB per warp
+    uint8_t *raw_base = smem + STAGES * L::STAGE_BYTES;                       // ATMA: raw activation ring; WSLAB: one slab per stage
+    static_assert(!WSLAB || RAWS == 0, "the slab ring of backward-weight takes the place of the raw ring");
+    uint8_t *out_base = raw_base + RAWS * L::RAW_BYTES + STAGES * L::WSLAB_BYTES;      // ATMA: epilogue staging, 2 x 4 KB per warp
     // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], then ATMA: raw_full[RAWS], raw_empty[RAWS]; WTMA: landed[STAGES]
     uint8_t *table_base = out_base + L::OUT_BYTES;                            // backward-weight: per-warp row tables
     uint64_t *bars = (uint64_t *)(table_base + L::TABLE_BYTES);
-    constexpr int XBARS = WTMA ? STAGES : 2 * RAWS;
+    constexpr int XBARS = (WTMA || WSLAB) ? STAGES : 2 * RAWS;
     uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4 + XBARS);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     volatile int *progress = abort_flag + 1;              // last K-block (CTA sequence number) producer group 0 has stored
@@ -309,7 +317,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
         // a raw tile is filled by one expect_tx arrival plus the TMA bytes, and released by the four warps of the group that read it
         // (a slab serves nine K-blocks shared by both groups: all eight producer warps release it)
         for (int s = 0; s < RAWS; s++) { mbar_init(bar_raw_full + 8 * s, 1); mbar_init(bar_raw_empty + 8 * s, STMA ? 8 : 4); }
-        if constexpr (WTMA) for (int s = 0; s < STAGES; s++) mbar_init(bar_raw_full + 8 * s, 1);       // "landed": one expect_tx arrival + the bytes
+        if constexpr (WTMA || WSLAB) for (int s = 0; s < STAGES; s++) mbar_init(bar_raw_full + 8 * s, 1);       // "landed": one expect_tx arrival + the bytes
         *abort_flag = 0;
         *progress = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -320,6 +328,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
+    int fail_code = 0;          // which wait gave up (numbered in source order), reported through the status word
 
     // K-block range of a tile's split
     auto kb_range = [&](int t, int &kb0, int &nkb) {
@@ -348,7 +357,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             settle();
             for (int g = group; t < total_tiles; g += 2) {
                 const int s = g % STAGES;
-                if (!mbar_wait_warp(bar_raw_full + 8 * s, (g / STAGES) & 1, abort_flag)) { failed = true; break; }
+                if (!mbar_wait_warp(bar_raw_full + 8 * s, (g / STAGES) & 1, abort_flag)) { failed = true, fail_code = 1; break; }
                 uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
                 if constexpr (SPLIT3) {
                     uint8_t *sB_hi = sA_hi + 2 * L::A_BYTES;
@@ -364,6 +373,68 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     };
                     split_plane(sA_hi, sA_hi + L::A_BYTES, L::A_BYTES);
                     split_plane(sB_hi, sB_hi + L::B_BYTES, L::B_BYTES);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                it += 2; settle();
+            }
+        } else if constexpr (WSLAB) {
+            // K-block g of the CTA's sequence has landed in stage g % STAGES: the dy tile where the hi plane of B lives (already
+            // swizzled by the copy) and the raw slab of x beside the ring.  Warp wq of the group builds rows [32 wq, 32 wq + 32)
+            // of A -- row r = tap r % 9 of channel r / 9 -- with one lane per pixel: the value is the slab element at the
+            // pixel's position shifted by the tap, or zero where the tap leaves the image row (left / right edge; above and
+            // below the image the copy delivered zeros) or the pixel lies past the end of the plane.  Then the group splits B.
+            const int group = warp >> 2, wq = warp & 3, gtid = tid & 127;
+            const int W = P.img_w, cpi = P.chunks_per_image;
+            int tab[32];                        // (slab offset of the row's tap relative to the pixel) << 2 | which edge masks it
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const int r = wq * 32 + j, c_rel = r / 9, tap = r - 9 * c_rel, tr = tap / 3, ts = tap - 3 * tr;
+                tab[j] = r < WS_ROWS ? (c_rel * WS_SLAB_PX + (tr - 1) * W + (ts - 1)) * 4 + ts : 3;      // kind 3: a row that stays zero
+            }
+            uint32_t so[8];                     // this lane's byte offset inside a swizzled row whose number is e modulo 8
+#pragma unroll
+            for (int e = 0; e < 8; e++) so[e] = (uint32_t)(((((lane >> 2) ^ e) & 7) << 4) + ((lane & 3) << 2));
+            int t = blockIdx.x, kb0 = 0, nkb = 0, it = group;
+            auto settle = [&]() {
+                while (t < total_tiles) {
+                    kb_range(t, kb0, nkb);
+                    if (it < nkb) return;
+                    it -= nkb; t += gridDim.x;
+                }
+            };
+            settle();
+            for (int g = group; t < total_tiles; g += 2) {
+                const int s = g % STAGES;
+                if (!mbar_wait_warp(bar_raw_full + 8 * s, (g / STAGES) & 1, abort_flag)) { failed = true, fail_code = 2; break; }
+                const int x0 = ((kb0 + it) % cpi) * 32;
+                const int base = ((x0 - W - 1 + 4096) & ~3) - 4096;
+                const int px = x0 + lane, q = px % W;
+                const bool inside = px < P.plane_px;
+                // bit `kind` set = rows of that kind are zero for this lane: 0 left neighbour, 1 same column, 2 right neighbour, 3 always
+                const unsigned zero_bits = ((!inside || q == 0) ? 1u : 0u) | (!inside ? 2u : 0u) | ((!inside || q == W - 1) ? 4u : 0u) | 8u;
+                const float *slab = (const float *)(raw_base + s * L::WSLAB_BYTES) + (x0 - base + lane);
+                uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES + wq * (32 * 128);
+                uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const int e = tab[j];
+                    const float v = ((zero_bits >> (e & 3)) & 1u) ? 0.f : slab[e >> 2];
+                    const uint32_t off = (uint32_t)(j * 128) + so[j & 7];
+                    if (SPLIT3) { float hi, lo; split_tf32(v, hi, lo); *(float *)(sA_hi + off) = hi; *(float *)(sA_lo + off) = lo; }
+                    else *(float *)(sA_hi + off) = v;
+                }
+                if constexpr (SPLIT3) {
+                    uint8_t *sB_hi = stage_base + s * L::STAGE_BYTES + 2 * L::A_BYTES, *sB_lo = sB_hi + L::B_BYTES;
+#pragma unroll 4
+                    for (int off = gtid * 16; off < L::B_BYTES; off += 128 * 16) {
+                        const float4 v = *(const float4 *)(sB_hi + off);
+                        float4 hi, lo;
+                        split_tf32(v.x, hi.x, lo.x); split_tf32(v.y, hi.y, lo.y); split_tf32(v.z, hi.z, lo.z); split_tf32(v.w, hi.w, lo.w);
+                        *(float4 *)(sB_lo + off) = lo;
+                        if (!P.raw_hi) *(float4 *)(sB_hi + off) = hi;
+                    }
                 }
                 fence_async_smem();
                 __syncwarp();
@@ -428,7 +499,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             for (int g = group; t < total_tiles; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 3; break; }
                 store(s);
                 fence_async_smem();
                 __syncwarp();
@@ -576,11 +647,11 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                 }
             };
             settle();
-            if (t < total_tiles && !load_row(t, kb0, it, group)) failed = true;
+            if (t < total_tiles && !load_row(t, kb0, it, group)) failed = true, fail_code = 4;
             for (int g = group; t < total_tiles && !failed; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 5; break; }
                 if (arow == 0) {
                     // packed weights of this K-block / filter tile: one bulk copy into the stage's B_hi|B_lo area
                     const int n_tile = (t % tiles_mn) / P.tiles_m;
@@ -595,7 +666,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);      // one arrive per warp: 32 lanes on one barrier word serialise
                 if (tid == 0) *progress = g;        // paces the prefetch warp
                 it += 2; settle();
-                if (t < total_tiles && !load_row(t, kb0, it, g + 2)) failed = true;
+                if (t < total_tiles && !load_row(t, kb0, it, g + 2)) failed = true, fail_code = 6;
             }
         } else {
             // backward-weight: one lane per k.  As above, two groups of four warps take alternate K-blocks; a warp gathers
@@ -702,7 +773,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             for (int g = group; t < total_tiles; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 7; break; }
                 store_tiles(s);
                 fence_async_smem();
                 __syncwarp();
@@ -727,14 +798,14 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             const int nmain = P.nmain;
             for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x, local++) {
                 int kb0, nkb; kb_range(t, kb0, nkb);
-                if (!mbar_wait(bar_acc_empty + 8 * set, set_phase, abort_flag)) { failed = true; break; }
+                if (!mbar_wait(bar_acc_empty + 8 * set, set_phase, abort_flag)) { failed = true, fail_code = 8; break; }
                 tc_fence_after();
                 const uint32_t set_base = tmem_base + (uint32_t)(set * set_cols);
                 const uint32_t d_small = set_base + (uint32_t)small_off;
                 int rot = 0;                   // which of the rotating main accumulators the next k-step adds into
                 int fresh = nmain + 1;         // accumulators not written yet in this tile: the mains' first k-steps and the cross terms' first
                 for (int it = 0; it < nkb; it++) {
-                    if (!mbar_wait(bar_full + 8 * s, full_phase, abort_flag)) { failed = true; break; }
+                    if (!mbar_wait(bar_full + 8 * s, full_phase, abort_flag)) { failed = true, fail_code = 9; break; }
                     tc_fence_after();
                     const uint32_t a_hi = stage0_lo + s * STAGE_STEP;
                     const uint32_t a_lo = a_hi + A_STEP;
@@ -783,13 +854,36 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
                     for (int it = 0; it < nkb; it++, g++) {
                         const int s = g % STAGES;
-                        if (!mbar_wait(bar_empty + 8 * s, ((g / STAGES) & 1) ^ 1, abort_flag)) { failed = true; break; }
+                        if (!mbar_wait(bar_empty + 8 * s, ((g / STAGES) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 10; break; }
                         const int kbi = kb0 + it, img = kbi / P.chunks_per_image, x0 = (kbi % P.chunks_per_image) * 32;
                         const uint32_t dstA = smem_u32(stage_base + s * L::STAGE_BYTES);
                         const uint32_t dstB = dstA + (SPLIT3 ? 2 : 1) * L::A_BYTES;
                         mbar_expect_tx(bar_raw_full + 8 * s, (uint32_t)(L::A_BYTES + L::B_BYTES));
                         tma_load_3d(dstA, &P.mapA, x0, m0, img, bar_raw_full + 8 * s);
                         tma_load_3d(dstB, &P.mapOut, x0, n0, img, bar_raw_full + 8 * s);
+                    }
+                }
+            }
+            __syncwarp();
+        } else if constexpr (WSLAB) {
+            // lane 0 fills the stages: per K-block the dy tile ([BN filters][32 pixels], swizzled, into the hi plane of B) and the
+            // raw slab of x ([16 channels][160 pixels] starting W + 1 pixels before the K-block, rounded down to 16 bytes)
+            if (lane == 0) {
+                int g = 0;
+                const int W = P.img_w, cpi = P.chunks_per_image;
+                for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
+                    int kb0, nkb; kb_range(t, kb0, nkb);
+                    const int mn = t % tiles_mn;
+                    const int c0 = (mn % P.tiles_m) * WS_CH, n0 = (mn / P.tiles_m) * BN_;
+                    for (int it = 0; it < nkb; it++, g++) {
+                        const int s = g % STAGES;
+                        if (!mbar_wait(bar_empty + 8 * s, ((g / STAGES) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 11; break; }
+                        const int kbi = kb0 + it, img = kbi / cpi, x0 = (kbi % cpi) * 32;
+                        const int base = ((x0 - W - 1 + 4096) & ~3) - 4096;
+                        const uint32_t dstB = smem_u32(stage_base + s * L::STAGE_BYTES) + (SPLIT3 ? 2 : 1) * L::A_BYTES;
+                        mbar_expect_tx(bar_raw_full + 8 * s, (uint32_t)(L::B_BYTES + L::WSLAB_BYTES));
+                        tma_load_3d(dstB, &P.mapOut, x0, n0, img, bar_raw_full + 8 * s);
+                        tma_load_3d(smem_u32(raw_base + s * L::WSLAB_BYTES), &P.mapA, base, c0, img, bar_raw_full + 8 * s);
                     }
                 }
             }
@@ -806,7 +900,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     const int base = ((t0 - P.img_w - 1 + 4096) & ~3) - 4096;
                     for (int cg = 0; cg < nkb / 9; cg++, ss++) {
                         const int rs = ss & 1;
-                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((ss >> 1) & 1) ^ 1, abort_flag)) { failed = true; break; }
+                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((ss >> 1) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 12; break; }
                         mbar_expect_tx(bar_raw_full + 8 * rs, (uint32_t)(2 * L::RAW_BYTES));
                         tma_load_3d(smem_u32(raw_base + rs * (2 * L::RAW_BYTES)), &P.mapA, base, (kb0 / 9 + cg) * BK, img, bar_raw_full + 8 * rs);
                     }
@@ -827,7 +921,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     for (int j = 0; j < 4; j++) { zs[j] = (cm0 + j) / P.chunks_per_image; xs[j] = ((cm0 + j) % P.chunks_per_image) * 32; }
                     for (int it = 0; it < nkb; it++, g++) {
                         const int rs = g % RAWS;
-                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((g / RAWS) & 1) ^ 1, abort_flag)) { failed = true; break; }
+                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((g / RAWS) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 13; break; }
                         mbar_expect_tx(bar_raw_full + 8 * rs, (uint32_t)L::RAW_BYTES);
                         const uint32_t dst = smem_u32(raw_base + rs * L::RAW_BYTES);
 #pragma unroll
@@ -879,7 +973,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             const int mn = t % tiles_mn, split = t / tiles_mn;
             const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
             const int set = local % nsets;
-            if (!mbar_wait_warp(bar_acc_full + 8 * set, (local / nsets) & 1, abort_flag)) { failed = true; break; }
+            if (!mbar_wait_warp(bar_acc_full + 8 * set, (local / nsets) & 1, abort_flag)) { failed = true, fail_code = 14; break; }
             tc_fence_after();
             if constexpr (ATMA) {
                 // This warp's 32 rows are one 32-pixel chunk of one image.  Per 32 columns: drain the accumulators, write the
@@ -943,9 +1037,11 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                 continue;
             }
             const int m = m0 + quarter * 32 + lane;
-            const bool m_ok = m < P.M_total;
-            float *obase = P.out + (long long)split * P.split_stride + (m_ok ? (long long)__ldg(P.outM + m) : 0);
-            if (P.accumulate) {
+            // WSLAB: row r of tile tm is element tm * 126 + r of the (channel, tap) space (rows 126 and 127 hold nothing)
+            const int ws_off = (m0 / BM) * WS_ROWS + quarter * 32 + lane;
+            const bool m_ok = WSLAB ? (quarter * 32 + lane < WS_ROWS && ws_off < P.M_total) : m < P.M_total;
+            float *obase = P.out + (long long)split * P.split_stride + (m_ok ? (WSLAB ? (long long)ws_off : (long long)__ldg(P.outM + m)) : 0);
+            if (P.accumulate && !WSLAB) {
                 // The read-modify-write below waits on the old output values.  While this tile's MMAs are still running,
                 // pull the lines of the NEXT tile of this CTA into L2 (the first tile prefetches its own): lane j of the
                 // warp takes columns j, j + 32, ... of the warp's 32 rows (one 128-byte line each).
@@ -1034,7 +1130,8 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             __syncwarp();
         }
     }
-    if (failed) { *abort_flag = 1; atomicExch(P.status, 1); }
+    // status word: site of the first wait that gave up | warp << 8 | kernel variant (TMA mode << 16, WGRAD << 20, BGATHER << 21)
+    if (failed) { *abort_flag = 1; atomicCAS(P.status, 0, fail_code | (warp << 8) | (TMA << 16) | ((WGRAD ? 1 : 0) << 20) | ((BGATHER ? 1 : 0) << 21)); }
     tc_fence_before();
     __syncthreads();
     if (warp == 8) tmem_dealloc(tmem_base, 512);
@@ -1220,7 +1317,7 @@ __global__ void __launch_bounds__(256) pack_b_multi_kernel(const __grid_constant
 
 template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, int TMA = 0>
 int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
-    using L = Layout<BN_, PREC != 1, TMA == 1 || TMA == 3>;
+    using L = Layout<BN_, PREC != 1, TMA == 1 || TMA == 3, TMA == 4>;
     static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
     bool &configured = configured_dev[dev];
     if (!configured) {
@@ -1267,6 +1364,7 @@ bool encode_plane_map(CUtensorMap *map, const float *base, int pixels, int chann
 }
 int g_conv_tma = 2;            // eddlb200_set_option("conv_tma", 0 off / 1 stores only / 2 stores and adds)
 int g_conv_tma3 = 1;           // eddlb200_set_option("conv_tma_3x3", 0 / 1)
+int g_conv_wslab = 1;          // eddlb200_set_option("conv_tma_wgrad_3x3", 0 / 1)
 int g_conv_wtma = 2;           // eddlb200_set_option("conv_tma_wgrad", 0 off / 1 on / 2 on, landed values used as the hi plane as they are)
 
 int *g_status[EDDLB200_MAX_DEVICES] = {};
@@ -1408,6 +1506,18 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     }
     if (wtma) { T.check = 4; T.K_total = 0; T.K_pad = 0; }             // no k tables; check 4 keeps these tables apart in the cache
     int k_pad = wtma ? g.n * w_chunks * BK : T.K_pad;
+    // backward-weight of 3x3 stride-1 "same" layers: the dy operand by TMA as above, the x operand built in shared memory from
+    // raw slabs that TMA delivers (one per K-block for all nine taps of the tile's 14 channels)
+    bool wslab = mode == 2 && g_conv_wslab && g_conv_wtma > 0 && g.kr == 3 && g.kc == 3 && g.sr == 1 && g.sc == 1 && g.pt == 1 && g.pl == 1 &&
+                 g.ih == g.oh && g.iw == g.ow && g.iw >= 3 && 2 * (g.iw + 1) + BK + 3 <= WS_SLAB_PX && (g.oh * g.ow) % 4 == 0 && g.oh * g.ow >= 32 &&
+                 g.c >= WS_CH && g.k >= 32 && aligned16(srcA) && aligned16(srcB);
+    if (wslab) {
+        const int ws_bn = T.N_total <= 32 ? 32 : (T.N_total <= 64 ? 64 : 128);
+        P.chunks_per_image = w_chunks; P.images = g.n; P.raw_hi = g_conv_wtma > 1; P.img_w = g.iw; P.plane_px = g.oh * g.ow;
+        if (!encode_plane_map(&P.mapA, srcA, g.oh * g.ow, g.c, g.n, WS_SLAB_CH, false, WS_SLAB_PX) ||
+            !encode_plane_map(&P.mapOut, srcB, g.oh * g.ow, g.k, g.n, ws_bn, true)) wslab = false;
+    }
+    if (wslab) { T.check = 6; T.K_total = 0; T.K_pad = 0; k_pad = g.n * w_chunks * BK; }      // no k tables; check 6 keeps these tables apart in the cache
     // any backward-weight: dy alone has that property whatever the filter and stride
     const bool b_vector = mode == 2 && (g.oh * g.ow) % 4 == 0 && T.K_total % BK == 0 && aligned16(srcB);
     // forward / backward-data of a 1x1 stride-1 unpadded convolution: rows are pixels of one image plane, k is the channel,
@@ -1436,7 +1546,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         if (!encode_plane_map(&P.mapA, srcA, pq_, a_channels, g.n, BK, false, SLAB_PX) || !encode_plane_map(&P.mapOut, out, pq_, o_channels, g.n)) stma = false;
     }
     if (stma) { T.check = 5; T.M_total = 0; allow_split = false; T.K_pad = (a_channels + BK - 1) / BK * 9 * BK; T.K_total = T.K_pad; k_pad = T.K_pad; }
-    const int m_rows = atma ? g.n * chunks * 32 : stma ? g.n * tiles_per_image * BM : T.M_total;
+    const int m_rows = atma ? g.n * chunks * 32 : stma ? g.n * tiles_per_image * BM : wslab ? (g.c + WS_CH - 1) / WS_CH * BM : T.M_total;
     // the compact k table keeps 27 bits of offset beside the 5-bit tap number
     if (T.check == 1 && (long long)(g.c > g.k ? g.c : g.k) * (g.ih * g.iw > g.oh * g.ow ? g.ih * g.iw : g.oh * g.ow) + (long long)(g.kr + 1) * (g.iw + g.ow) >= (1ll << 26)) T.check = 2;
     P.check = T.check;
@@ -1527,7 +1637,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     }
     P.srcA = srcA; P.srcB = srcB;
     P.rowA = T.rowA; P.kA = T.kA; P.rowB = T.rowB; P.kB = T.kB; P.outM = T.outM; P.kC = T.kC;
-    P.M_total = m_rows; P.N_total = T.N_total; P.K_pad = k_pad;
+    P.M_total = wslab ? T.M_total : m_rows; P.N_total = T.N_total; P.K_pad = k_pad;      // slab-fed backward-weight: the real (channel, tap) count
     P.kblocks_per_split = kbs;
     P.tiles_m = tiles_m; P.tiles_n = tiles_n; P.splits = splits;
     // a single accumulator drifts by ~2.5e-6 at 64 k-steps (K = 512); longer chains rotate over three
@@ -1541,6 +1651,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     int r;
     // backward-weight has no bf16 variant: precision 2 runs it as precision 0
     if (wtma) r = precision != 1 ? launch_bn<0, false, true, 2>(cx, st, P, grid, bn, dev) : launch_bn<1, false, true, 2>(cx, st, P, grid, bn, dev);
+    else if (wslab) r = precision != 1 ? launch_bn<0, false, true, 4>(cx, st, P, grid, bn, dev) : launch_bn<1, false, true, 4>(cx, st, P, grid, bn, dev);
     else if (mode == 2 && both_rowmajor) r = precision != 1 ? launch_bn<0, false, true>(cx, st, P, grid, bn, dev) : launch_bn<1, false, true>(cx, st, P, grid, bn, dev);
     else if (mode == 2 && b_vector) r = precision != 1 ? launch_bn<0, true, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true, true>(cx, st, P, grid, bn, dev);
     else if (mode == 2) r = precision != 1 ? launch_bn<0, true>(cx, st, P, grid, bn, dev) : launch_bn<1, true>(cx, st, P, grid, bn, dev);
@@ -1686,6 +1797,7 @@ int conv_tc_set_prefetch(int on) { g_conv_prefetch = on ? 1 : 0; return 0; }
 int conv_tc_set_tma(int level) { g_conv_tma = level < 0 ? 0 : (level > 2 ? 2 : level); return 0; }
 int conv_tc_set_pack_cache(int on) { g_conv_pack_cache = on ? 1 : 0; return 0; }
 int conv_tc_set_tma_3x3(int on) { g_conv_tma3 = on ? 1 : 0; return 0; }
+int conv_tc_set_tma_wgrad_3x3(int on) { g_conv_wslab = on ? 1 : 0; return 0; }
 int conv_tc_set_tma_wgrad(int level) { g_conv_wtma = level < 0 ? 0 : (level > 2 ? 2 : level); return 0; }
 
 // 0 = no kernel of this file has timed out on the device since the last call

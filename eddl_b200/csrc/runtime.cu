@@ -510,7 +510,7 @@ int eddlb200_sync(int dev) {
     if (cx->comm_stream) { if (int r = cuda_status(cudaStreamSynchronize(cx->comm_stream), "eddlb200_sync(communication stream)")) return r; cx->avg_pending.clear(); }
     int flag = 0;
     if (int r = conv_tc_status(dev, st, &flag)) return cuda_status((cudaError_t)r, "eddlb200_sync");
-    if (flag) return set_error(EDDLB200_ETIMEOUT, "a tensor-core convolution kernel gave up waiting on a pipeline barrier");
+    if (flag) return set_error(EDDLB200_ETIMEOUT, "a tensor-core convolution kernel gave up waiting on a pipeline barrier (site %d, warp %d, variant 0x%x)", flag & 0xff, (flag >> 8) & 0xff, flag >> 16);
     return 0;
 }
 

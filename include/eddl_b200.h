@@ -269,6 +269,10 @@ int eddlb200_reduce_sum2d(int dev, const float *a, float *b, int rows, int cols,
  *          straight into the operand ring and the landed fp32 values serve as the hi planes as they are (the tensor core
  *          reads only their upper 19 bits: same bits as 1); 1 = the hi planes are rewritten with the low bits cleared;
  *          0 = the gather kernel.
+ *          "conv_tma_wgrad_3x3" 1 (default) = backward-weight of 3x3 stride-1 pad-1 layers (rows of at most 60 pixels, planes of a
+ *          multiple of 4 pixels, at least 14 channels and 32 filters): dy is copied by TMA into the operand ring and the
+ *          tap-shifted x operand is built in shared memory from raw slabs that TMA delivers, one per K-block for the nine
+ *          taps of 14 channels; 0 = the gather kernel.  Agreement to rounding (K-blocks end at image boundaries).
  *          "conv_dense_1x1" 1 (default) = 1x1 unpadded layers that skip pixels (stride > 1) or whose planes are not a
  *          multiple of 4 pixels run as dense 1x1 stride-1 layers over gathered copies of their operands (library-owned
  *          device buffers that only grow); 0 = the strided gather kernels.  Agreement to rounding.

@@ -74,7 +74,7 @@ def test_tuning_options_are_host_side_switches():
     cdll.eddlb200_set_option.restype = ctypes.c_int
     for name, value in ((b"conv_prefetch", 0), (b"conv_prefetch", 1), (b"bn_waves", 4), (b"bn_waves", 16),
                         (b"bn_min_items", 2048), (b"bn_min_items", 8192), (b"conv_path", 0), (b"conv_tma", 0), (b"conv_tma", 2), (b"conv_tma_wgrad", 0), (b"conv_tma_wgrad", 2),
-                        (b"conv_tma_3x3", 0), (b"conv_tma_3x3", 1), (b"conv_dense_1x1", 0), (b"conv_dense_1x1", 1), (b"conv_pack_cache", 0), (b"conv_pack_cache", 1)):
+                        (b"conv_tma_3x3", 0), (b"conv_tma_3x3", 1), (b"conv_tma_wgrad_3x3", 0), (b"conv_tma_wgrad_3x3", 1), (b"conv_dense_1x1", 0), (b"conv_dense_1x1", 1), (b"conv_pack_cache", 0), (b"conv_pack_cache", 1)):
         assert cdll.eddlb200_set_option(name, value) == 0, (name, value)
     for name, value in ((b"conv_prefetch", 2), (b"bn_waves", 0), (b"no_such_option", 1), (b"conv_path", 7), (b"conv_tma", 3), (b"conv_tma_3x3", 2),
                         (b"conv_dense_1x1", -1)):

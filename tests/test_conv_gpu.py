@@ -420,3 +420,35 @@ def test_conv_path_counts_tell_fallbacks_from_tensor_core_calls(lib):
         lib.call("set_option", b"conv_path", 0)
     t2, f2 = counts()
     assert (t2 - t1, f2 - f1) == (0, 3)
+
+
+WSLAB_SHAPES = SLAB_SHAPES + [(2, 20, 6, 6, 32), (5, 14, 10, 10, 40), (2, 15, 8, 12, 33)]
+
+
+@pytest.mark.parametrize("shape", WSLAB_SHAPES)
+def test_slab_fed_backward_weight_of_3x3_layers(lib, shape):
+    """Backward-weight of 3x3 stride-1 pad-1 layers with the x operand built from TMA-delivered slabs (tiles of 14 channels x 9
+    taps, K-blocks of 32 pixels of one image): into zeros and into a non-zero gradient, with the bias gradient, against the
+    oracle within 1e-5 and against the gather kernel to rounding (the reduction is cut into other K-blocks: an image's last
+    chunk is padded instead of running on into the next image)."""
+    n, c, h, w, k = shape
+    rng = np.random.default_rng(83)
+    x = rng.standard_normal((n, c, h, w)).astype(F); wt = rng.standard_normal((k, c, 3, 3)).astype(F)
+    b = rng.standard_normal(k).astype(F)
+    dy = rng.standard_normal((n, k, h, w)).astype(F)
+    gw0 = rng.standard_normal(wt.shape).astype(F); gb0 = rng.standard_normal(k).astype(F)
+    out = {}
+    for level in (0, 1):
+        try:
+            lib.call("set_option", b"conv_tma_wgrad_3x3", level)
+            r1 = run_conv(lib, x, wt, b, dy, gw0, gb0, None, (1, 1), (1, 1, 1, 1))
+            r2 = run_conv(lib, x, wt, None, dy, None, None, None, (1, 1), (1, 1, 1, 1))
+        finally:
+            lib.call("set_option", b"conv_tma_wgrad_3x3", 1)
+        out[level] = (r1["gw"], r1["gb"], r2["gw"])
+    lib.call("sync", 0)
+    g1, gb1 = orc.conv2d_bwd_weight(x, dy, gw0, gb0, (1, 1), (1, 1, 1, 1), (3, 3))
+    g2, _ = orc.conv2d_bwd_weight(x, dy, None, None, (1, 1), (1, 1, 1, 1), (3, 3))
+    for a, bb, wv, name in zip(out[0], out[1], (g1, gb1, g2), ("gw accumulated", "bias gradient", "gw into zeros")):
+        assert relerr(bb, wv) <= 1e-5, name
+        assert relerr(a, bb) <= 3e-6, name

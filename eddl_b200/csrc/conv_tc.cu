@@ -44,6 +44,7 @@
 #include <array>
 #include <map>
 #include <mutex>
+#include <type_traits>
 #include <vector>
 #include "common.cuh"
 #include "conv_common.cuh"
@@ -62,9 +63,9 @@ constexpr int NTHREADS = NPROD + 32 + NEPI + 32;     // + warp 13: L2 prefetch o
 constexpr int NTHREADS_ATMA = NTHREADS + NEPI;
 constexpr int threads_of(int tma) { return (tma == 1 || tma == 3) ? NTHREADS_ATMA : NTHREADS; }
 // backward-weight of 3x3 stride-1 pad-1 layers fed from raw slabs (TMA = 4): a tile's 128 rows are the nine taps of 14 channels
-// (126 rows, the last two stay zero) and a K-block is 32 pixels of one image; one slab of [16 channels][160 pixels] -- the 32
-// pixels plus a halo of W + 1 either side, its start rounded down to 16 bytes -- serves all 126 rows
-constexpr int WS_CH = 14, WS_ROWS = 9 * WS_CH, WS_SLAB_PX = 160, WS_SLAB_CH = 16;
+// (126 rows, the last two stay zero) and a K-block is 32 pixels of one image; one slab of [16 channels][152 pixels] -- the 32
+// pixels plus a halo of W + 1 either side, its start rounded down to 16 bytes -- serves all 126 rows (W <= 57)
+constexpr int WS_CH = 14, WS_ROWS = 9 * WS_CH, WS_SLAB_PX = 152, WS_SLAB_CH = 16;
 constexpr int SLAB_PX = 256;        // pixels per channel of a raw slab (3x3 TMA-fed kernels): 128 rows + a halo of W + 1 either side + alignment
 constexpr int PF_AHEAD = 8;         // K-blocks the prefetch warp may run ahead of the producers
 constexpr int INVALID_Y = -20000;
@@ -248,6 +249,25 @@ struct Layout {
     static_assert(SMEM_BYTES <= 232448, "shared memory of a CTA");
 };
 
+// Shared memory of the TMA-fed backward-weight kernels (WTMA, WSLAB).  What TMA delivers -- the dy tile in its final place
+// as the hi plane of B, and the x tile as the hi plane of A (WTMA) or the raw slab of x (WSLAB) -- lives in a HI ring that is
+// as deep as shared memory allows: a copy takes about 2700 cycles from issue to landing (measured, L2 hits included), twice
+// the 1284 cycles of a K-block's MMAs, so three or more K-blocks must be in flight beside the one being converted and the one
+// being multiplied.  What the producer warps compute -- the lo planes, and for WSLAB the whole A operand -- lives in a LO ring
+// of two slots, one per producer group: it is occupied only from the conversion to the end of the K-block's MMAs.
+template <int BN_, bool SPLIT3, bool WSLAB>
+struct WLayout {
+    static constexpr int A_BYTES = BM * BK * 4;
+    static constexpr int B_BYTES = BN_ * BK * 4;
+    static constexpr int X_BYTES = WSLAB ? WS_SLAB_CH * WS_SLAB_PX * 4 : A_BYTES;       // what lands beside the dy tile
+    static constexpr int LO_BYTES = WSLAB ? (SPLIT3 ? 2 : 1) * A_BYTES + (SPLIT3 ? B_BYTES : 0) : (SPLIT3 ? A_BYTES + B_BYTES : 0);
+    static constexpr int LO_SLOTS = 2;
+    static constexpr int BUDGET = 232448 - 1024 - 256 - LO_SLOTS * LO_BYTES;
+    static constexpr int HI_SLOTS = BUDGET / (B_BYTES + X_BYTES) > 6 ? 6 : BUDGET / (B_BYTES + X_BYTES);
+    static_assert(HI_SLOTS >= 3, "the landing ring needs three slots");
+    static constexpr int SMEM_BYTES = 1024 + HI_SLOTS * (B_BYTES + X_BYTES) + LO_SLOTS * LO_BYTES + 256;
+};
+
 // Persistent, warp-specialised kernel: each CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the
 // (split, filter tile, row tile) space.
 //   warps 0-7   producers: gather / split / store the A tile (and B for backward-weight).  Forward / backward-data: two
@@ -291,8 +311,15 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
     uint8_t *out_base = raw_base + RAWS * L::RAW_BYTES + STAGES * L::WSLAB_BYTES;      // ATMA: epilogue staging, 2 x 4 KB per warp
     // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], then ATMA: raw_full[RAWS], raw_empty[RAWS]; WTMA: landed[STAGES]
     uint8_t *table_base = out_base + L::OUT_BYTES;                            // backward-weight: per-warp row tables
-    uint64_t *bars = (uint64_t *)(table_base + L::TABLE_BYTES);
-    constexpr int XBARS = (WTMA || WSLAB) ? STAGES : 2 * RAWS;
+    constexpr bool WMODE = WTMA || WSLAB;
+    static_assert(!WMODE || (2 * STAGES + 4 + 2 * WLayout<BN_, SPLIT3, WSLAB>::HI_SLOTS) * 8 + 16 <= 256, "barrier words");
+    using WL = WLayout<BN_, SPLIT3, WSLAB>;
+    constexpr int HS = WMODE ? WL::HI_SLOTS : 0;
+    // WMODE: [dy tiles: HS x B_BYTES][LO ring: 2 x LO_BYTES][x tiles or slabs: HS x X_BYTES], all swizzled tiles 1024-byte aligned
+    uint8_t *w_hib = smem, *w_lo = smem + HS * WL::B_BYTES, *w_x = w_lo + WL::LO_SLOTS * WL::LO_BYTES;
+    if constexpr (WMODE) table_base = w_x + HS * WL::X_BYTES;       // the barrier words follow
+    constexpr int XBARS = WMODE ? 2 * HS : 2 * RAWS;
+    uint64_t *bars = (uint64_t *)(table_base + (WMODE ? 0 : L::TABLE_BYTES));
     uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4 + XBARS);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     volatile int *progress = abort_flag + 1;              // last K-block (CTA sequence number) producer group 0 has stored
@@ -317,7 +344,8 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
         // a raw tile is filled by one expect_tx arrival plus the TMA bytes, and released by the four warps of the group that read it
         // (a slab serves nine K-blocks shared by both groups: all eight producer warps release it)
         for (int s = 0; s < RAWS; s++) { mbar_init(bar_raw_full + 8 * s, 1); mbar_init(bar_raw_empty + 8 * s, STMA ? 8 : 4); }
-        if constexpr (WTMA || WSLAB) for (int s = 0; s < STAGES; s++) mbar_init(bar_raw_full + 8 * s, 1);       // "landed": one expect_tx arrival + the bytes
+        // WMODE: landed[HS] (one expect_tx arrival + the bytes) and hi_empty[HS] (one commit of the MMA thread)
+        if constexpr (WMODE) for (int s = 0; s < 2 * HS; s++) mbar_init(bar_raw_full + 8 * s, 1);
         *abort_flag = 0;
         *progress = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -341,10 +369,10 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
         // ============================ producers ============================
         constexpr uint32_t B_IMAGE = (uint32_t)L::B_BYTES * (SPLIT3 ? 2u : 1u);
         if constexpr (WTMA) {
-            // The raw fp32 tiles of K-block g have landed in stage g % STAGES (A rows where the hi plane of A lives, B rows
-            // where the hi plane of B lives, both already swizzled by the copy).  The group's 128 threads walk them 16 bytes
-            // at a time -- the split is elementwise, so the swizzle does not matter -- and write lo = v - hi to the lo plane
-            // and, unless the tensor core is known to ignore the low mantissa bits itself, hi back in place.
+            // The raw fp32 tiles of K-block g have landed in HI slot g % HS, already swizzled by the copy: they ARE the hi planes
+            // (the tensor core reads only the upper 19 bits of a TF32 operand).  The group's 128 threads walk them 16 bytes at a
+            // time -- the split is elementwise, so the swizzle does not matter -- and write lo = v - hi into the group's LO slot
+            // (and, unless raw_hi, hi back in place).
             const int group = warp >> 2, gtid = tid & 127;
             int t = blockIdx.x, kb0 = 0, nkb = 0, it = group;
             auto settle = [&]() {
@@ -356,32 +384,37 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             };
             settle();
             for (int g = group; t < total_tiles; g += 2) {
-                const int s = g % STAGES;
-                if (!mbar_wait_warp(bar_raw_full + 8 * s, (g / STAGES) & 1, abort_flag)) { failed = true, fail_code = 1; break; }
-                uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES;
+                const int h = g % HS, l = group;
+                if (!mbar_wait_warp(bar_raw_full + 8 * h, (g / HS) & 1, abort_flag)) { failed = true, fail_code = 1; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * l, ((g >> 1) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 2; break; }
                 if constexpr (SPLIT3) {
-                    uint8_t *sB_hi = sA_hi + 2 * L::A_BYTES;
-                    auto split_plane = [&](uint8_t *hi_plane, uint8_t *lo_plane, int bytes) {
-#pragma unroll 4
-                        for (int off = gtid * 16; off < bytes; off += 128 * 16) {
-                            const float4 v = *(const float4 *)(hi_plane + off);
+                    uint8_t *lo_slot = w_lo + l * WL::LO_BYTES;
+                    // all of a plane's loads go out before its first store: the compiler cannot move a shared-memory load above
+                    // an earlier shared-memory store, so load / split / store per piece would cost one load latency per piece
+                    auto split_plane = [&](uint8_t *hi_plane, uint8_t *lo_plane, auto bytes_c) {
+                        constexpr int PIECES = decltype(bytes_c)::value / (128 * 16);
+                        float4 v[PIECES];
+#pragma unroll
+                        for (int i = 0; i < PIECES; i++) v[i] = *(const float4 *)(hi_plane + (gtid + 128 * i) * 16);
+#pragma unroll
+                        for (int i = 0; i < PIECES; i++) {
                             float4 hi, lo;
-                            split_tf32(v.x, hi.x, lo.x); split_tf32(v.y, hi.y, lo.y); split_tf32(v.z, hi.z, lo.z); split_tf32(v.w, hi.w, lo.w);
-                            *(float4 *)(lo_plane + off) = lo;
-                            if (!P.raw_hi) *(float4 *)(hi_plane + off) = hi;
+                            split_tf32(v[i].x, hi.x, lo.x); split_tf32(v[i].y, hi.y, lo.y); split_tf32(v[i].z, hi.z, lo.z); split_tf32(v[i].w, hi.w, lo.w);
+                            *(float4 *)(lo_plane + (gtid + 128 * i) * 16) = lo;
+                            if (!P.raw_hi) *(float4 *)(hi_plane + (gtid + 128 * i) * 16) = hi;
                         }
                     };
-                    split_plane(sA_hi, sA_hi + L::A_BYTES, L::A_BYTES);
-                    split_plane(sB_hi, sB_hi + L::B_BYTES, L::B_BYTES);
+                    split_plane(w_x + h * WL::X_BYTES, lo_slot, std::integral_constant<int, WL::A_BYTES>{});
+                    split_plane(w_hib + h * WL::B_BYTES, lo_slot + WL::A_BYTES, std::integral_constant<int, WL::B_BYTES>{});
                 }
                 fence_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                if (lane == 0) mbar_arrive(bar_full + 8 * l);
                 it += 2; settle();
             }
         } else if constexpr (WSLAB) {
-            // K-block g of the CTA's sequence has landed in stage g % STAGES: the dy tile where the hi plane of B lives (already
-            // swizzled by the copy) and the raw slab of x beside the ring.  Warp wq of the group builds rows [32 wq, 32 wq + 32)
+            // K-block g of the CTA's sequence has landed in HI slot g % HS: the dy tile (the hi plane of B, already swizzled by the
+            // copy) and the raw slab of x.  Warp wq of the group builds rows [32 wq, 32 wq + 32)
             // of A -- row r = tap r % 9 of channel r / 9 -- with one lane per pixel: the value is the slab element at the
             // pixel's position shifted by the tap, or zero where the tap leaves the image row (left / right edge; above and
             // below the image the copy delivered zeros) or the pixel lies past the end of the plane.  Then the group splits B.
@@ -406,39 +439,46 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             };
             settle();
             for (int g = group; t < total_tiles; g += 2) {
-                const int s = g % STAGES;
-                if (!mbar_wait_warp(bar_raw_full + 8 * s, (g / STAGES) & 1, abort_flag)) { failed = true, fail_code = 2; break; }
+                const int h = g % HS, l = group;
+                if (!mbar_wait_warp(bar_raw_full + 8 * h, (g / HS) & 1, abort_flag)) { failed = true, fail_code = 3; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * l, ((g >> 1) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 4; break; }
                 const int x0 = ((kb0 + it) % cpi) * 32;
                 const int base = ((x0 - W - 1 + 4096) & ~3) - 4096;
                 const int px = x0 + lane, q = px % W;
                 const bool inside = px < P.plane_px;
                 // bit `kind` set = rows of that kind are zero for this lane: 0 left neighbour, 1 same column, 2 right neighbour, 3 always
                 const unsigned zero_bits = ((!inside || q == 0) ? 1u : 0u) | (!inside ? 2u : 0u) | ((!inside || q == W - 1) ? 4u : 0u) | 8u;
-                const float *slab = (const float *)(raw_base + s * L::WSLAB_BYTES) + (x0 - base + lane);
-                uint8_t *sA_hi = stage_base + s * L::STAGE_BYTES + wq * (32 * 128);
-                uint8_t *sA_lo = sA_hi + L::A_BYTES;                      // only when SPLIT3
+                const float *slab = (const float *)(w_x + h * WL::X_BYTES) + (x0 - base + lane);
+                uint8_t *sA_hi = w_lo + l * WL::LO_BYTES + wq * (32 * 128);
+                uint8_t *sA_lo = sA_hi + WL::A_BYTES;                     // only when SPLIT3
+                // all loads before the first store (a shared-memory load cannot be moved above an earlier shared-memory store)
+                float av[32];
+#pragma unroll
+                for (int j = 0; j < 32; j++) av[j] = slab[tab[j] >> 2];
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
-                    const int e = tab[j];
-                    const float v = ((zero_bits >> (e & 3)) & 1u) ? 0.f : slab[e >> 2];
+                    const float v = ((zero_bits >> (tab[j] & 3)) & 1u) ? 0.f : av[j];
                     const uint32_t off = (uint32_t)(j * 128) + so[j & 7];
                     if (SPLIT3) { float hi, lo; split_tf32(v, hi, lo); *(float *)(sA_hi + off) = hi; *(float *)(sA_lo + off) = lo; }
                     else *(float *)(sA_hi + off) = v;
                 }
                 if constexpr (SPLIT3) {
-                    uint8_t *sB_hi = stage_base + s * L::STAGE_BYTES + 2 * L::A_BYTES, *sB_lo = sB_hi + L::B_BYTES;
-#pragma unroll 4
-                    for (int off = gtid * 16; off < L::B_BYTES; off += 128 * 16) {
-                        const float4 v = *(const float4 *)(sB_hi + off);
+                    uint8_t *sB_hi = w_hib + h * WL::B_BYTES, *sB_lo = w_lo + l * WL::LO_BYTES + 2 * WL::A_BYTES;
+                    constexpr int PIECES = WL::B_BYTES / (128 * 16);
+                    float4 bv[PIECES];
+#pragma unroll
+                    for (int i = 0; i < PIECES; i++) bv[i] = *(const float4 *)(sB_hi + (gtid + 128 * i) * 16);
+#pragma unroll
+                    for (int i = 0; i < PIECES; i++) {
                         float4 hi, lo;
-                        split_tf32(v.x, hi.x, lo.x); split_tf32(v.y, hi.y, lo.y); split_tf32(v.z, hi.z, lo.z); split_tf32(v.w, hi.w, lo.w);
-                        *(float4 *)(sB_lo + off) = lo;
-                        if (!P.raw_hi) *(float4 *)(sB_hi + off) = hi;
+                        split_tf32(bv[i].x, hi.x, lo.x); split_tf32(bv[i].y, hi.y, lo.y); split_tf32(bv[i].z, hi.z, lo.z); split_tf32(bv[i].w, hi.w, lo.w);
+                        *(float4 *)(sB_lo + (gtid + 128 * i) * 16) = lo;
+                        if (!P.raw_hi) *(float4 *)(sB_hi + (gtid + 128 * i) * 16) = hi;
                     }
                 }
                 fence_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                if (lane == 0) mbar_arrive(bar_full + 8 * l);
                 it += 2; settle();
             }
         } else if constexpr (BGATHER && !WGRAD) {
@@ -499,7 +539,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             for (int g = group; t < total_tiles; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 3; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 5; break; }
                 store(s);
                 fence_async_smem();
                 __syncwarp();
@@ -647,11 +687,11 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                 }
             };
             settle();
-            if (t < total_tiles && !load_row(t, kb0, it, group)) failed = true, fail_code = 4;
+            if (t < total_tiles && !load_row(t, kb0, it, group)) failed = true, fail_code = 6;
             for (int g = group; t < total_tiles && !failed; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 5; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 7; break; }
                 if (arow == 0) {
                     // packed weights of this K-block / filter tile: one bulk copy into the stage's B_hi|B_lo area
                     const int n_tile = (t % tiles_mn) / P.tiles_m;
@@ -666,7 +706,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);      // one arrive per warp: 32 lanes on one barrier word serialise
                 if (tid == 0) *progress = g;        // paces the prefetch warp
                 it += 2; settle();
-                if (t < total_tiles && !load_row(t, kb0, it, g + 2)) failed = true, fail_code = 6;
+                if (t < total_tiles && !load_row(t, kb0, it, g + 2)) failed = true, fail_code = 8;
             }
         } else {
             // backward-weight: one lane per k.  As above, two groups of four warps take alternate K-blocks; a warp gathers
@@ -773,7 +813,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             for (int g = group; t < total_tiles; g += 2) {
                 const int s = g % STAGES;
                 const uint32_t par = ((g / STAGES) & 1) ^ 1;
-                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 7; break; }
+                if (!mbar_wait_warp(bar_empty + 8 * s, par, abort_flag)) { failed = true, fail_code = 9; break; }
                 store_tiles(s);
                 fence_async_smem();
                 __syncwarp();
@@ -794,23 +834,32 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             const uint32_t stage0_lo = ((smem_u32(stage_base) >> 4) & 0x3FFFu) | (1u << 16);
             constexpr uint32_t STAGE_STEP = (uint32_t)L::STAGE_BYTES >> 4, A_STEP = (uint32_t)L::A_BYTES >> 4, B_STEP = (uint32_t)L::B_BYTES >> 4;
             int local = 0, set = 0;
-            uint32_t s = 0, full_phase = 0, set_phase = 1;
+            uint32_t s = 0, full_phase = 0, set_phase = 1, wh = 0;
+            auto lo_word = [&](const uint8_t *ptr) { return ((smem_u32(ptr) >> 4) & 0x3FFFu) | (1u << 16); };
+            const uint32_t w_hib_lo = lo_word(w_hib), w_lo_lo = lo_word(w_lo), w_x_lo = lo_word(w_x);
             const int nmain = P.nmain;
             for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x, local++) {
                 int kb0, nkb; kb_range(t, kb0, nkb);
-                if (!mbar_wait(bar_acc_empty + 8 * set, set_phase, abort_flag)) { failed = true, fail_code = 8; break; }
+                if (!mbar_wait(bar_acc_empty + 8 * set, set_phase, abort_flag)) { failed = true, fail_code = 10; break; }
                 tc_fence_after();
                 const uint32_t set_base = tmem_base + (uint32_t)(set * set_cols);
                 const uint32_t d_small = set_base + (uint32_t)small_off;
                 int rot = 0;                   // which of the rotating main accumulators the next k-step adds into
                 int fresh = nmain + 1;         // accumulators not written yet in this tile: the mains' first k-steps and the cross terms' first
                 for (int it = 0; it < nkb; it++) {
-                    if (!mbar_wait(bar_full + 8 * s, full_phase, abort_flag)) { failed = true, fail_code = 9; break; }
+                    if (!mbar_wait(bar_full + 8 * s, full_phase, abort_flag)) { failed = true, fail_code = 11; break; }
                     tc_fence_after();
-                    const uint32_t a_hi = stage0_lo + s * STAGE_STEP;
-                    const uint32_t a_lo = a_hi + A_STEP;
-                    const uint32_t b_hi = a_hi + (SPLIT3 ? 2u : 1u) * A_STEP;
-                    const uint32_t b_lo = b_hi + B_STEP;
+                    uint32_t a_hi = stage0_lo + s * STAGE_STEP;
+                    uint32_t a_lo = a_hi + A_STEP;
+                    uint32_t b_hi = a_hi + (SPLIT3 ? 2u : 1u) * A_STEP;
+                    uint32_t b_lo = b_hi + B_STEP;
+                    if constexpr (WMODE) {
+                        // s is the LO slot (0 / 1), wh the HI slot: hi planes where TMA put them, the rest in the LO slot
+                        const uint32_t lo_slot = w_lo_lo + s * ((uint32_t)WL::LO_BYTES >> 4);
+                        b_hi = w_hib_lo + wh * B_STEP;
+                        if constexpr (WTMA) { a_hi = w_x_lo + wh * A_STEP; a_lo = lo_slot; b_lo = lo_slot + A_STEP; }
+                        else { a_hi = lo_slot; a_lo = lo_slot + A_STEP; b_lo = lo_slot + (SPLIT3 ? 2u : 1u) * A_STEP; }
+                    }
 #pragma unroll
                     for (int ks = 0; ks < BK / 8; ks++) {
                         const uint32_t o = 2u * ks;      // 8 fp32 = 32 bytes along K inside the swizzle row = 2 units of 16 bytes
@@ -828,8 +877,12 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                         if (fresh > 1) fresh--;
                         if (++rot == nmain) rot = 0;
                     }
-                    umma_commit(bar_empty + 8 * s);      // frees the stage when these MMAs have read it
-                    if (++s == (uint32_t)STAGES) { s = 0; full_phase ^= 1u; }
+                    umma_commit(bar_empty + 8 * s);      // frees the stage (WMODE: the LO slot) when these MMAs have read it
+                    if constexpr (WMODE) {
+                        umma_commit(bar_raw_full + 8 * (HS + wh));      // ... and the HI slot
+                        if (++wh == (uint32_t)HS) wh = 0;
+                        if (++s == 2u) { s = 0; full_phase ^= 1u; }
+                    } else if (++s == (uint32_t)STAGES) { s = 0; full_phase ^= 1u; }
                 }
                 if (!failed) umma_commit(bar_acc_full + 8 * set);     // this tile's accumulators are complete
                 if (++set == nsets) { set = 0; set_phase ^= 1u; }
@@ -844,8 +897,8 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
         // rows are consecutive pixels, so that is every line the producers will read, and their loads then hit in L2.
         // Nothing waits on this warp; its own wait on the producers' progress is bounded and it simply stops on a time-out.
         if constexpr (WTMA) {
-            // lane 0 fills the operand ring: for K-block number g of the CTA's sequence, 32 pixels of one image for the
-            // tile's 128 channel rows of x (A) and its BN filter rows of dy (B), as soon as the MMAs have released the stage
+            // lane 0 fills the HI ring: for K-block number g of the CTA's sequence, 32 pixels of one image for the tile's 128
+            // channel rows of x (A) and its BN filter rows of dy (B), as soon as the MMAs have released the slot
             if (lane == 0) {
                 int g = 0;
                 for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
@@ -853,21 +906,19 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     const int mn = t % tiles_mn;
                     const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
                     for (int it = 0; it < nkb; it++, g++) {
-                        const int s = g % STAGES;
-                        if (!mbar_wait(bar_empty + 8 * s, ((g / STAGES) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 10; break; }
+                        const int h = g % HS;
+                        if (!mbar_wait(bar_raw_full + 8 * (HS + h), ((g / HS) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 12; break; }
                         const int kbi = kb0 + it, img = kbi / P.chunks_per_image, x0 = (kbi % P.chunks_per_image) * 32;
-                        const uint32_t dstA = smem_u32(stage_base + s * L::STAGE_BYTES);
-                        const uint32_t dstB = dstA + (SPLIT3 ? 2 : 1) * L::A_BYTES;
-                        mbar_expect_tx(bar_raw_full + 8 * s, (uint32_t)(L::A_BYTES + L::B_BYTES));
-                        tma_load_3d(dstA, &P.mapA, x0, m0, img, bar_raw_full + 8 * s);
-                        tma_load_3d(dstB, &P.mapOut, x0, n0, img, bar_raw_full + 8 * s);
+                        mbar_expect_tx(bar_raw_full + 8 * h, (uint32_t)(WL::A_BYTES + WL::B_BYTES));
+                        tma_load_3d(smem_u32(w_x + h * WL::X_BYTES), &P.mapA, x0, m0, img, bar_raw_full + 8 * h);
+                        tma_load_3d(smem_u32(w_hib + h * WL::B_BYTES), &P.mapOut, x0, n0, img, bar_raw_full + 8 * h);
                     }
                 }
             }
             __syncwarp();
         } else if constexpr (WSLAB) {
-            // lane 0 fills the stages: per K-block the dy tile ([BN filters][32 pixels], swizzled, into the hi plane of B) and the
-            // raw slab of x ([16 channels][160 pixels] starting W + 1 pixels before the K-block, rounded down to 16 bytes)
+            // lane 0 fills the HI ring: per K-block the dy tile ([BN filters][32 pixels], swizzled: the hi plane of B) and the raw
+            // slab of x ([16 channels][152 pixels] starting W + 1 pixels before the K-block, rounded down to 16 bytes)
             if (lane == 0) {
                 int g = 0;
                 const int W = P.img_w, cpi = P.chunks_per_image;
@@ -876,14 +927,13 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     const int mn = t % tiles_mn;
                     const int c0 = (mn % P.tiles_m) * WS_CH, n0 = (mn / P.tiles_m) * BN_;
                     for (int it = 0; it < nkb; it++, g++) {
-                        const int s = g % STAGES;
-                        if (!mbar_wait(bar_empty + 8 * s, ((g / STAGES) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 11; break; }
+                        const int h = g % HS;
+                        if (!mbar_wait(bar_raw_full + 8 * (HS + h), ((g / HS) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 13; break; }
                         const int kbi = kb0 + it, img = kbi / cpi, x0 = (kbi % cpi) * 32;
                         const int base = ((x0 - W - 1 + 4096) & ~3) - 4096;
-                        const uint32_t dstB = smem_u32(stage_base + s * L::STAGE_BYTES) + (SPLIT3 ? 2 : 1) * L::A_BYTES;
-                        mbar_expect_tx(bar_raw_full + 8 * s, (uint32_t)(L::B_BYTES + L::WSLAB_BYTES));
-                        tma_load_3d(dstB, &P.mapOut, x0, n0, img, bar_raw_full + 8 * s);
-                        tma_load_3d(smem_u32(raw_base + s * L::WSLAB_BYTES), &P.mapA, base, c0, img, bar_raw_full + 8 * s);
+                        mbar_expect_tx(bar_raw_full + 8 * h, (uint32_t)(WL::B_BYTES + WL::X_BYTES));
+                        tma_load_3d(smem_u32(w_hib + h * WL::B_BYTES), &P.mapOut, x0, n0, img, bar_raw_full + 8 * h);
+                        tma_load_3d(smem_u32(w_x + h * WL::X_BYTES), &P.mapA, base, c0, img, bar_raw_full + 8 * h);
                     }
                 }
             }
@@ -900,7 +950,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     const int base = ((t0 - P.img_w - 1 + 4096) & ~3) - 4096;
                     for (int cg = 0; cg < nkb / 9; cg++, ss++) {
                         const int rs = ss & 1;
-                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((ss >> 1) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 12; break; }
+                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((ss >> 1) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 14; break; }
                         mbar_expect_tx(bar_raw_full + 8 * rs, (uint32_t)(2 * L::RAW_BYTES));
                         tma_load_3d(smem_u32(raw_base + rs * (2 * L::RAW_BYTES)), &P.mapA, base, (kb0 / 9 + cg) * BK, img, bar_raw_full + 8 * rs);
                     }
@@ -921,7 +971,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
                     for (int j = 0; j < 4; j++) { zs[j] = (cm0 + j) / P.chunks_per_image; xs[j] = ((cm0 + j) % P.chunks_per_image) * 32; }
                     for (int it = 0; it < nkb; it++, g++) {
                         const int rs = g % RAWS;
-                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((g / RAWS) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 13; break; }
+                        if (!mbar_wait(bar_raw_empty + 8 * rs, ((g / RAWS) & 1) ^ 1, abort_flag)) { failed = true, fail_code = 15; break; }
                         mbar_expect_tx(bar_raw_full + 8 * rs, (uint32_t)L::RAW_BYTES);
                         const uint32_t dst = smem_u32(raw_base + rs * L::RAW_BYTES);
 #pragma unroll
@@ -973,7 +1023,7 @@ __global__ void __launch_bounds__(threads_of(TMA), 1) igemm_tc_kernel(const __gr
             const int mn = t % tiles_mn, split = t / tiles_mn;
             const int m0 = (mn % P.tiles_m) * BM, n0 = (mn / P.tiles_m) * BN_;
             const int set = local % nsets;
-            if (!mbar_wait_warp(bar_acc_full + 8 * set, (local / nsets) & 1, abort_flag)) { failed = true, fail_code = 14; break; }
+            if (!mbar_wait_warp(bar_acc_full + 8 * set, (local / nsets) & 1, abort_flag)) { failed = true, fail_code = 16; break; }
             tc_fence_after();
             if constexpr (ATMA) {
                 // This warp's 32 rows are one 32-pixel chunk of one image.  Per 32 columns: drain the accumulators, write the
@@ -1318,14 +1368,15 @@ __global__ void __launch_bounds__(256) pack_b_multi_kernel(const __grid_constant
 template <int BN_, int PREC, bool WGRAD, bool BGATHER = false, int TMA = 0>
 int launch_variant(DevCtx *cx, cudaStream_t st, const TcParams &P, dim3 grid, int dev) {
     using L = Layout<BN_, PREC != 1, TMA == 1 || TMA == 3, TMA == 4>;
+    constexpr int SMEM = (TMA == 2 || TMA == 4) ? WLayout<BN_, PREC != 1, TMA == 4>::SMEM_BYTES : L::SMEM_BYTES;
     static bool configured_dev[EDDLB200_MAX_DEVICES] = {};
     bool &configured = configured_dev[dev];
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return cuda_status(e, "conv_tc(smem attribute)");
         configured = true;
     }
-    igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER, TMA><<<grid, threads_of(TMA), L::SMEM_BYTES, st>>>(P);
+    igemm_tc_kernel<BN_, PREC, WGRAD, BGATHER, TMA><<<grid, threads_of(TMA), SMEM, st>>>(P);
     EB_LAUNCH_CHECK("conv_tc");
     return 0;
 }

@@ -1782,6 +1782,15 @@ __global__ void __launch_bounds__(256) col2im_gather_kernel(ConvGeom g, const fl
     }
 }
 
+// out[c][r] = in[r][c] for a small rows x cols matrix (the weight tensor of a few-channel layer)
+__global__ void __launch_bounds__(256) transpose_kernel(const float *__restrict__ in, float *__restrict__ out, int rows, int cols) {
+    const size_t total = (size_t)rows * cols, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int c = (int)(i / rows), r = (int)(i - (size_t)c * rows);
+        out[i] = __ldg(in + (size_t)r * cols + c);
+    }
+}
+
 // Backward-data for layers with very few input channels (the 7x7 stem: C = 3).  With pixels on M and channels on N the
 // GEMM would gather every dy value for 3 useful columns out of 32; instead T[(n,p,q)][(c,r,s)] = sum_f dy * w is one dense
 // GEMM that reads dy exactly once (K = filters), followed by the gather-form col2im above.
@@ -1797,11 +1806,36 @@ int run_small_c_bwd_data(DevCtx *cx, cudaStream_t st, int dev, const ConvGeom &g
         if (cudaMalloc((void **)&tbuf[dev], t_elems * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return 1; }
         tcap[dev] = t_elems;
     }
-    TableArgs T{};
-    T.g = g; T.mode = 3;
-    TcParams P{};
-    T.M_total = g.n * pq; T.N_total = g.c * rs; T.K_total = g.k; P.limY = 1; P.limX = 1; P.out_n_stride = pq;
-    if (int r = run_one(cx, st, dev, T, P, dy, w, tbuf[dev], nullptr, precision, t_elems, false)) return r;
+    // The GEMM is a 1x1 stride-1 convolution of dy ([image][filter][pixel], the filters as input channels) with the weights
+    // transposed to [(c, r, s)][filter]: with a transposed copy of the (small) weight tensor it runs on the TMA-fed kernel,
+    // whose epilogue hands whole blocks to TMA stores -- this GEMM has two K-blocks per tile and writes 12 times what it reads
+    static float *wt[EDDLB200_MAX_DEVICES] = {}; static size_t wcap[EDDLB200_MAX_DEVICES] = {};
+    const size_t w_elems = (size_t)g.k * g.c * rs;
+    bool dense = g_conv_tma > 0 && pq % 4 == 0 && pq >= 32 && g.k >= 32 && g.c * rs >= 32 && pq < 16000 * 16000;
+    if (dense && wcap[dev] < w_elems) {
+        cudaStreamSynchronize(st);
+        if (wt[dev]) cudaFree(wt[dev]);
+        wt[dev] = nullptr; wcap[dev] = 0;
+        if (cudaMalloc((void **)&wt[dev], w_elems * sizeof(float)) != cudaSuccess) { cudaGetLastError(); dense = false; }
+        else wcap[dev] = w_elems;
+    }
+    if (dense) {
+        transpose_kernel<<<grid_for(w_elems, 256), 256, 0, st>>>(w, wt[dev], g.k, g.c * rs);
+        EB_LAUNCH_CHECK("conv_tc(transpose weights)");
+        if (watch_any(cx)) note_write(cx, wt[dev], w_elems * sizeof(float));       // the packed image of the copy is stale now
+        // the plane as one row of pq pixels: a 1x1 layer does not care about its two-dimensional shape
+        const ConvGeom g1{g.n, g.k, 1, pq, g.c * rs, 1, 1, 1, pq, 1, 1, 0, 0};
+        const int r = pq < 16000 ? run(cx, st, dev, 0, g1, dy, wt[dev], tbuf[dev], nullptr, precision) : 1;
+        if (r != 0 && r != 1) return r;
+        dense = r == 0;
+    }
+    if (!dense) {
+        TableArgs T{};
+        T.g = g; T.mode = 3;
+        TcParams P{};
+        T.M_total = g.n * pq; T.N_total = g.c * rs; T.K_total = g.k; P.limY = 1; P.limX = 1; P.out_n_stride = pq;
+        if (int r = run_one(cx, st, dev, T, P, dy, w, tbuf[dev], nullptr, precision, t_elems, false)) return r;
+    }
     col2im_gather_kernel<<<grid_for((size_t)g.n * g.c * g.ih * g.iw, 256), 256, 0, st>>>(g, tbuf[dev], dx);
     EB_LAUNCH_CHECK("conv_tc(col2im gather)");
     return 0;

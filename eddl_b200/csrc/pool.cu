@@ -12,6 +12,7 @@
 // gather form -- one thread per INPUT element that visits the (at most
 // ceil(kr/sr)*ceil(kc/sc)) windows covering it in increasing output order -- so there
 // are no float atomics and the sum order equals the reference's sequential order.
+#include <cstdint>
 #include "common.cuh"
 
 namespace {
@@ -240,6 +241,28 @@ __global__ void __launch_bounds__(256) maxpool_bwd_plane_kernel(const float *__r
                 *reinterpret_cast<float4 *>(idp + base) = acc;        // untouched elements get their own value back
                 xq += dxq; y += dy;
                 if (xq >= iw4) { xq -= iw4; y++; }
+            }
+        } else if ((g.iw & 1) == 0 && (((uintptr_t)id) & 7) == 0) {
+            // the same with two elements per thread (rows of an even length that is not a multiple of four, e.g. the 114 x 114
+            // planes behind an explicit padding layer): 8-byte accesses to the input delta
+            const int iw2 = g.iw >> 1;
+            int y = threadIdx.x / iw2, xq = threadIdx.x - y * iw2;
+            const int dy = blockDim.x / iw2, dxq = blockDim.x - dy * iw2;
+#pragma unroll 2
+            for (int q2 = threadIdx.x; q2 < (ipl >> 1); q2 += blockDim.x) {
+                const int rt = rowtab[y], x0 = xq << 1, base = q2 << 1;
+                const int oi0 = rt & 0xffff, oi1 = rt >> 16, oj0 = coltab[x0] & 0xffff, oj1 = coltab[x0 + 1] >> 16;
+                float2 acc = id_zero ? make_float2(0.f, 0.f) : *reinterpret_cast<const float2 *>(idp + base);
+                for (int oi = oi0; oi <= oi1; oi++)
+                    for (int oj = oj0; oj <= oj1; oj++) {
+                        const int p = oi * g.ow + oj, e = skey[p] - base;
+                        const float v = sd[p];
+                        acc.x = e == 0 ? __fadd_rn(acc.x, v) : acc.x;
+                        acc.y = e == 1 ? __fadd_rn(acc.y, v) : acc.y;
+                    }
+                *reinterpret_cast<float2 *>(idp + base) = acc;
+                xq += dxq; y += dy;
+                if (xq >= iw2) { xq -= iw2; y++; }
             }
         } else {
             int y = threadIdx.x / g.iw, x = threadIdx.x - y * g.iw;

@@ -137,7 +137,9 @@ POOL_CASES = [((2, 2), (2, 2), (0, 0, 0, 0), (2, 3, 28, 28)), ((2, 2), (2, 2), (
               ((3, 3), (1, 1), (1, 1, 1, 1), (1, 3, 33, 34)),
               # four-elements-per-thread path (width a multiple of 4): nine covering windows per element; windows with gaps
               ((3, 3), (1, 1), (1, 1, 1, 1), (2, 2, 36, 40)), ((2, 2), (3, 3), (0, 0, 0, 0), (1, 2, 36, 36)),
-              ((5, 5), (2, 2), (2, 2, 2, 2), (1, 2, 32, 48))]
+              ((5, 5), (2, 2), (2, 2, 2, 2), (1, 2, 32, 48)),
+              # two-elements-per-thread path (even width, not a multiple of 4): the 114 x 114 planes behind ResNet's padding layer
+              ((3, 3), (2, 2), (0, 0, 0, 0), (2, 3, 114, 114)), ((3, 3), (1, 1), (1, 1, 1, 1), (1, 2, 33, 34)), ((2, 2), (2, 2), (0, 0, 0, 0), (1, 3, 38, 42))]
 
 
 @pytest.mark.parametrize("kernel,stride,pads,shape", POOL_CASES)

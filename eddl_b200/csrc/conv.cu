@@ -38,13 +38,17 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const float *__restrict_
 // Such a layer is a dense 1x1 stride-1 convolution over the pixels it actually reads.  Gathering those pixels into a dense
 // [image][channel][pitch] copy (pitch = pixels rounded up to four, the tail zero) is one pass over the smaller tensor, after which
 // the TMA-fed kernels apply: the strided kernels spend most of their time computing addresses, the copy moves a few tens of MB.
+// dst plane: rows of `ow` elements of which the first `vw` come from the source (the rest are zero), npix elements in all
 __global__ void __launch_bounds__(256) plane_gather_kernel(const float *__restrict__ src, float *__restrict__ dst, unsigned total,
-                                                           int ihw, int iw, int sr, int sc, int ow, int npix, int pitch) {
+                                                           int ihw, int iw, int sr, int sc, int ow, int vw, int npix, int pitch) {
     const unsigned stride = gridDim.x * blockDim.x;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         const unsigned plane = idx / (unsigned)pitch, p = idx - plane * pitch;
         float v = 0.f;
-        if (p < (unsigned)npix) { const unsigned oy = p / (unsigned)ow, ox = p - oy * ow; v = src[(size_t)plane * ihw + oy * sr * iw + ox * sc]; }
+        if (p < (unsigned)npix) {
+            const unsigned oy = p / (unsigned)ow, ox = p - oy * ow;
+            if (ox < (unsigned)vw) v = src[(size_t)plane * ihw + oy * sr * iw + ox * sc];
+        }
         dst[idx] = v;
     }
 }
@@ -123,9 +127,10 @@ float *dense_buf(cudaStream_t st, int slot, size_t bytes) {
     return buf[dev][slot];
 }
 
-int gather_planes(DevCtx *cx, cudaStream_t st, const float *src, float *dst, size_t planes, int ih, int iw, int sr, int sc, int oh, int ow, int pitch) {
+int gather_planes(DevCtx *cx, cudaStream_t st, const float *src, float *dst, size_t planes, int ih, int iw, int sr, int sc, int oh, int ow, int pitch,
+                  int valid_w = -1) {
     const unsigned total = (unsigned)(planes * pitch);
-    plane_gather_kernel<<<grid_for(total, 256), 256, 0, st>>>(src, dst, total, ih * iw, iw, sr, sc, ow, oh * ow, pitch);
+    plane_gather_kernel<<<grid_for(total, 256), 256, 0, st>>>(src, dst, total, ih * iw, iw, sr, sc, ow, valid_w < 0 ? ow : valid_w, oh * ow, pitch);
     EB_LAUNCH_CHECK("conv2D(gather)");
     return 0;
 }
@@ -267,6 +272,23 @@ int eddlb200_conv2d_bwd_weight(int dev, const float *x, const float *dy, float *
     if (gbias) {
         bias_grad_kernel<<<k, 256, 0, st>>>(dy, gbias, n, k, oh * ow);
         EB_LAUNCH_CHECK("gpu_conv2D_grad(bias)");
+    }
+    if (tc_enabled() && g_conv_dense && kr == 3 && kc == 3 && sr == 1 && sc == 1 && pad_top == 1 && pad_left == 1 && ih == oh && iw == ow &&
+        (ih * iw) % 4 != 0 && ih * iw >= 32 && c >= 14 && k >= 32) {
+        // A 3x3 "same" layer on a ragged plane (7x7 = 49 pixels): the TMA-fed backward-weight kernel needs planes of a multiple of
+        // four pixels.  Copies of x and dy with rows padded by zero columns give it one: the zero column of dy adds nothing, the
+        // zero column of x is exactly what the right-hand padding of the layer reads, and the left edge is masked by the kernel.
+        int wp = iw + 1;
+        while ((ih * wp) % 4 != 0) wp++;
+        float *xs = dense_buf(st, 0, (size_t)n * c * ih * wp * sizeof(float));
+        float *dys = dense_buf(st, 1, (size_t)n * k * ih * wp * sizeof(float));
+        if (xs && dys) {
+            if (int r = gather_planes(cx, st, x, xs, (size_t)n * c, ih, iw, 1, 1, ih, wp, ih * wp, iw)) return r;
+            if (int r = gather_planes(cx, st, dy, dys, (size_t)n * k, oh, ow, 1, 1, oh, wp, oh * wp, ow)) return r;
+            const ConvGeom gp{n, c, ih, wp, k, 3, 3, oh, wp, 1, 1, 1, 1};
+            int r = conv_tc_bwd_weight(cx, st, gp, xs, dys, gw, precision, gw_zero);
+            if (r != 1) { g_conv_calls[dev][0]++; return r; }
+        }
     }
     if (tc_enabled()) {
         const Dense1x1 d = dense_1x1(g, false);

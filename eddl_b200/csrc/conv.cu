@@ -156,6 +156,7 @@ bool tc_enabled() {
 }  // namespace
 
 namespace eb {
+bool conv_tc_allowed() { return tc_enabled(); }
 int splitk_reduce_accumulate(DevCtx *cx, cudaStream_t st, const float *part, float *out, size_t count, int splits) {
     splitk_reduce_kernel<<<grid_for(count, 256), 256, 0, st>>>(part, out, count, splits);
     EB_LAUNCH_CHECK("splitk_reduce");

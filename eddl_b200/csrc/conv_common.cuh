@@ -22,6 +22,8 @@ int conv_tc_fwd(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, 
 // dx_zero: dx is known to hold zeros (the caller took over a deferred zero fill of it), so the result may be stored
 // instead of added; routes that cannot use this write the zeros first.
 int conv_tc_bwd_data(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *dy, const float *w, float *dx, int precision, bool dx_zero);
+int conv_tc_gemm(DevCtx *cx, cudaStream_t st, const float *a, int ta, const float *b, int tb, float *c, int inc_c, int m, int n, int k, int precision);
+bool conv_tc_allowed();          // false while eddlb200_set_option("conv_path", 1) / EDDL_B200_CONV=simt forces the fp32 FMA kernels
 int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const float *x, const float *dy, float *gw, int precision, bool gw_zero);
 
 // 1 (default): the tensor-core kernel's prefetch warp pulls the activation operand of 1x1 layers into L2 ahead of the gather.

@@ -1236,6 +1236,9 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
                 const int n = m / pq, t = m - n * pq;
                 T.rowA[m] = make_int2(n * g.k * pq + t, pack_yx(0, 0));
                 T.outM[m] = n * g.c * rs * pq + t;
+            } else if (T.mode == 4) {       // plain GEMM C[M x N] = op(A) op(B): g.n = M, g.c = K, g.k = N, g.ih / g.iw = transpose flags
+                T.rowA[m] = make_int2(g.ih ? m : m * g.c, pack_yx(0, 0));
+                T.outM[m] = m * g.k;
             } else {                        // (c, r, s)
                 const int c = m / rs, t = m - c * rs, r = t / g.kc, s = t - r * g.kc;
                 T.rowA[m] = make_int2(c * hw + (r - g.pt) * g.iw + (s - g.pl), pack_yx(r - g.pt, s - g.pl));
@@ -1264,6 +1267,9 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
             } else if (T.mode == 3) {       // filter f
                 T.kA[k] = make_int2(k * pq, pack_yx(0, 0));
                 T.kB[k] = k * g.c * rs;
+            } else if (T.mode == 4) {       // op(A)[m][k] = A[k * M + m] or A[m * K + k];  op(B)[k][n] = B[n * K + k] or B[k * N + n]
+                T.kA[k] = make_int2(g.ih ? k * g.n : k, pack_yx(0, 0));
+                T.kB[k] = g.iw ? k : k * g.k;
             } else {                        // (n, p, q)
                 const int n = k / pq, t = k - n * pq, p = t / g.ow, q = t - p * g.ow;
                 T.kA[k] = make_int2(n * g.c * hw + p * g.sr * g.iw + q * g.sc, pack_yx(p * g.sr, q * g.sc));
@@ -1276,6 +1282,7 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableArgs T) {
             if (T.mode == 0) T.rowB[n] = n * g.c * rs;          // filter row of w[f][c*r*s]
             else if (T.mode == 1) T.rowB[n] = n * rs;           // in-channel c of w[f][c][r][s]
             else if (T.mode == 3) T.rowB[n] = n;                // (c,r,s) column of w[f][c*r*s]
+            else if (T.mode == 4) T.rowB[n] = g.iw ? n * g.c : n;
             else T.rowB[n] = n * pq;                            // filter plane of dy[n][f][p*q]
         }
     }
@@ -1531,7 +1538,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     // how the gathered operand is tested against the zero padding
     T.limY = P.limY; T.limX = P.limX;
     T.check = 2;
-    if (mode == 3) T.check = (T.K_total % BK == 0) ? 0 : 2;
+    if (mode == 3 || mode == 4) T.check = (T.K_total % BK == 0) ? 0 : 2;
     else if (mode == 0) {
         const bool inside = g.pt == 0 && g.pl == 0 && (g.oh - 1) * g.sr + g.kr <= g.ih && (g.ow - 1) * g.sc + g.kc <= g.iw;
         T.check = (inside && T.K_total % BK == 0) ? 0 : (g.kr * g.kc <= 31 ? 1 : 2);
@@ -1674,13 +1681,16 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
         EB_LAUNCH_CHECK("conv_tc(tables)");
     }
     P.packedB = nullptr;
+    // which coordinate of B is contiguous in memory (the pack kernel reads along it): the in-channel row for backward-data,
+    // n for a GEMM whose B is not transposed
+    const bool b_row_fastest = mode == 1 || (mode == 4 && !g.iw);
     if (mode != 2) {
         const float *img = tb_cached ? packed_weights(cx, st, dev, table_key(T), bn, precision, srcB, (size_t)g.k * g.c * g.kr * g.kc * sizeof(float),
-                                                       T.rowB, T.kB, kblocks, tiles_n, T.N_total, mode == 1) : nullptr;
+                                                       T.rowB, T.kB, kblocks, tiles_n, T.N_total, b_row_fastest) : nullptr;
         if (!img) {
             // no cached image (tables not cached, cache full, or allocation failed): pack into the scratch arena for this call
             dim3 pgrid(kblocks, tiles_n);
-            pack_b_kernel<<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, mode == 1, precision);
+            pack_b_kernel<<<pgrid, 256, 0, st>>>(srcB, T.rowB, T.kB, (float *)(ws + o_pack), bn, T.N_total, tiles_n, b_row_fastest, precision);
             EB_LAUNCH_CHECK("conv_tc(pack weights)");
             img = (const float *)(ws + o_pack);
         }
@@ -1695,7 +1705,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     P.nmain = (kbs * (BK / 8) > 64) ? NMAIN : 1;
     P.status = g_status[dev];
     if (splits > 1) { P.out = (float *)(ws + o_part); P.split_stride = (long long)out_total; P.accumulate = 0; P.bias = nullptr; }
-    else { P.out = out; P.split_stride = 0; P.accumulate = (mode == 1 || mode == 2) && !out_zero; P.add_zero = out_zero; P.bias = bias; }
+    else { P.out = out; P.split_stride = 0; P.accumulate = mode == 4 ? T.ca == 1 : ((mode == 1 || mode == 2) && !out_zero); P.add_zero = out_zero; P.bias = bias; }
     P.reduce_out = (atma || stma) && P.accumulate;
     const long long total_tiles = (long long)tiles_m * tiles_n * splits;
     dim3 grid((unsigned)(total_tiles < EDDLB200_NUM_SMS ? total_tiles : EDDLB200_NUM_SMS), 1, 1);
@@ -1715,7 +1725,7 @@ int run_one(DevCtx *cx, cudaStream_t st, int dev, TableArgs T, TcParams P, const
     else r = launch_bn<1, false>(cx, st, P, grid, bn, dev);
     if (r) return r;
     if (splits > 1) {
-        if (mode == 0 || out_zero) {
+        if (mode == 0 || out_zero || (mode == 4 && T.ca != 1)) {
             // `out` holds nothing to add to: store the sum of the partials (0 + p0 + p1 + ...)
             splitk_store_kernel<<<grid_for(out_total, 256), 256, 0, st>>>((const float *)(ws + o_part), out, out_total, splits, mode == 0 ? bias : nullptr, g.oh * g.ow, g.k);
             EB_LAUNCH_CHECK("conv_tc(split-K store)");
@@ -1876,6 +1886,20 @@ int conv_tc_bwd_weight(DevCtx *cx, cudaStream_t st, const ConvGeom &g, const flo
     if (!fits(g)) return 1;
     int dev = 0; cudaGetDevice(&dev);
     return run(cx, st, dev, 2, g, x, dy, gw, nullptr, precision, gw_zero);
+}
+
+// C[m x n] (row-major) = op(A) op(B), += when inc_c == 1, written into known zeros when inc_c == 2: the dense layers' GEMMs
+// (Tensor::mult2D, src/tensor/tensor_math.cpp) on the same kernel, as a "convolution" whose rows are the rows of op(A).
+// 1 = not taken (the caller falls back to the fp32 FMA GEMM).
+int conv_tc_gemm(DevCtx *cx, cudaStream_t st, const float *a, int ta, const float *b, int tb, float *c, int inc_c, int m, int n, int k, int precision) {
+    if ((long long)m * k >= 0x7fffffffLL || (long long)n * k >= 0x7fffffffLL || (long long)m * n >= 0x7fffffffLL) return 1;
+    int dev = 0; cudaGetDevice(&dev);
+    TableArgs T{};
+    T.g = ConvGeom{m, k, ta ? 1 : 0, tb ? 1 : 0, n, 1, 1, 1, 1, 1, 1, 0, 0};
+    T.mode = 4; T.ca = inc_c;
+    TcParams P{};
+    T.M_total = m; T.N_total = n; T.K_total = k; P.limY = 1; P.limX = 1; P.out_n_stride = 1;
+    return run_one(cx, st, dev, T, P, a, b, c, nullptr, precision, (size_t)m * n, true, inc_c == 2);
 }
 
 int conv_tc_set_prefetch(int on) { g_conv_prefetch = on ? 1 : 0; return 0; }

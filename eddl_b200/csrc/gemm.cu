@@ -8,6 +8,7 @@
 // accumulators per thread, exact fp32 accumulation.  When the output has fewer tiles than the GPU has SMs (batch 64:
 // 16 or 32 tiles) the k range is split across blockIdx.z and the partials are combined in a fixed order.
 #include "common.cuh"
+#include "conv_common.cuh"
 
 namespace {
 
@@ -126,6 +127,12 @@ int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, flo
     }
     if (inc_c == 1) EB_MODIFIES(c, (size_t)m * n * sizeof(float)); else EB_WRITES(c, (size_t)m * n * sizeof(float));
     ProfScope prof(cx, PROF_GEMM, 2.0 * m * (double)n * k);
+    // GEMMs of a dense layer's size run on the tensor-core kernel (3xTF32, like the convolutions); tiny ones and a library
+    // forced to the FMA path stay here
+    if (conv_tc_allowed() && k >= 32 && (double)m * n * k >= 262144.0) {
+        const int r = conv_tc_gemm(cx, st, a, ta, b, tb, c, inc_c, m, n, k, 0);
+        if (r != 1) return r;
+    }
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
     const int tiles = (int)(grid.x * grid.y);
     int splits = 1;

@@ -127,9 +127,10 @@ int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, flo
     }
     if (inc_c == 1) EB_MODIFIES(c, (size_t)m * n * sizeof(float)); else EB_WRITES(c, (size_t)m * n * sizeof(float));
     ProfScope prof(cx, PROF_GEMM, 2.0 * m * (double)n * k);
-    // GEMMs of a dense layer's size run on the tensor-core kernel (3xTF32, like the convolutions); tiny ones and a library
-    // forced to the FMA path stay here
-    if (conv_tc_allowed() && k >= 32 && (double)m * n * k >= 262144.0) {
+    // Large products (ResNet-50's 2048 x 1000 classifier at batch 64) run on the tensor-core kernel (3xTF32, like the
+    // convolutions).  Below 2^26 multiply-adds its extra launches (operand packing, split-K combine) cost more than they save
+    // (VGG-16-BN's 512 x 512 layers at batch 128 were 2 % of a step slower there), and a library forced to the FMA path stays here.
+    if (conv_tc_allowed() && k >= 32 && (double)m * n * k >= 67108864.0) {
         const int r = conv_tc_gemm(cx, st, a, ta, b, tb, c, inc_c, m, n, k, 0);
         if (r != 1) return r;
     }

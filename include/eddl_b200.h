@@ -231,7 +231,7 @@ int eddlb200_rand_binary(int dev, float *a, size_t n, float p, size_t seed, size
 /* ---- dense algebra (src/hardware/gpu/gpu_math.cu:457-528; gpu_reduction.cu:232-244;
  *      src/hardware/cpu/cpu_math.cpp:302-325,369-401) */
 /* gpu_mult2D: C[m,n] = (inc_c ? C : 0) + op(A) * op(B), row-major; A is [m,k] (or [k,m]
- * when ta), B is [k,n] (or [n,k] when tb).  Products of a dense layer's size (k >= 32, m n k >= 2^18) run on the
+ * when ta), B is [k,n] (or [n,k] when tb).  Large products (k >= 32, m n k >= 2^26) run on the
  * tensor-core kernel of the convolutions in its fp32-equivalent 3xTF32 mode (about 1e-6 relative); smaller ones, and all of
  * them under "conv_path" 1, on an exact-fp32 FMA kernel. */
 int eddlb200_mult2d(int dev, const float *a, int ta, const float *b, int tb, float *c, int inc_c,

@@ -267,7 +267,8 @@ def test_batchnorm_against_reference_fixture(lib, refout, tag, affine, mom):
 
 
 # ---------------------------------------------------------------------------------------- dense algebra
-@pytest.mark.parametrize("m,n,k", [(7, 5, 13), (100, 10, 576), (128, 512, 512), (64, 1000, 2048), (1, 1, 1), (65, 129, 17)])
+@pytest.mark.parametrize("m,n,k", [(7, 5, 13), (100, 10, 576), (128, 512, 512), (64, 1000, 2048), (1, 1, 1), (65, 129, 17),
+                                   (192, 320, 1100)])       # the last two large ones run on the tensor-core kernel (one with a ragged k)
 def test_mult2d_and_reductions(lib, ref, m, n, k):
     rng = np.random.default_rng(m * n + k)
     a, b, c0 = rnd(rng, m, k), rnd(rng, k, n), rnd(rng, m, n)

@@ -424,7 +424,8 @@ def test_conv_path_counts_tell_fallbacks_from_tensor_core_calls(lib):
 
 WSLAB_SHAPES = SLAB_SHAPES + [(2, 20, 6, 6, 32), (5, 14, 10, 10, 40), (2, 15, 8, 12, 33),
                               # ragged planes (not a multiple of four pixels): run over copies whose rows are padded with zero columns
-                              (3, 64, 7, 7, 48), (2, 33, 9, 9, 40), (4, 16, 5, 11, 32)]
+                              (3, 64, 7, 7, 48), (2, 33, 9, 9, 40), (4, 16, 5, 11, 32),
+                              (2, 16, 8, 57, 32)]          # the widest row a backward-weight slab holds
 
 
 @pytest.mark.parametrize("shape", WSLAB_SHAPES)
